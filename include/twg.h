@@ -1,0 +1,242 @@
+/*
+ * twg.h - C ABI of the B200 (sm_100a) data-parallel op path behind torch-webgpu's
+ * PrivateUse1 operator interface.
+ *
+ * Every entry point is extern "C", takes plain pointers and sizes, returns an int
+ * status (TWG_OK == 0, negative == TwgStatus error), never throws, never aborts and
+ * never blocks the host unless its comment says "blocks".  twg_last_error() returns
+ * a thread-local message for the most recent failing call on the calling thread.
+ *
+ * Each declaration names the reference interface (path inside the torch-webgpu
+ * project : line) that it replaces.  The reference reaches its GPU through two
+ * launcher templates, binary_kernel<Op>(iter, alpha) and unary_kernel<Op>(iter)
+ * (csrc/ops/binary.h:29-30, csrc/ops/unary.h:30-31), an allocator
+ * (csrc/core/webgpu_allocator.h:17) and Queue.WriteBuffer / CopyBufferToBuffer /
+ * MapAsync calls in csrc/ops/copy.cpp; this header is what a foreign-function
+ * binding for that path would bind instead.
+ *
+ * Conventions
+ *   - "stream" is a cudaStream_t passed as void*; NULL is the legacy default stream.
+ *   - Device pointers must belong to the device that is current on the calling
+ *     thread (twg_set_device), except for twg_malloc which takes the ordinal.
+ *   - bool tensors are arrays of bytes holding exactly 0x00 or 0x01.
+ */
+#ifndef TWG_H_
+#define TWG_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TWG_MAX_DIMS 8      /* same limit as the reference (csrc/ops/binary.h:105-106) */
+#define TWG_MAX_TENSORS 8   /* operands of one pointwise launch: outputs first, then inputs */
+
+typedef enum TwgStatus {
+  TWG_OK = 0,
+  TWG_ERR_INVALID = -1,      /* bad argument (null pointer, ndim > 8, unknown op ...) */
+  TWG_ERR_CUDA = -2,         /* a CUDA runtime/driver call failed; see twg_last_error() */
+  TWG_ERR_OOM = -3,          /* device allocation failed even after emptying the cache */
+  TWG_ERR_TIMEOUT = -4,      /* a bounded device-side wait gave up (masked_select look-back) */
+  TWG_ERR_UNSUPPORTED = -5,  /* valid request that this build has no kernel for */
+  TWG_ERR_INJECTED = -6      /* host-side fault injection hook fired (tests only) */
+} TwgStatus;
+
+/* ------------------------------------------------------------------------------------------
+ * Iteration descriptor.  Same information the reference packs into its `Params` uniform
+ * (csrc/ops/binary.h:108-124, csrc/ops/unary.h:88-101) but 64-bit, in ELEMENTS, and passed
+ * by value to the kernel.  Dimension 0 varies fastest (at::TensorIterator order).
+ * strides[t][d] is operand t's stride along dimension d; operands are ordered outputs
+ * first, then inputs, matching iter.tensor(i).  A stride of 0 broadcasts.  Data pointers
+ * handed to the entry points already include the tensor's storage offset.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct TwgIterDesc {
+  int32_t ndim;      /* 0..TWG_MAX_DIMS; 0 with numel==1 is a scalar */
+  int32_t ntensors;  /* number of operand rows of `strides` that are valid */
+  int64_t numel;     /* product of shape[0..ndim) */
+  int64_t shape[TWG_MAX_DIMS];
+  int64_t strides[TWG_MAX_TENSORS][TWG_MAX_DIMS];
+} TwgIterDesc;
+
+/* Fill `d` for `ntensors` dense 1-D operands of `numel` elements. */
+int twg_iter_contiguous(TwgIterDesc* d, int ntensors, int64_t numel);
+/* Merge adjacent dimensions that every operand walks as one dense run and drop size-1
+ * dimensions, preserving element order (what at::TensorIterator::coalesce_dimensions does
+ * before the reference reads iter.shape()/strides(), csrc/ops/binary.h:43-47). */
+int twg_iter_coalesce(TwgIterDesc* d);
+
+/* ---- library / device / stream (replaces WebGPUContext, csrc/core/webgpu_context.cpp:9-68,
+ *      and the guard's device bookkeeping, csrc/core/webgpu_device_guard.cpp:9-49) -------- */
+const char* twg_last_error(void);
+const char* twg_version(void);
+int twg_device_count(int* count);
+int twg_set_device(int device);
+int twg_get_device(int* device);
+/* Per-device stream pool.  index 0 is the device's compute stream, 1 its copy stream,
+ * 2..TWG_NUM_STREAMS-1 spare streams handed out by the guard's getNewStream. */
+#define TWG_NUM_STREAMS 8
+int twg_get_stream(int device, int index, void** stream);
+int twg_stream_sync(void* stream);           /* blocks */
+int twg_device_sync(int device);             /* blocks */
+int twg_stream_query(void* stream, int* done);
+/* events (c10::DeviceGuardImplInterface record/block/queryEvent; the reference has none) */
+int twg_event_create(void** event);
+int twg_event_destroy(void* event);
+int twg_event_record(void* event, void* stream);
+int twg_event_wait(void* event, void* stream);       /* stream waits; host does not */
+int twg_event_query(void* event, int* done);
+int twg_event_sync(void* event);                     /* blocks */
+int twg_event_elapsed_ms(void* start, void* stop, float* ms);
+
+/* ---- caching allocator (replaces WebGPUAllocator::allocate / WebGPUCachingAllocator,
+ *      csrc/core/webgpu_allocator.cpp:10-49, which creates one wgpu::Buffer per tensor) ---- */
+typedef struct TwgMemStats {
+  int64_t allocated_bytes;      /* bytes in live blocks */
+  int64_t reserved_bytes;       /* bytes obtained from cudaMalloc and still held */
+  int64_t peak_allocated_bytes;
+  int64_t peak_reserved_bytes;
+  int64_t num_allocs;           /* twg_malloc calls served */
+  int64_t num_cache_hits;       /* ... of which from the free lists */
+  int64_t num_device_mallocs;   /* cudaMalloc calls */
+  int64_t num_device_frees;     /* cudaFree calls */
+} TwgMemStats;
+int twg_malloc(void** ptr, size_t nbytes, int device, void* stream);  /* nbytes==0 -> *ptr=NULL */
+int twg_free(void* ptr);                                   /* NULL is a no-op */
+int twg_record_stream(void* ptr, void* stream);            /* block is also in use on `stream` */
+int twg_trim(void* ptr, size_t new_nbytes);                /* give the tail of a block back */
+int twg_block_size(void* ptr, size_t* nbytes, int* device);
+int twg_empty_cache(int device);                           /* device < 0: all devices; blocks */
+int twg_memory_stats(int device, TwgMemStats* stats);
+int twg_reset_peak_stats(int device);
+/* Host-side fault injection for tests: cap on reserved bytes per device (0 = no cap). */
+int twg_set_memory_budget(int device, size_t max_reserved_bytes);
+
+/* ---- copies (replaces Queue.WriteBuffer, copy.cpp:90; CopyBufferToBuffer, copy.cpp:113-120;
+ *      the MapAsync read-back, copy.cpp:27-55) ---------------------------------------------- */
+/* Host -> device.  Pinned sources are one cudaMemcpyAsync; pageable sources are staged through
+ * a ring of pinned buffers and the call returns once the source has been consumed. */
+int twg_memcpy_h2d(void* dst_dev, const void* src_host, size_t nbytes, void* stream);
+/* Device -> host.  If `blocking` is non-zero, or the destination is pageable, the call returns
+ * after the bytes are in `dst_host` (blocks); otherwise it is a single cudaMemcpyAsync. */
+int twg_memcpy_d2h(void* dst_host, const void* src_dev, size_t nbytes, void* stream, int blocking);
+int twg_memcpy_d2d(void* dst_dev, const void* src_dev, size_t nbytes, void* stream);
+int twg_memset(void* dst_dev, int value, size_t nbytes, void* stream);
+int twg_host_alloc_pinned(void** ptr, size_t nbytes);
+int twg_host_free_pinned(void* ptr);
+/* Strided / broadcasting device copy of `itemsize`-byte elements (1, 2, 4, 8 or 16).
+ * Replaces unary_kernel<UnaryOp::Copy> (csrc/ops/copy.cpp:123-134, unary.cpp:88).
+ * desc operands: [0] = out, [1] = in. */
+int twg_copy_strided(const TwgIterDesc* desc, int itemsize, const void* in, void* out, void* stream);
+
+/* ---- pointwise kernels ------------------------------------------------------------------- */
+typedef enum TwgUnaryOp {
+  TWG_UNARY_COPY = 0,       /* unary.cpp:88  */
+  TWG_UNARY_RELU = 1,       /* unary.cpp:91  */
+  TWG_UNARY_GELU_TANH = 2,  /* unary.cpp:94 (the only GELU the reference computes) */
+  TWG_UNARY_SILU = 3,       /* unary.cpp:97  */
+  TWG_UNARY_GELU_ERF = 4,   /* approximate='none'; the reference ignores the argument
+                               (activation_functions.cpp:56) and its tests compare against
+                               the erf form (tests/ops/test_gelu.py:11-14) */
+  TWG_UNARY_ABS = 5         /* CPU fallback in the reference (bindings.cpp:35) */
+} TwgUnaryOp;
+typedef enum TwgBinaryOp {
+  TWG_BINARY_ADD = 0,             /* out = a + alpha*b, one rounding (binary.cpp:97) */
+  TWG_BINARY_MUL = 1,             /* binary.cpp:100 */
+  TWG_BINARY_FUSED_ADD_RELU = 2   /* binary.cpp:103 */
+} TwgBinaryOp;
+typedef enum TwgCompareOp { TWG_CMP_EQ = 0, TWG_CMP_NE = 1, TWG_CMP_LT = 2, TWG_CMP_LE = 3,
+                            TWG_CMP_GT = 4, TWG_CMP_GE = 5 } TwgCompareOp;
+
+/* unary_kernel<Op>(iter) (csrc/ops/unary.h:30-181).  desc operands: [0]=out, [1]=in. */
+int twg_unary_f32(int op, const TwgIterDesc* desc, const float* in, float* out, void* stream);
+/* binary_kernel<Op>(iter, alpha) (csrc/ops/binary.h:29-215).  desc: [0]=out, [1]=a, [2]=b. */
+int twg_binary_f32(int op, const TwgIterDesc* desc, const float* a, const float* b, float alpha,
+                   float* out, void* stream);
+/* eq.Tensor / ne.Scalar ..., CPU fallbacks in the reference (csrc/bindings.cpp:36-39).
+ * b == NULL compares against `scalar`; then desc has operands [0]=out, [1]=a only,
+ * otherwise [0]=out, [1]=a, [2]=b.  out is bool bytes. */
+int twg_compare_f32(int op, const TwgIterDesc* desc, const float* a, const float* b, float scalar,
+                    uint8_t* out, void* stream);
+/* bitwise_and.Tensor(_out), CPU fallback in the reference (csrc/bindings.cpp:40-41).
+ * itemsize 1 with is_bool != 0 is logical and of bool bytes; itemsize 1/2/4/8 otherwise is the
+ * integer bitwise and.  desc: [0]=out, [1]=a, [2]=b. */
+int twg_bitwise_and(const TwgIterDesc* desc, int itemsize, int is_bool, const void* a, const void* b,
+                    void* out, void* stream);
+
+/* ---- masked_select, CPU fallback in the reference (csrc/bindings.cpp:42) ------------------
+ * Single-pass stream compaction.  desc describes the BROADCAST shape in logical row-major
+ * order reversed (dimension 0 = last logical dimension, fastest): operand [0] = src strides,
+ * [1] = mask strides (0 where broadcast).  out receives the selected values in row-major order
+ * and must have room for desc->numel elements.  result_dev points at two int64 on the device:
+ * [0] = number of selected elements, [1] = TwgStatus of the device-side scan (TWG_ERR_TIMEOUT
+ * if the bounded look-back wait gave up).  workspace must hold at least
+ * twg_masked_select_workspace_bytes(numel) bytes, 256-byte aligned; the call clears it. */
+size_t twg_masked_select_workspace_bytes(int64_t numel);
+int twg_masked_select_f32(const TwgIterDesc* desc, const float* src, const uint8_t* mask, float* out,
+                          int64_t* result_dev, void* workspace, size_t workspace_bytes, void* stream);
+/* Test hook: make every look-back wait give up after `polls` polls (0 restores the default). */
+int twg_masked_select_set_poll_budget(int64_t polls);
+
+/* ---- fused pointwise programs for the torch.compile backend ---------------------------------
+ * Replaces the reference's FX -> HighIR -> LowIR -> RUN_SHADER lowering whose only fusion is
+ * ADD,RELU -> webgpu::fused_add_relu (python/torch_webgpu/compiler/high_ir.py:108-120,
+ * lowering.py:36-48).  A program is a straight-line SSA list over f32 / bool values; value i
+ * is the result of instruction i. */
+typedef enum TwgFusedOpcode {
+  TWG_F_INPUT_F32 = 0,   /* a = input slot                      -> f32  */
+  TWG_F_INPUT_BOOL = 1,  /* a = input slot                      -> bool */
+  TWG_F_CONST_F32 = 2,   /* imm                                 -> f32  */
+  TWG_F_ADD = 3,         /* v[a] + imm*v[b], one rounding       -> f32  */
+  TWG_F_MUL = 4,         /* v[a] * v[b]                         -> f32  */
+  TWG_F_RELU = 5,
+  TWG_F_SILU = 6,
+  TWG_F_GELU_ERF = 7,
+  TWG_F_GELU_TANH = 8,
+  TWG_F_ABS = 9,
+  TWG_F_EQ = 10,         /* v[a] == v[b]                        -> bool */
+  TWG_F_NE = 11,
+  TWG_F_LT = 12,
+  TWG_F_LE = 13,
+  TWG_F_GT = 14,
+  TWG_F_GE = 15,
+  TWG_F_AND = 16,        /* bool & bool                         -> bool */
+  TWG_F_OUTPUT = 17      /* store v[a] to output slot b (f32 or bool by v[a]'s type) */
+} TwgFusedOpcode;
+typedef struct TwgFusedInstr {
+  int32_t opcode;
+  int32_t a;
+  int32_t b;
+  float imm;
+} TwgFusedInstr;
+typedef struct TwgFusedProgram TwgFusedProgram;  /* opaque */
+/* Build (or fetch from the cache) the kernel for `prog`.  Programs that match a kernel
+ * instantiated ahead of time in the library are served from it; others are generated from the
+ * same C++ templates and compiled for sm_100a with NVRTC on first use (blocks). */
+int twg_fused_compile(const TwgFusedInstr* prog, int ninstr, TwgFusedProgram** out);
+/* 0 = ahead-of-time instantiation, 1 = NVRTC. */
+int twg_fused_kind(const TwgFusedProgram* p, int* kind);
+/* desc operands: outputs (slot order) first, then inputs (slot order).  ptrs likewise. */
+int twg_fused_launch(const TwgFusedProgram* p, const TwgIterDesc* desc, void* const* ptrs, void* stream);
+int twg_fused_release(TwgFusedProgram* p);
+/* Path of the NVRTC shared library to load on first use (default: the loader's search path for
+ * libnvrtc.so.12, then /usr/local/cuda/lib64).  Honoured only before the first NVRTC build. */
+int twg_fused_set_nvrtc_path(const char* path);
+/* Generated CUDA source of a program (ahead-of-time programs report the same text NVRTC would
+ * be given); the pointer stays valid until twg_fused_release. */
+int twg_fused_source(const TwgFusedProgram* p, const char** source);
+
+/* ---- launch accounting: number of kernels this library launched on the calling thread's
+ *      behalf since the last reset (all threads), used by the benchmark's gpu_launches ----- */
+int64_t twg_launch_count(void);
+void twg_reset_launch_count(void);
+/* Launch shape the most recent pointwise / copy / masked_select call on this thread used:
+ * 0 none (empty tensor), 1 dense vector path, 2 2-D permuted tile path, 3 strided 32-bit index
+ * path, 4 strided 64-bit index path. */
+int twg_last_launch_path(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TWG_H_ */

@@ -1,0 +1,544 @@
+// Fused pointwise programs for the torch.compile backend.
+//
+// A program is a straight-line SSA list over f32 / bool values (TwgFusedInstr).  It becomes ONE
+// kernel: the generated functor is plugged into the same dense / tile / strided launch shapes as
+// the single ops (twg_pointwise.cuh), so intermediates live in registers and never touch HBM.
+// Programs that the library instantiates ahead of time are matched by value; anything else is
+// turned into a small CUDA translation unit around the same header and compiled for sm_100a with
+// NVRTC on first use (loaded with the driver API, cached per device).
+#include <dlfcn.h>
+
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "twg_launch.cuh"
+
+namespace twg {
+
+// The text of twg_pointwise.cuh, embedded at build time for NVRTC.
+static const char kPointwiseHeader[] =
+#include "twg_pointwise_src.inc"
+    ;
+
+// ------------------------------------------------------------------------------------------
+// program analysis
+// ------------------------------------------------------------------------------------------
+enum ValType { kF32 = 0, kBool = 1, kNone = 2 };
+
+struct Analysis {
+  int nin = 0, nout = 0;
+  unsigned in_byte_mask = 0, out_byte_mask = 0;
+  std::vector<int> type;  // per instruction
+};
+
+static int analyse(const TwgFusedInstr* prog, int n, Analysis* a) {
+  TWG_REQUIRE(prog != nullptr && n > 0 && n <= 4096, "fused program: bad instruction count %d", n);
+  a->type.assign(n, kNone);
+  std::vector<int> in_seen, out_seen;
+  for (int i = 0; i < n; ++i) {
+    const TwgFusedInstr& I = prog[i];
+    auto operand = [&](int idx, int want) -> int {
+      if (idx < 0 || idx >= i || a->type[idx] == kNone)
+        return set_error(TWG_ERR_INVALID, "fused program: instruction %d reads value %d which is not defined before it", i, idx);
+      if (a->type[idx] != want)
+        return set_error(TWG_ERR_INVALID, "fused program: instruction %d expects a %s operand", i, want == kF32 ? "f32" : "bool");
+      return TWG_OK;
+    };
+    switch (I.opcode) {
+      case TWG_F_INPUT_F32:
+      case TWG_F_INPUT_BOOL: {
+        TWG_REQUIRE(I.a >= 0 && I.a < TWG_MAX_TENSORS, "fused program: input slot %d out of range", I.a);
+        if ((int)in_seen.size() <= I.a) in_seen.resize(I.a + 1, 0);
+        TWG_REQUIRE(!in_seen[I.a], "fused program: input slot %d is declared twice", I.a);
+        in_seen[I.a] = 1;
+        if (I.opcode == TWG_F_INPUT_BOOL) a->in_byte_mask |= 1u << I.a;
+        a->type[i] = I.opcode == TWG_F_INPUT_BOOL ? kBool : kF32;
+        break;
+      }
+      case TWG_F_CONST_F32: a->type[i] = kF32; break;
+      case TWG_F_ADD:
+      case TWG_F_MUL:
+        if (int rc = operand(I.a, kF32)) return rc;
+        if (int rc = operand(I.b, kF32)) return rc;
+        a->type[i] = kF32;
+        break;
+      case TWG_F_RELU:
+      case TWG_F_SILU:
+      case TWG_F_GELU_ERF:
+      case TWG_F_GELU_TANH:
+      case TWG_F_ABS:
+        if (int rc = operand(I.a, kF32)) return rc;
+        a->type[i] = kF32;
+        break;
+      case TWG_F_EQ:
+      case TWG_F_NE:
+      case TWG_F_LT:
+      case TWG_F_LE:
+      case TWG_F_GT:
+      case TWG_F_GE:
+        if (int rc = operand(I.a, kF32)) return rc;
+        if (int rc = operand(I.b, kF32)) return rc;
+        a->type[i] = kBool;
+        break;
+      case TWG_F_AND:
+        if (int rc = operand(I.a, kBool)) return rc;
+        if (int rc = operand(I.b, kBool)) return rc;
+        a->type[i] = kBool;
+        break;
+      case TWG_F_OUTPUT: {
+        TWG_REQUIRE(I.a >= 0 && I.a < i && a->type[I.a] != kNone, "fused program: output %d stores an undefined value", i);
+        TWG_REQUIRE(I.b >= 0 && I.b < TWG_MAX_TENSORS, "fused program: output slot %d out of range", I.b);
+        if ((int)out_seen.size() <= I.b) out_seen.resize(I.b + 1, 0);
+        TWG_REQUIRE(!out_seen[I.b], "fused program: output slot %d is stored twice", I.b);
+        out_seen[I.b] = 1;
+        if (a->type[I.a] == kBool) a->out_byte_mask |= 1u << I.b;
+        break;
+      }
+      default: return set_error(TWG_ERR_INVALID, "fused program: unknown opcode %d at instruction %d", I.opcode, i);
+    }
+  }
+  for (size_t k = 0; k < in_seen.size(); ++k) TWG_REQUIRE(in_seen[k], "fused program: input slot %zu is never declared", k);
+  for (size_t k = 0; k < out_seen.size(); ++k) TWG_REQUIRE(out_seen[k], "fused program: output slot %zu is never stored", k);
+  a->nin = (int)in_seen.size();
+  a->nout = (int)out_seen.size();
+  TWG_REQUIRE(a->nout >= 1, "fused program: no output");
+  TWG_REQUIRE(a->nin + a->nout <= TWG_MAX_TENSORS, "fused program: %d operands exceed the limit of %d",
+              a->nin + a->nout, TWG_MAX_TENSORS);
+  return TWG_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// source generation
+// ------------------------------------------------------------------------------------------
+static std::string hexf(float f) {
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  char buf[48];
+  snprintf(buf, sizeof(buf), "__uint_as_float(0x%08xu)", u);
+  return buf;
+}
+
+static std::string generate_source(const TwgFusedInstr* prog, int n, const Analysis& a) {
+  std::string s;
+  char line[256];
+  s += "#include \"twg_pointwise.cuh\"\nnamespace twg {\nstruct Prog {\n";
+  snprintf(line, sizeof(line),
+           "  static constexpr int NIN = %d, NOUT = %d;\n  static constexpr unsigned kInByteMask = %uu, kOutByteMask = %uu;\n",
+           a.nin, a.nout, a.in_byte_mask, a.out_byte_mask);
+  s += line;
+  s += "  __device__ __forceinline__ void operator()(const u32* in, u32* out) const {\n";
+  static const char* unary[] = {"f_relu", "f_silu", "f_gelu_erf", "f_gelu_tanh", "f_abs"};
+  static const char* cmp[] = {"f_eq", "f_ne", "f_lt", "f_le", "f_gt", "f_ge"};
+  for (int i = 0; i < n; ++i) {
+    const TwgFusedInstr& I = prog[i];
+    switch (I.opcode) {
+      case TWG_F_INPUT_F32: snprintf(line, sizeof(line), "    const float v%d = as_f(in[%d]);\n", i, I.a); break;
+      case TWG_F_INPUT_BOOL: snprintf(line, sizeof(line), "    const u32 v%d = in[%d];\n", i, I.a); break;
+      case TWG_F_CONST_F32: snprintf(line, sizeof(line), "    const float v%d = %s;\n", i, hexf(I.imm).c_str()); break;
+      case TWG_F_ADD:
+        snprintf(line, sizeof(line), "    const float v%d = f_add(v%d, v%d, %s);\n", i, I.a, I.b, hexf(I.imm).c_str());
+        break;
+      case TWG_F_MUL: snprintf(line, sizeof(line), "    const float v%d = f_mul(v%d, v%d);\n", i, I.a, I.b); break;
+      case TWG_F_RELU:
+      case TWG_F_SILU:
+      case TWG_F_GELU_ERF:
+      case TWG_F_GELU_TANH:
+      case TWG_F_ABS:
+        snprintf(line, sizeof(line), "    const float v%d = %s(v%d);\n", i, unary[I.opcode - TWG_F_RELU], I.a);
+        break;
+      case TWG_F_EQ:
+      case TWG_F_NE:
+      case TWG_F_LT:
+      case TWG_F_LE:
+      case TWG_F_GT:
+      case TWG_F_GE:
+        snprintf(line, sizeof(line), "    const u32 v%d = %s(v%d, v%d);\n", i, cmp[I.opcode - TWG_F_EQ], I.a, I.b);
+        break;
+      case TWG_F_AND: snprintf(line, sizeof(line), "    const u32 v%d = f_and(v%d, v%d);\n", i, I.a, I.b); break;
+      case TWG_F_OUTPUT:
+        if (a.type[I.a] == kBool) snprintf(line, sizeof(line), "    out[%d] = v%d;\n", I.b, I.a);
+        else snprintf(line, sizeof(line), "    out[%d] = as_u(v%d);\n", I.b, I.a);
+        break;
+      default: line[0] = 0;
+    }
+    s += line;
+  }
+  s += "  }\n};\n}  // namespace twg\nusing namespace twg;\n";
+  snprintf(line, sizeof(line), "constexpr int NT = %d;\n", a.nin + a.nout);
+  s += line;
+  snprintf(line, sizeof(line),
+           "extern \"C\" __global__ void __launch_bounds__(kBlock) twg_fused_dense(PwPtrs<NT> p, i64 nunits, i64 n) "
+           "{ pw_contig_body<Prog, %d>(p, Prog{}, nunits, n); }\n", kDenseUnroll);
+  s += line;
+  s += "extern \"C\" __global__ void __launch_bounds__(kTile * kTileRows) twg_fused_tile(PwPtrs<NT> p, TileDesc<NT> d) "
+       "{ pw_tile_body<Prog>(p, Prog{}, d); }\n";
+  snprintf(line, sizeof(line),
+           "extern \"C\" __global__ void __launch_bounds__(kBlock) twg_fused_strided32(PwPtrs<NT> p, StridedDesc<NT, u32> d, i64 n) "
+           "{ pw_strided_body<Prog, %d, u32>(p, Prog{}, d, n); }\n", kStridedUnroll);
+  s += line;
+  snprintf(line, sizeof(line),
+           "extern \"C\" __global__ void __launch_bounds__(kBlock) twg_fused_strided64(PwPtrs<NT> p, StridedDesc<NT, u64> d, i64 n) "
+           "{ pw_strided_body<Prog, %d, u64>(p, Prog{}, d, n); }\n", kStridedUnroll);
+  s += line;
+  return s;
+}
+
+// ------------------------------------------------------------------------------------------
+// programs instantiated ahead of time
+// ------------------------------------------------------------------------------------------
+// relu(a + b): the reference's only fusion (python/torch_webgpu/compiler/high_ir.py:108-120).
+struct AotAddRelu {
+  static constexpr int NIN = 2, NOUT = 1;
+  static constexpr unsigned kInByteMask = 0u, kOutByteMask = 0u;
+  __device__ __forceinline__ void operator()(const u32* in, u32* out) const {
+    out[0] = as_u(f_relu(f_add(as_f(in[0]), as_f(in[1]), 1.0f)));
+  }
+};
+// m = (relu(silu(a + b) + c) == 0) & (a != 0): three f32 streams in, one bool stream out.
+struct AotChainMask {
+  static constexpr int NIN = 3, NOUT = 1;
+  static constexpr unsigned kInByteMask = 0u, kOutByteMask = 1u;
+  __device__ __forceinline__ void operator()(const u32* in, u32* out) const {
+    const float a = as_f(in[0]), b = as_f(in[1]), c = as_f(in[2]);
+    const float y = f_relu(f_add(f_silu(f_add(a, b, 1.0f)), c, 1.0f));
+    out[0] = f_and(f_eq(y, 0.0f), f_ne(a, 0.0f));
+  }
+};
+// Same chain that also keeps y.
+struct AotChainMaskY {
+  static constexpr int NIN = 3, NOUT = 2;
+  static constexpr unsigned kInByteMask = 0u, kOutByteMask = 2u;
+  __device__ __forceinline__ void operator()(const u32* in, u32* out) const {
+    const float a = as_f(in[0]), b = as_f(in[1]), c = as_f(in[2]);
+    const float y = f_relu(f_add(f_silu(f_add(a, b, 1.0f)), c, 1.0f));
+    out[0] = as_u(y);
+    out[1] = f_and(f_eq(y, 0.0f), f_ne(a, 0.0f));
+  }
+};
+
+static const TwgFusedInstr kProgAddRelu[] = {
+    {TWG_F_INPUT_F32, 0, 0, 0.f}, {TWG_F_INPUT_F32, 1, 0, 0.f}, {TWG_F_ADD, 0, 1, 1.f},
+    {TWG_F_RELU, 2, 0, 0.f},      {TWG_F_OUTPUT, 3, 0, 0.f}};
+static const TwgFusedInstr kProgChainMask[] = {
+    {TWG_F_INPUT_F32, 0, 0, 0.f}, {TWG_F_INPUT_F32, 1, 0, 0.f}, {TWG_F_INPUT_F32, 2, 0, 0.f},
+    {TWG_F_ADD, 0, 1, 1.f},       {TWG_F_SILU, 3, 0, 0.f},      {TWG_F_ADD, 4, 2, 1.f},
+    {TWG_F_RELU, 5, 0, 0.f},      {TWG_F_CONST_F32, 0, 0, 0.f}, {TWG_F_EQ, 6, 7, 0.f},
+    {TWG_F_CONST_F32, 0, 0, 0.f}, {TWG_F_NE, 0, 9, 0.f},        {TWG_F_AND, 8, 10, 0.f},
+    {TWG_F_OUTPUT, 11, 0, 0.f}};
+static const TwgFusedInstr kProgChainMaskY[] = {
+    {TWG_F_INPUT_F32, 0, 0, 0.f}, {TWG_F_INPUT_F32, 1, 0, 0.f}, {TWG_F_INPUT_F32, 2, 0, 0.f},
+    {TWG_F_ADD, 0, 1, 1.f},       {TWG_F_SILU, 3, 0, 0.f},      {TWG_F_ADD, 4, 2, 1.f},
+    {TWG_F_RELU, 5, 0, 0.f},      {TWG_F_CONST_F32, 0, 0, 0.f}, {TWG_F_EQ, 6, 7, 0.f},
+    {TWG_F_CONST_F32, 0, 0, 0.f}, {TWG_F_NE, 0, 9, 0.f},        {TWG_F_AND, 8, 10, 0.f},
+    {TWG_F_OUTPUT, 6, 0, 0.f},    {TWG_F_OUTPUT, 11, 1, 0.f}};
+
+typedef int (*AotLaunch)(const TwgIterDesc*, void* const*, cudaStream_t);
+template <class F>
+int aot_launch(const TwgIterDesc* d, void* const* ptrs, cudaStream_t s) { return launch_pointwise(F{}, d, ptrs, s); }
+
+struct AotEntry {
+  const TwgFusedInstr* prog;
+  int n;
+  AotLaunch launch;
+};
+static const AotEntry kAot[] = {
+    {kProgAddRelu, (int)(sizeof(kProgAddRelu) / sizeof(TwgFusedInstr)), &aot_launch<AotAddRelu>},
+    {kProgChainMask, (int)(sizeof(kProgChainMask) / sizeof(TwgFusedInstr)), &aot_launch<AotChainMask>},
+    {kProgChainMaskY, (int)(sizeof(kProgChainMaskY) / sizeof(TwgFusedInstr)), &aot_launch<AotChainMaskY>},
+};
+
+static bool same_program(const TwgFusedInstr* a, int na, const TwgFusedInstr* b, int nb) {
+  if (na != nb) return false;
+  for (int i = 0; i < na; ++i) {
+    if (a[i].opcode != b[i].opcode) return false;
+    const int op = a[i].opcode;
+    const bool uses_b = op == TWG_F_ADD || op == TWG_F_MUL || (op >= TWG_F_EQ && op <= TWG_F_OUTPUT);
+    const bool uses_a = op != TWG_F_CONST_F32;
+    const bool uses_imm = op == TWG_F_CONST_F32 || op == TWG_F_ADD;
+    if (uses_a && a[i].a != b[i].a) return false;
+    if (uses_b && a[i].b != b[i].b) return false;
+    if (uses_imm && memcmp(&a[i].imm, &b[i].imm, 4) != 0) return false;
+  }
+  return true;
+}
+
+// ------------------------------------------------------------------------------------------
+// NVRTC + driver API, loaded lazily with dlopen so that the library itself has no link-time
+// dependency on either (it must load on machines without a GPU driver).
+// ------------------------------------------------------------------------------------------
+typedef struct _nvrtcProgram* nvrtcProgram;
+typedef int nvrtcResult;
+typedef struct CUmod_st* CUmodule;
+typedef struct CUfunc_st* CUfunction;
+typedef struct CUstream_st* CUstream;
+typedef int CUresult;
+
+struct Dyn {
+  std::mutex mu;
+  bool loaded = false;
+  std::string nvrtc_path;
+  void* nvrtc = nullptr;
+  void* cuda = nullptr;
+  nvrtcResult (*CreateProgram)(nvrtcProgram*, const char*, const char*, int, const char* const*, const char* const*);
+  nvrtcResult (*DestroyProgram)(nvrtcProgram*);
+  nvrtcResult (*CompileProgram)(nvrtcProgram, int, const char* const*);
+  nvrtcResult (*GetCUBINSize)(nvrtcProgram, size_t*);
+  nvrtcResult (*GetCUBIN)(nvrtcProgram, char*);
+  nvrtcResult (*GetProgramLogSize)(nvrtcProgram, size_t*);
+  nvrtcResult (*GetProgramLog)(nvrtcProgram, char*);
+  const char* (*GetErrorString)(nvrtcResult);
+  CUresult (*ModuleLoadData)(CUmodule*, const void*);
+  CUresult (*ModuleUnload)(CUmodule);
+  CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*);
+  CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
+                           void**, void**);
+  CUresult (*CuGetErrorString)(CUresult, const char**);
+};
+static Dyn g_dyn;
+
+template <class T>
+static bool sym(void* lib, const char* name, T* out) {
+  *out = reinterpret_cast<T>(dlsym(lib, name));
+  return *out != nullptr;
+}
+
+static int load_dyn() {
+  Dyn& d = g_dyn;
+  std::lock_guard<std::mutex> lock(d.mu);
+  if (d.loaded) return TWG_OK;
+  std::vector<std::string> candidates;
+  if (!d.nvrtc_path.empty()) candidates.push_back(d.nvrtc_path);
+  if (const char* env = getenv("TWG_NVRTC_PATH")) candidates.push_back(env);
+  candidates.push_back("libnvrtc.so.12");
+  candidates.push_back("/usr/local/cuda/lib64/libnvrtc.so.12");
+  candidates.push_back("libnvrtc.so");
+  for (const auto& c : candidates) {
+    d.nvrtc = dlopen(c.c_str(), RTLD_NOW | RTLD_LOCAL);
+    if (d.nvrtc) break;
+  }
+  if (!d.nvrtc) return set_error(TWG_ERR_UNSUPPORTED, "cannot load NVRTC (libnvrtc.so.12): %s", dlerror());
+  d.cuda = dlopen("libcuda.so.1", RTLD_NOW | RTLD_LOCAL);
+  if (!d.cuda) return set_error(TWG_ERR_CUDA, "cannot load the CUDA driver library libcuda.so.1: %s", dlerror());
+  bool ok = sym(d.nvrtc, "nvrtcCreateProgram", &d.CreateProgram) && sym(d.nvrtc, "nvrtcDestroyProgram", &d.DestroyProgram) &&
+            sym(d.nvrtc, "nvrtcCompileProgram", &d.CompileProgram) && sym(d.nvrtc, "nvrtcGetCUBINSize", &d.GetCUBINSize) &&
+            sym(d.nvrtc, "nvrtcGetCUBIN", &d.GetCUBIN) && sym(d.nvrtc, "nvrtcGetProgramLogSize", &d.GetProgramLogSize) &&
+            sym(d.nvrtc, "nvrtcGetProgramLog", &d.GetProgramLog) && sym(d.nvrtc, "nvrtcGetErrorString", &d.GetErrorString) &&
+            sym(d.cuda, "cuModuleLoadData", &d.ModuleLoadData) && sym(d.cuda, "cuModuleUnload", &d.ModuleUnload) &&
+            sym(d.cuda, "cuModuleGetFunction", &d.ModuleGetFunction) && sym(d.cuda, "cuLaunchKernel", &d.LaunchKernel) &&
+            sym(d.cuda, "cuGetErrorString", &d.CuGetErrorString);
+  if (!ok) return set_error(TWG_ERR_UNSUPPORTED, "NVRTC / driver library lacks a required entry point");
+  d.loaded = true;
+  return TWG_OK;
+}
+
+static int cu_fail(CUresult r, const char* what) {
+  const char* msg = nullptr;
+  if (g_dyn.CuGetErrorString) g_dyn.CuGetErrorString(r, &msg);
+  return set_error(TWG_ERR_CUDA, "%s failed: %s (CUresult %d)", what, msg ? msg : "unknown", r);
+}
+
+static int nvrtc_compile(const std::string& source, std::vector<char>* cubin) {
+  if (int rc = load_dyn()) return rc;
+  Dyn& d = g_dyn;
+  nvrtcProgram prog = nullptr;
+  const char* headers[] = {kPointwiseHeader};
+  const char* names[] = {"twg_pointwise.cuh"};
+  nvrtcResult r = d.CreateProgram(&prog, source.c_str(), "twg_fused.cu", 1, headers, names);
+  if (r != 0) return set_error(TWG_ERR_CUDA, "nvrtcCreateProgram failed: %s", d.GetErrorString(r));
+  const char* opts[] = {"--gpu-architecture=sm_100a", "--std=c++17", "-lineinfo"};
+  r = d.CompileProgram(prog, 3, opts);
+  if (r != 0) {
+    size_t n = 0;
+    d.GetProgramLogSize(prog, &n);
+    std::string log(n, '\0');
+    if (n) d.GetProgramLog(prog, &log[0]);
+    d.DestroyProgram(&prog);
+    return set_error(TWG_ERR_CUDA, "NVRTC compilation failed: %s\n%.800s", d.GetErrorString(r), log.c_str());
+  }
+  size_t size = 0;
+  r = d.GetCUBINSize(prog, &size);
+  if (r == 0) {
+    cubin->resize(size);
+    r = d.GetCUBIN(prog, cubin->data());
+  }
+  d.DestroyProgram(&prog);
+  if (r != 0 || size == 0) return set_error(TWG_ERR_CUDA, "NVRTC produced no cubin: %s", d.GetErrorString(r));
+  return TWG_OK;
+}
+
+struct DeviceModule {
+  CUmodule mod = nullptr;
+  CUfunction dense = nullptr, tile = nullptr, strided32 = nullptr, strided64 = nullptr;
+};
+
+}  // namespace twg
+
+using namespace twg;
+
+struct TwgFusedProgram {
+  std::vector<TwgFusedInstr> prog;
+  Analysis an;
+  std::string source;
+  int kind = 0;  // 0 ahead-of-time, 1 NVRTC
+  AotLaunch aot = nullptr;
+  std::vector<char> cubin;
+  std::mutex mu;
+  std::map<int, DeviceModule> modules;  // per device ordinal
+};
+
+namespace twg {
+
+static int get_module(TwgFusedProgram* p, DeviceModule** out) {
+  int dev = 0;
+  TWG_CUDA(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(p->mu);
+  auto it = p->modules.find(dev);
+  if (it == p->modules.end()) {
+    TWG_CUDA(cudaFree(nullptr));  // make sure the primary context exists and is current
+    DeviceModule m;
+    CUresult r = g_dyn.ModuleLoadData(&m.mod, p->cubin.data());
+    if (r != 0) return cu_fail(r, "cuModuleLoadData");
+    struct { const char* name; CUfunction* fn; } want[] = {{"twg_fused_dense", &m.dense}, {"twg_fused_tile", &m.tile},
+                                                           {"twg_fused_strided32", &m.strided32},
+                                                           {"twg_fused_strided64", &m.strided64}};
+    for (auto& w : want) {
+      r = g_dyn.ModuleGetFunction(w.fn, m.mod, w.name);
+      if (r != 0) return cu_fail(r, "cuModuleGetFunction");
+    }
+    it = p->modules.emplace(dev, m).first;
+  }
+  *out = &it->second;
+  return TWG_OK;
+}
+
+template <int NT>
+static int jit_launch(TwgFusedProgram* p, const TwgIterDesc* desc, void* const* ptrs_in, cudaStream_t stream) {
+  PwSig sig{p->an.nin, p->an.nout, p->an.in_byte_mask, p->an.out_byte_mask};
+  PwPlan plan;
+  if (int rc = plan_pointwise(sig, desc, ptrs_in, &plan)) return rc;
+  if (plan.path == kPathNone) return TWG_OK;
+  DeviceModule* m = nullptr;
+  if (int rc = get_module(p, &m)) return rc;
+  PwPtrs<NT> ptrs;
+  for (int t = 0; t < NT; ++t) ptrs.p[t] = ptrs_in[t];
+  i64 n = plan.d.numel, nunits = plan.nunits;
+  CUresult r;
+  CUstream cs = reinterpret_cast<CUstream>(stream);
+  switch (plan.path) {
+    case kPathDense: {
+      void* args[] = {&ptrs, &nunits, &n};
+      r = g_dyn.LaunchKernel(m->dense, plan.grid, 1, 1, kBlock, 1, 1, 0, cs, args, nullptr);
+      break;
+    }
+    case kPathTile: {
+      TileDesc<NT> td;
+      fill_tile_desc<NT>(plan, &td);
+      void* args[] = {&ptrs, &td};
+      r = g_dyn.LaunchKernel(m->tile, plan.grid, 1, 1, kTile, kTileRows, 1, 0, cs, args, nullptr);
+      break;
+    }
+    case kPathStrided32: {
+      StridedDesc<NT, u32> sd;
+      fill_strided_desc<NT>(plan.d, &sd);
+      void* args[] = {&ptrs, &sd, &n};
+      r = g_dyn.LaunchKernel(m->strided32, plan.grid, 1, 1, kBlock, 1, 1, 0, cs, args, nullptr);
+      break;
+    }
+    default: {
+      StridedDesc<NT, u64> sd;
+      fill_strided_desc<NT>(plan.d, &sd);
+      void* args[] = {&ptrs, &sd, &n};
+      r = g_dyn.LaunchKernel(m->strided64, plan.grid, 1, 1, kBlock, 1, 1, 0, cs, args, nullptr);
+      break;
+    }
+  }
+  if (r != 0) return cu_fail(r, "cuLaunchKernel");
+  count_launch();
+  g_last_path = plan.path;
+  return TWG_OK;
+}
+
+// cache of compiled programs, keyed by generated source
+static std::mutex g_cache_mu;
+static std::map<std::string, TwgFusedProgram*> g_cache;
+
+}  // namespace twg
+
+extern "C" int twg_fused_set_nvrtc_path(const char* path) {
+  std::lock_guard<std::mutex> lock(g_dyn.mu);
+  g_dyn.nvrtc_path = path ? path : "";
+  return TWG_OK;
+}
+
+extern "C" int twg_fused_compile(const TwgFusedInstr* prog, int ninstr, TwgFusedProgram** out) {
+  TWG_REQUIRE(out != nullptr, "twg_fused_compile: null result pointer");
+  *out = nullptr;
+  Analysis an;
+  if (int rc = analyse(prog, ninstr, &an)) return rc;
+  std::string source = generate_source(prog, ninstr, an);
+  std::lock_guard<std::mutex> lock(g_cache_mu);
+  auto it = g_cache.find(source);
+  if (it != g_cache.end()) {
+    *out = it->second;
+    return TWG_OK;
+  }
+  TwgFusedProgram* p = new TwgFusedProgram();
+  p->prog.assign(prog, prog + ninstr);
+  p->an = an;
+  p->source = source;
+  for (const AotEntry& e : kAot)
+    if (same_program(prog, ninstr, e.prog, e.n)) { p->aot = e.launch; break; }
+  if (p->aot) {
+    p->kind = 0;
+  } else {
+    p->kind = 1;
+    if (int rc = nvrtc_compile(source, &p->cubin)) {
+      delete p;
+      return rc;
+    }
+  }
+  g_cache[source] = p;
+  *out = p;
+  return TWG_OK;
+}
+
+extern "C" int twg_fused_kind(const TwgFusedProgram* p, int* kind) {
+  TWG_REQUIRE(p && kind, "twg_fused_kind: null argument");
+  *kind = p->kind;
+  return TWG_OK;
+}
+
+extern "C" int twg_fused_source(const TwgFusedProgram* p, const char** source) {
+  TWG_REQUIRE(p && source, "twg_fused_source: null argument");
+  *source = p->source.c_str();
+  return TWG_OK;
+}
+
+extern "C" int twg_fused_launch(const TwgFusedProgram* cp, const TwgIterDesc* desc, void* const* ptrs, void* stream) {
+  TWG_REQUIRE(cp && ptrs, "twg_fused_launch: null argument");
+  TwgFusedProgram* p = const_cast<TwgFusedProgram*>(cp);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (p->aot) return p->aot(desc, ptrs, s);
+  switch (p->an.nin + p->an.nout) {
+    case 1: return jit_launch<1>(p, desc, ptrs, s);
+    case 2: return jit_launch<2>(p, desc, ptrs, s);
+    case 3: return jit_launch<3>(p, desc, ptrs, s);
+    case 4: return jit_launch<4>(p, desc, ptrs, s);
+    case 5: return jit_launch<5>(p, desc, ptrs, s);
+    case 6: return jit_launch<6>(p, desc, ptrs, s);
+    case 7: return jit_launch<7>(p, desc, ptrs, s);
+    case 8: return jit_launch<8>(p, desc, ptrs, s);
+    default: return set_error(TWG_ERR_INVALID, "twg_fused_launch: bad operand count");
+  }
+}
+
+// Programs are owned by the cache and shared between callers; release is a no-op kept for
+// symmetry with compile so that callers can treat handles as owned.
+extern "C" int twg_fused_release(TwgFusedProgram* p) {
+  (void)p;
+  return TWG_OK;
+}

@@ -1,0 +1,46 @@
+// Host-side helpers shared by the translation units of the library: error reporting,
+// launch accounting, descriptor lowering and the generic pointwise launcher.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "twg.h"
+
+namespace twg {
+
+// Store a formatted message for twg_last_error() on this thread and return `code`.
+int set_error(int code, const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what, const char* file, int line);
+void count_launch(int n = 1);
+// Properties of the current device (cached per ordinal).
+int sm_count();
+
+#define TWG_CUDA(expr)                                                          \
+  do {                                                                          \
+    cudaError_t twg_e_ = (expr);                                                \
+    if (twg_e_ != cudaSuccess) return ::twg::cuda_fail(twg_e_, #expr, __FILE__, __LINE__); \
+  } while (0)
+
+#define TWG_CHECK_LAUNCH()                                                      \
+  do {                                                                          \
+    cudaError_t twg_e_ = cudaGetLastError();                                    \
+    if (twg_e_ != cudaSuccess) return ::twg::cuda_fail(twg_e_, "kernel launch", __FILE__, __LINE__); \
+    ::twg::count_launch();                                                      \
+  } while (0)
+
+#define TWG_REQUIRE(cond, ...)                                                  \
+  do {                                                                          \
+    if (!(cond)) return ::twg::set_error(TWG_ERR_INVALID, __VA_ARGS__);         \
+  } while (0)
+
+// Validate a descriptor for `ntensors` operands.
+int check_desc(const TwgIterDesc* d, int ntensors);
+// Largest element offset operand t can reach (strides are non-negative in TensorIterator order
+// except for flipped views, which take the 64-bit path through the absolute value).
+int64_t max_offset(const TwgIterDesc& d, int t);
+// Host-side multiply-shift divisor for u32 numerators below 2^31.
+void make_fastdiv(uint32_t d, uint32_t* m, uint32_t* s);
+
+}  // namespace twg

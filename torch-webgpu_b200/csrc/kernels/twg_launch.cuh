@@ -1,0 +1,117 @@
+// Host-side launcher for the pointwise functor kernels: lowers a TwgIterDesc to one of the three
+// launch shapes of twg_pointwise.cuh and enqueues it.  The planning step works on a run-time
+// operand signature so that kernels instantiated ahead of time and kernels compiled by NVRTC
+// take exactly the same decisions.
+#pragma once
+
+#include <algorithm>
+#include <cstdlib>
+
+#include "twg_internal.h"
+#include "twg_pointwise.cuh"
+
+namespace twg {
+
+// Shape chosen for a launch; twg_last_launch_path() reports it so tests can assert which kernel
+// served a layout.
+enum PwPath { kPathNone = 0, kPathDense = 1, kPathTile = 2, kPathStrided32 = 3, kPathStrided64 = 4 };
+extern thread_local int g_last_path;
+
+constexpr int kDenseUnroll = 4;    // 128-bit requests in flight per input per thread
+constexpr int kStridedUnroll = 4;
+
+inline bool is_aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// Operand signature of a pointwise kernel: outputs first, then inputs; bit set = 1-byte operand.
+struct PwSig {
+  int nin, nout;
+  unsigned in_byte_mask, out_byte_mask;
+  int nt() const { return nin + nout; }
+  bool byte(int t) const { return t < nout ? (out_byte_mask >> t) & 1u : (in_byte_mask >> (t - nout)) & 1u; }
+  int vec() const {
+    return (in_byte_mask == ((1u << nin) - 1u) && out_byte_mask == ((1u << nout) - 1u)) ? 16 : 4;
+  }
+};
+template <class F>
+PwSig sig_of() { return PwSig{F::NIN, F::NOUT, F::kInByteMask, F::kOutByteMask}; }
+
+struct PwPlan {
+  int path = kPathNone;
+  TwgIterDesc d;         // coalesced
+  int64_t nunits = 0;    // dense path
+  uint32_t dim1_mask = 0;
+  int64_t tiles0 = 0, ntiles = 0;
+  unsigned grid = 1;
+};
+
+// Decide the launch shape.  Returns TWG_OK with plan->path == kPathNone for an empty iteration.
+int plan_pointwise(const PwSig& sig, const TwgIterDesc* desc, void* const* ptrs, PwPlan* plan);
+// Shared by the element-size-generic kernels in copy.cu.
+bool plan_tile(const TwgIterDesc& d, int nt, PwPlan* plan);
+bool fits_32bit(const TwgIterDesc& d, int nt);
+
+template <int NT>
+void fill_tile_desc(const PwPlan& p, TileDesc<NT>* td) {
+  td->shape0 = p.d.shape[0];
+  td->shape1 = p.d.shape[1];
+  td->tiles0 = p.tiles0;
+  td->ntiles = p.ntiles;
+  for (int t = 0; t < NT; ++t) { td->s0[t] = p.d.strides[t][0]; td->s1[t] = p.d.strides[t][1]; }
+  td->dim1_mask = p.dim1_mask;
+}
+template <int NT>
+void fill_strided_desc(const TwgIterDesc& d, StridedDesc<NT, u32>* sd) {
+  sd->ndim = d.ndim;
+  for (int k = 0; k < kMaxDims; ++k) {
+    const uint32_t s = k < d.ndim ? (uint32_t)d.shape[k] : 1u;
+    sd->shape[k].d = s;
+    make_fastdiv(s, &sd->shape[k].m, &sd->shape[k].s);
+    for (int t = 0; t < NT; ++t) sd->strides[t][k] = k < d.ndim ? (uint32_t)d.strides[t][k] : 0u;
+  }
+}
+template <int NT>
+void fill_strided_desc(const TwgIterDesc& d, StridedDesc<NT, u64>* sd) {
+  sd->ndim = d.ndim;
+  for (int k = 0; k < kMaxDims; ++k) {
+    sd->shape[k] = k < d.ndim ? (u64)d.shape[k] : 1ull;
+    for (int t = 0; t < NT; ++t) sd->strides[t][k] = k < d.ndim ? d.strides[t][k] : 0;
+  }
+}
+
+template <class F>
+int launch_pointwise(const F& f, const TwgIterDesc* desc, void* const* ptrs_in, cudaStream_t stream) {
+  constexpr int NT = PwTraits<F>::NT;
+  PwPlan plan;
+  if (int rc = plan_pointwise(sig_of<F>(), desc, ptrs_in, &plan)) return rc;
+  if (plan.path == kPathNone) return TWG_OK;
+  PwPtrs<NT> ptrs;
+  for (int t = 0; t < NT; ++t) ptrs.p[t] = ptrs_in[t];
+  switch (plan.path) {
+    case kPathDense:
+      pw_contig_kernel<F, kDenseUnroll><<<plan.grid, kBlock, 0, stream>>>(ptrs, f, plan.nunits, plan.d.numel);
+      break;
+    case kPathTile: {
+      TileDesc<NT> td;
+      fill_tile_desc<NT>(plan, &td);
+      pw_tile_kernel<F><<<plan.grid, dim3(kTile, kTileRows), 0, stream>>>(ptrs, f, td);
+      break;
+    }
+    case kPathStrided32: {
+      StridedDesc<NT, u32> sd;
+      fill_strided_desc<NT>(plan.d, &sd);
+      pw_strided_kernel<F, kStridedUnroll, u32><<<plan.grid, kBlock, 0, stream>>>(ptrs, f, sd, plan.d.numel);
+      break;
+    }
+    default: {
+      StridedDesc<NT, u64> sd;
+      fill_strided_desc<NT>(plan.d, &sd);
+      pw_strided_kernel<F, kStridedUnroll, u64><<<plan.grid, kBlock, 0, stream>>>(ptrs, f, sd, plan.d.numel);
+      break;
+    }
+  }
+  TWG_CHECK_LAUNCH();
+  g_last_path = plan.path;
+  return TWG_OK;
+}
+
+}  // namespace twg

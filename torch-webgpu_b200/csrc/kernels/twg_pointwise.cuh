@@ -1,0 +1,468 @@
+// Device-side building blocks of every pointwise kernel in the library: the element functions,
+// the three launch shapes (dense 128-bit vector path, 2-D permuted tile path, generic
+// strided/broadcast index-math path) and the functor protocol that binds them.
+//
+// The same header is compiled ahead of time by nvcc into the library and, as text, by NVRTC for
+// fused programs built at torch.compile time, so it must not include any host header.
+//
+// Functor protocol (type F):
+//   static constexpr int NIN, NOUT            number of inputs / outputs
+//   static constexpr unsigned kInByteMask     bit k set: input k is 1-byte (bool/u8), else f32
+//   static constexpr unsigned kOutByteMask    same for outputs
+//   __device__ void operator()(const u32* in, u32* out) const
+// Values travel in 32-bit registers: f32 as its bit pattern, bool as 0/1.
+#pragma once
+
+namespace twg {
+
+typedef unsigned int u32;
+typedef unsigned char u8;
+typedef long long i64;
+typedef unsigned long long u64;
+
+constexpr int kMaxDims = 8;
+constexpr int kBlock = 256;  // threads per CTA of the dense and strided kernels
+
+// ------------------------------------------------------------------------------------------
+// Element functions.  They restate PyTorch's CPU kernels, which is what the reference's tests
+// assert against and what its CPU-fallback ops execute; explicit _rn intrinsics keep the
+// compiler from contracting or reassociating anything.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ float f_add(float a, float b, float alpha) { return __fmaf_rn(alpha, b, a); }
+__device__ __forceinline__ float f_mul(float a, float b) { return __fmul_rn(a, b); }
+// max(0,x) that keeps NaN and -0.0 (clamp_min semantics of the CPU kernel).
+__device__ __forceinline__ float f_relu(float x) { return (x < 0.0f) ? 0.0f : x; }
+__device__ __forceinline__ float f_abs(float x) { return fabsf(x); }
+__device__ __forceinline__ float f_silu(float x) {
+  return __fdiv_rn(x, __fadd_rn(1.0f, expf(-x)));
+}
+__device__ __forceinline__ float f_gelu_erf(float x) {
+  // x * 0.5 * (1 + erf(x / sqrt(2)))
+  const float kAlpha = 0.70710678118654752440f;
+  return __fmul_rn(__fmul_rn(x, 0.5f), __fadd_rn(1.0f, erff(__fmul_rn(x, kAlpha))));
+}
+__device__ __forceinline__ float f_gelu_tanh(float x) {
+  // 0.5 * x * (1 + tanh(sqrt(2/pi) * (x + 0.044715 x^3)))
+  const float kBeta = 0.79788456080286535588f;  // sqrt(2) * (2/sqrt(pi)) * 0.5
+  const float kKappa = 0.044715f;
+  float x3 = __fmul_rn(__fmul_rn(x, x), x);
+  float inner = __fmul_rn(kBeta, __fadd_rn(x, __fmul_rn(kKappa, x3)));
+  return __fmul_rn(__fmul_rn(0.5f, x), __fadd_rn(1.0f, tanhf(inner)));
+}
+__device__ __forceinline__ u32 f_eq(float a, float b) { return a == b ? 1u : 0u; }
+__device__ __forceinline__ u32 f_ne(float a, float b) { return a != b ? 1u : 0u; }
+__device__ __forceinline__ u32 f_lt(float a, float b) { return a < b ? 1u : 0u; }
+__device__ __forceinline__ u32 f_le(float a, float b) { return a <= b ? 1u : 0u; }
+__device__ __forceinline__ u32 f_gt(float a, float b) { return a > b ? 1u : 0u; }
+__device__ __forceinline__ u32 f_ge(float a, float b) { return a >= b ? 1u : 0u; }
+__device__ __forceinline__ u32 f_and(u32 a, u32 b) { return a & b; }
+
+__device__ __forceinline__ float as_f(u32 v) { return __uint_as_float(v); }
+__device__ __forceinline__ u32 as_u(float v) { return __float_as_uint(v); }
+
+// ------------------------------------------------------------------------------------------
+// Memory access helpers.  Streaming hints: every byte is touched once, so loads do not
+// allocate in L1 and stores are marked evict-first.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 ld_v4(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
+}
+__device__ __forceinline__ u32 ld_b32(const void* p) {
+  u32 r;
+  asm volatile("ld.global.L1::no_allocate.u32 %0, [%1];" : "=r"(r) : "l"(p));
+  return r;
+}
+__device__ __forceinline__ u32 ld_b8(const void* p) {
+  u32 r;
+  asm volatile("ld.global.L1::no_allocate.u8 %0, [%1];" : "=r"(r) : "l"(p));
+  return r;
+}
+__device__ __forceinline__ void st_v4(void* p, uint4 v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ void st_b32(void* p, u32 v) {
+  asm volatile("st.global.cs.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_b8(void* p, u32 v) {
+  asm volatile("st.global.cs.u8 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// One "unit" is VEC consecutive elements: 4 when any operand is f32 (float4 / uchar4 accesses),
+// 16 when every operand is a byte type (uint4 accesses).
+template <int VEC, bool BYTE>
+__device__ __forceinline__ void load_unit(const void* base, i64 unit, u32 (&r)[VEC]) {
+  if constexpr (!BYTE) {
+    static_assert(VEC == 4, "f32 units are 4 wide");
+    uint4 v = ld_v4(reinterpret_cast<const uint4*>(base) + unit);
+    r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
+  } else if constexpr (VEC == 4) {
+    u32 w = ld_b32(reinterpret_cast<const u32*>(base) + unit);
+    w = __vcmpne4(w, 0u) & 0x01010101u;  // any non-zero byte counts as true
+    r[0] = w & 0xffu; r[1] = (w >> 8) & 0xffu; r[2] = (w >> 16) & 0xffu; r[3] = w >> 24;
+  } else {
+    static_assert(VEC == 16, "byte units are 4 or 16 wide");
+    uint4 v = ld_v4(reinterpret_cast<const uint4*>(base) + unit);
+    u32 w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      r[4 * i + 0] = w[i] & 0xffu; r[4 * i + 1] = (w[i] >> 8) & 0xffu;
+      r[4 * i + 2] = (w[i] >> 16) & 0xffu; r[4 * i + 3] = w[i] >> 24;
+    }
+  }
+}
+template <int VEC, bool BYTE>
+__device__ __forceinline__ void store_unit(void* base, i64 unit, const u32 (&r)[VEC]) {
+  if constexpr (!BYTE) {
+    st_v4(reinterpret_cast<uint4*>(base) + unit, make_uint4(r[0], r[1], r[2], r[3]));
+  } else if constexpr (VEC == 4) {
+    st_b32(reinterpret_cast<u32*>(base) + unit, r[0] | (r[1] << 8) | (r[2] << 16) | (r[3] << 24));
+  } else {
+    uint4 v;
+    v.x = r[0] | (r[1] << 8) | (r[2] << 16) | (r[3] << 24);
+    v.y = r[4] | (r[5] << 8) | (r[6] << 16) | (r[7] << 24);
+    v.z = r[8] | (r[9] << 8) | (r[10] << 16) | (r[11] << 24);
+    v.w = r[12] | (r[13] << 8) | (r[14] << 16) | (r[15] << 24);
+    st_v4(reinterpret_cast<uint4*>(base) + unit, v);
+  }
+}
+template <bool BYTE>
+__device__ __forceinline__ u32 load_elem(const void* base, i64 idx) {
+  if constexpr (BYTE) return ld_b8(reinterpret_cast<const u8*>(base) + idx);
+  else return ld_b32(reinterpret_cast<const u32*>(base) + idx);
+}
+template <bool BYTE>
+__device__ __forceinline__ void store_elem(void* base, i64 idx, u32 v) {
+  if constexpr (BYTE) st_b8(reinterpret_cast<u8*>(base) + idx, v);
+  else st_b32(reinterpret_cast<u32*>(base) + idx, v);
+}
+
+template <int NT>
+struct PwPtrs {
+  void* p[NT];  // outputs first, then inputs
+};
+
+template <class F>
+struct PwTraits {
+  static constexpr int NIN = F::NIN, NOUT = F::NOUT, NT = F::NIN + F::NOUT;
+  static constexpr bool in_byte(int k) { return (F::kInByteMask >> k) & 1u; }
+  static constexpr bool out_byte(int k) { return (F::kOutByteMask >> k) & 1u; }
+  static constexpr bool all_bytes() {
+    return F::kInByteMask == ((1u << F::NIN) - 1u) && F::kOutByteMask == ((1u << F::NOUT) - 1u);
+  }
+  static constexpr int VEC = all_bytes() ? 16 : 4;
+};
+
+// compile-time loops over operands (operand type is a template argument of load/store)
+template <class F, int VEC, int K = 0>
+__device__ __forceinline__ void load_inputs_unit(const PwPtrs<PwTraits<F>::NT>& ptrs, i64 unit,
+                                                 u32 (&v)[F::NIN][VEC]) {
+  if constexpr (K < F::NIN) {
+    load_unit<VEC, PwTraits<F>::in_byte(K)>(ptrs.p[F::NOUT + K], unit, v[K]);
+    load_inputs_unit<F, VEC, K + 1>(ptrs, unit, v);
+  }
+}
+template <class F, int VEC, int K = 0>
+__device__ __forceinline__ void store_outputs_unit(const PwPtrs<PwTraits<F>::NT>& ptrs, i64 unit,
+                                                   const u32 (&v)[F::NOUT][VEC]) {
+  if constexpr (K < F::NOUT) {
+    store_unit<VEC, PwTraits<F>::out_byte(K)>(ptrs.p[K], unit, v[K]);
+    store_outputs_unit<F, VEC, K + 1>(ptrs, unit, v);
+  }
+}
+template <class F, int K = 0>
+__device__ __forceinline__ void load_inputs_elem(const PwPtrs<PwTraits<F>::NT>& ptrs, const i64* off,
+                                                 u32* v) {
+  if constexpr (K < F::NIN) {
+    u32 x = load_elem<PwTraits<F>::in_byte(K)>(ptrs.p[F::NOUT + K], off[F::NOUT + K]);
+    if constexpr (PwTraits<F>::in_byte(K)) x = (x != 0u) ? 1u : 0u;
+    v[K] = x;
+    load_inputs_elem<F, K + 1>(ptrs, off, v);
+  }
+}
+template <class F, int K = 0>
+__device__ __forceinline__ void store_outputs_elem(const PwPtrs<PwTraits<F>::NT>& ptrs, const i64* off,
+                                                   const u32* v) {
+  if constexpr (K < F::NOUT) {
+    store_elem<PwTraits<F>::out_byte(K)>(ptrs.p[K], off[K], v[K]);
+    store_outputs_elem<F, K + 1>(ptrs, off, v);
+  }
+}
+
+template <class F, int VEC>
+__device__ __forceinline__ void apply_unit(const F& f, const u32 (&vin)[F::NIN][VEC], u32 (&vout)[F::NOUT][VEC]) {
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) {
+    u32 in[F::NIN > 0 ? F::NIN : 1], out[F::NOUT];
+#pragma unroll
+    for (int k = 0; k < F::NIN; ++k) in[k] = vin[k][e];
+    f(in, out);
+#pragma unroll
+    for (int k = 0; k < F::NOUT; ++k) vout[k][e] = out[k];
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Dense path.  All operands are contiguous and aligned to their unit size.  Each CTA walks
+// chunks of kBlock*U units; inside a chunk a thread owns units threadIdx.x + u*kBlock, so every
+// warp-wide access is one contiguous 512-byte (f32) or 128-byte (bool) run.  All loads of a
+// chunk are issued before the first use to keep U*NIN 128-bit requests in flight per thread.
+// `n` is the element count; the < VEC leftover elements are handled by CTA 0.
+// ------------------------------------------------------------------------------------------
+template <class F, int U>
+__device__ __forceinline__ void pw_contig_body(const PwPtrs<PwTraits<F>::NT>& ptrs, const F& f, i64 nunits, i64 n) {
+  constexpr int VEC = PwTraits<F>::VEC;
+  const i64 chunk_units = (i64)kBlock * U;
+  const i64 nchunks = (nunits + chunk_units - 1) / chunk_units;
+  for (i64 c = blockIdx.x; c < nchunks; c += gridDim.x) {
+    const i64 u0 = c * chunk_units + threadIdx.x;
+    u32 vin[U][F::NIN > 0 ? F::NIN : 1][VEC];
+    u32 vout[U][F::NOUT][VEC];
+    if (u0 + (i64)(U - 1) * kBlock < nunits) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) load_inputs_unit<F, VEC>(ptrs, u0 + (i64)u * kBlock, vin[u]);
+#pragma unroll
+      for (int u = 0; u < U; ++u) apply_unit<F, VEC>(f, vin[u], vout[u]);
+#pragma unroll
+      for (int u = 0; u < U; ++u) store_outputs_unit<F, VEC>(ptrs, u0 + (i64)u * kBlock, vout[u]);
+    } else {
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (u0 + (i64)u * kBlock < nunits) load_inputs_unit<F, VEC>(ptrs, u0 + (i64)u * kBlock, vin[u]);
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (u0 + (i64)u * kBlock < nunits) {
+          apply_unit<F, VEC>(f, vin[u], vout[u]);
+          store_outputs_unit<F, VEC>(ptrs, u0 + (i64)u * kBlock, vout[u]);
+        }
+    }
+  }
+  const i64 tail0 = nunits * VEC;
+  if (blockIdx.x == 0 && tail0 + threadIdx.x < n) {
+    i64 off[PwTraits<F>::NT];
+#pragma unroll
+    for (int t = 0; t < PwTraits<F>::NT; ++t) off[t] = tail0 + threadIdx.x;
+    u32 in[F::NIN > 0 ? F::NIN : 1], out[F::NOUT];
+    load_inputs_elem<F>(ptrs, off, in);
+    f(in, out);
+    store_outputs_elem<F>(ptrs, off, out);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Generic path: up to 8 dimensions, any strides including 0 (broadcast).  Consecutive threads
+// take consecutive linear indices, i.e. they walk dimension 0 (the fastest one), so accesses
+// coalesce whenever an operand's dimension-0 stride is 1.  IDX is u32 when the element count
+// and every operand's largest offset stay below 2^31 (division by multiply-shift), else u64.
+// ------------------------------------------------------------------------------------------
+struct FastDiv32 {
+  u32 d, m, s;
+  __device__ __forceinline__ u32 div(u32 n) const { return (__umulhi(n, m) + n) >> s; }  // n < 2^31
+};
+
+template <int NT, class IDX>
+struct StridedDesc;
+template <int NT>
+struct StridedDesc<NT, u32> {
+  int ndim;
+  FastDiv32 shape[kMaxDims];
+  u32 strides[NT][kMaxDims];
+};
+template <int NT>
+struct StridedDesc<NT, u64> {
+  int ndim;
+  u64 shape[kMaxDims];
+  i64 strides[NT][kMaxDims];
+};
+
+template <int NT>
+__device__ __forceinline__ void linear_to_offsets(const StridedDesc<NT, u32>& d, u32 lin, i64* off) {
+  u32 o[NT];
+#pragma unroll
+  for (int t = 0; t < NT; ++t) o[t] = 0;
+#pragma unroll
+  for (int k = 0; k < kMaxDims; ++k) {
+    if (k >= d.ndim) break;
+    u32 q = d.shape[k].div(lin);
+    u32 c = lin - q * d.shape[k].d;
+    lin = q;
+#pragma unroll
+    for (int t = 0; t < NT; ++t) o[t] += c * d.strides[t][k];
+  }
+#pragma unroll
+  for (int t = 0; t < NT; ++t) off[t] = (i64)o[t];
+}
+template <int NT>
+__device__ __forceinline__ void linear_to_offsets(const StridedDesc<NT, u64>& d, u64 lin, i64* off) {
+#pragma unroll
+  for (int t = 0; t < NT; ++t) off[t] = 0;
+#pragma unroll
+  for (int k = 0; k < kMaxDims; ++k) {
+    if (k >= d.ndim) break;
+    u64 q = lin / d.shape[k];
+    i64 c = (i64)(lin - q * d.shape[k]);
+    lin = q;
+#pragma unroll
+    for (int t = 0; t < NT; ++t) off[t] += c * d.strides[t][k];
+  }
+}
+
+template <class F, int U, class IDX>
+__device__ __forceinline__ void pw_strided_body(const PwPtrs<PwTraits<F>::NT>& ptrs, const F& f,
+                                                const StridedDesc<PwTraits<F>::NT, IDX>& d, i64 n) {
+  constexpr int NT = PwTraits<F>::NT;
+  const i64 step = (i64)gridDim.x * kBlock * U;
+  for (i64 base = (i64)blockIdx.x * kBlock * U + threadIdx.x; base < n; base += step) {
+    i64 off[U][NT];
+    u32 in[U][F::NIN > 0 ? F::NIN : 1], out[U][F::NOUT];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const i64 e = base + (i64)u * kBlock;
+      if (e < n) {
+        linear_to_offsets<NT>(d, (IDX)e, off[u]);
+        load_inputs_elem<F>(ptrs, off[u], in[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const i64 e = base + (i64)u * kBlock;
+      if (e < n) {
+        f(in[u], out[u]);
+        store_outputs_elem<F>(ptrs, off[u], out[u]);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// 2-D permuted path (a true transpose: some operands are dense along dimension 0, the others
+// along dimension 1).  A CTA of 32x8 threads owns a 32x32 tile.  Operands dense along dimension
+// 1 are moved through a padded shared-memory tile so that both their global accesses and
+// everyone else's are 128-byte runs.  bit t of `dim1_mask` set: operand t is dense along dim 1.
+// ------------------------------------------------------------------------------------------
+constexpr int kTile = 32;
+constexpr int kTileRows = 8;
+
+template <int NT>
+struct TileDesc {
+  i64 shape0, shape1;
+  i64 tiles0;  // ceil(shape0 / kTile)
+  i64 ntiles;
+  i64 s0[NT], s1[NT];
+  u32 dim1_mask;
+};
+
+template <class F, int K = 0>
+__device__ __forceinline__ void tile_load_inputs(const PwPtrs<PwTraits<F>::NT>& ptrs, const TileDesc<PwTraits<F>::NT>& d,
+                                                 i64 t0, i64 t1, u32 (*smem)[kTile][kTile + 1],
+                                                 u32 (&v)[kTile / kTileRows][F::NIN > 0 ? F::NIN : 1]) {
+  if constexpr (K < F::NIN) {
+    constexpr int T = F::NOUT + K;
+    constexpr bool BYTE = PwTraits<F>::in_byte(K);
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    if ((d.dim1_mask >> T) & 1u) {
+      // read with tx along dimension 1, park as smem[i0][i1]
+#pragma unroll
+      for (int r = 0; r < kTile / kTileRows; ++r) {
+        const i64 i0 = t0 + ty + r * kTileRows, i1 = t1 + tx;
+        u32 x = 0;
+        if (i0 < d.shape0 && i1 < d.shape1) x = load_elem<BYTE>(ptrs.p[T], i0 * d.s0[T] + i1 * d.s1[T]);
+        smem[K][ty + r * kTileRows][tx] = x;
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < kTile / kTileRows; ++r) {
+        const i64 i0 = t0 + tx, i1 = t1 + ty + r * kTileRows;
+        u32 x = 0;
+        if (i0 < d.shape0 && i1 < d.shape1) x = load_elem<BYTE>(ptrs.p[T], i0 * d.s0[T] + i1 * d.s1[T]);
+        v[r][K] = x;
+      }
+    }
+    tile_load_inputs<F, K + 1>(ptrs, d, t0, t1, smem, v);
+  }
+}
+template <class F, int K = 0>
+__device__ __forceinline__ void tile_gather_inputs(const TileDesc<PwTraits<F>::NT>& d, u32 (*smem)[kTile][kTile + 1],
+                                                   u32 (&v)[kTile / kTileRows][F::NIN > 0 ? F::NIN : 1]) {
+  if constexpr (K < F::NIN) {
+    constexpr int T = F::NOUT + K;
+    if ((d.dim1_mask >> T) & 1u) {
+#pragma unroll
+      for (int r = 0; r < kTile / kTileRows; ++r) v[r][K] = smem[K][threadIdx.x][threadIdx.y + r * kTileRows];
+    }
+    if constexpr (PwTraits<F>::in_byte(K)) {
+#pragma unroll
+      for (int r = 0; r < kTile / kTileRows; ++r) v[r][K] = v[r][K] != 0u ? 1u : 0u;
+    }
+    tile_gather_inputs<F, K + 1>(d, smem, v);
+  }
+}
+template <class F, int K = 0>
+__device__ __forceinline__ void tile_store_outputs(const PwPtrs<PwTraits<F>::NT>& ptrs, const TileDesc<PwTraits<F>::NT>& d,
+                                                   i64 t0, i64 t1, u32 (*smem)[kTile][kTile + 1],
+                                                   const u32 (&v)[kTile / kTileRows][F::NOUT]) {
+  if constexpr (K < F::NOUT) {
+    constexpr bool BYTE = PwTraits<F>::out_byte(K);
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    if ((d.dim1_mask >> K) & 1u) {
+      __syncthreads();  // previous use of smem[0] is finished
+#pragma unroll
+      for (int r = 0; r < kTile / kTileRows; ++r) smem[0][tx][ty + r * kTileRows] = v[r][K];
+      __syncthreads();
+#pragma unroll
+      for (int r = 0; r < kTile / kTileRows; ++r) {
+        const i64 i0 = t0 + ty + r * kTileRows, i1 = t1 + tx;
+        if (i0 < d.shape0 && i1 < d.shape1)
+          store_elem<BYTE>(ptrs.p[K], i0 * d.s0[K] + i1 * d.s1[K], smem[0][ty + r * kTileRows][tx]);
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < kTile / kTileRows; ++r) {
+        const i64 i0 = t0 + tx, i1 = t1 + ty + r * kTileRows;
+        if (i0 < d.shape0 && i1 < d.shape1) store_elem<BYTE>(ptrs.p[K], i0 * d.s0[K] + i1 * d.s1[K], v[r][K]);
+      }
+    }
+    tile_store_outputs<F, K + 1>(ptrs, d, t0, t1, smem, v);
+  }
+}
+
+template <class F>
+__device__ __forceinline__ void pw_tile_body(const PwPtrs<PwTraits<F>::NT>& ptrs, const F& f,
+                                             const TileDesc<PwTraits<F>::NT>& d) {
+  constexpr int R = kTile / kTileRows;
+  constexpr int NS = F::NIN > 0 ? F::NIN : 1;
+  __shared__ u32 smem[NS][kTile][kTile + 1];
+  for (i64 tile = blockIdx.x; tile < d.ntiles; tile += gridDim.x) {
+    const i64 t0 = (tile % d.tiles0) * kTile, t1 = (tile / d.tiles0) * kTile;
+    u32 vin[R][NS], vout[R][F::NOUT];
+    __syncthreads();  // smem free again (previous tile)
+    tile_load_inputs<F>(ptrs, d, t0, t1, smem, vin);
+    __syncthreads();
+    tile_gather_inputs<F>(d, smem, vin);
+#pragma unroll
+    for (int r = 0; r < R; ++r) f(vin[r], vout[r]);
+    tile_store_outputs<F>(ptrs, d, t0, t1, smem, vout);
+  }
+}
+
+// __global__ wrappers (templates for ahead-of-time instantiation)
+template <class F, int U>
+__global__ void __launch_bounds__(kBlock) pw_contig_kernel(PwPtrs<PwTraits<F>::NT> ptrs, F f, i64 nunits, i64 n) {
+  pw_contig_body<F, U>(ptrs, f, nunits, n);
+}
+template <class F, int U, class IDX>
+__global__ void __launch_bounds__(kBlock)
+    pw_strided_kernel(PwPtrs<PwTraits<F>::NT> ptrs, F f, StridedDesc<PwTraits<F>::NT, IDX> d, i64 n) {
+  pw_strided_body<F, U, IDX>(ptrs, f, d, n);
+}
+template <class F>
+__global__ void __launch_bounds__(kTile* kTileRows)
+    pw_tile_kernel(PwPtrs<PwTraits<F>::NT> ptrs, F f, TileDesc<PwTraits<F>::NT> d) {
+  pw_tile_body<F>(ptrs, f, d);
+}
+
+}  // namespace twg
