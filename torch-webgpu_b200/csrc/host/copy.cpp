@@ -1,0 +1,145 @@
+// copy_ / _copy_from / _copy_from_and_resize / to.device (the reference's csrc/ops/copy.cpp:69-189).
+//
+// Host->device and device->host transfers are cudaMemcpyAsync on the tensor's stream through the
+// library (pinned memory directly, pageable memory through a pinned staging ring); device->device
+// is a dense async copy or the strided copy kernel.  Differences from the reference, on purpose:
+// every dtype can be moved (it asserts Float on read-back, copy.cpp:22), storage offsets are
+// honoured in both directions (copy.cpp:42 ignores the source offset), non-contiguous device
+// tensors can be the destination of an upload, and the aten CPU `copy_` kernel is left alone -
+// the dispatcher already routes a mixed CPU/webgpu copy_ to the PrivateUse1 kernel.
+#include <ATen/NativeFunctions.h>
+#include <torch/library.h>
+
+#include "twg_host.h"
+
+namespace torch_webgpu {
+namespace ops {
+
+static c10::DeviceIndex dev_of(const at::Tensor& t) {
+  return t.device().index() < 0 ? core::current_device() : t.device().index();
+}
+
+static void device_strided_copy(at::Tensor& dst, const at::Tensor& src) {
+  at::TensorIteratorConfig config;
+  config.set_check_mem_overlap(true);
+  config.add_output(dst);
+  config.add_const_input(src);
+  config.check_all_same_dtype(true);
+  config.check_all_same_device(true);
+  auto iter = config.build();
+  if (iter.numel() == 0) return;
+  const c10::DeviceIndex dev = dev_of(dst);
+  core::DeviceScope scope(dev);
+  TwgIterDesc desc = desc_from_iter(iter);
+  TWG_TORCH_CHECK(twg_copy_strided(&desc, static_cast<int>(dst.dtype().itemsize()), iter.data_ptr(1), iter.data_ptr(0),
+                                   core::current_stream(dev)));
+}
+
+static void host_to_device(at::Tensor& dst, const at::Tensor& src, bool non_blocking) {
+  at::Tensor host = src;
+  if (host.scalar_type() != dst.scalar_type()) host = host.to(dst.scalar_type());
+  if (!host.sizes().equals(dst.sizes())) host = host.expand(dst.sizes());
+  host = host.contiguous();
+  const c10::DeviceIndex dev = dev_of(dst);
+  core::DeviceScope scope(dev);
+  void* stream = core::current_stream(dev);
+  const size_t nbytes = static_cast<size_t>(host.numel()) * host.dtype().itemsize();
+  if (nbytes == 0) return;
+  if (dst.is_contiguous()) {
+    TWG_TORCH_CHECK(twg_memcpy_h2d(dst.data_ptr(), host.const_data_ptr(), nbytes, stream));
+  } else {
+    at::Tensor staged = at::empty(dst.sizes(), dst.options());
+    TWG_TORCH_CHECK(twg_memcpy_h2d(staged.data_ptr(), host.const_data_ptr(), nbytes, stream));
+    device_strided_copy(dst, staged);
+  }
+  // A pinned source is read by the DMA engine after the library call returns; a blocking copy_
+  // must have consumed its source, so wait unless the caller asked for non_blocking.
+  if (!non_blocking) TWG_TORCH_CHECK(twg_stream_sync(stream));
+}
+
+static void device_to_host(at::Tensor& dst, const at::Tensor& src, bool non_blocking) {
+  const c10::DeviceIndex dev = dev_of(src);
+  core::DeviceScope scope(dev);
+  void* stream = core::current_stream(dev);
+  at::Tensor dense = src;
+  if (!dense.sizes().equals(dst.sizes())) dense = dense.expand(dst.sizes());
+  if (!dense.is_contiguous()) {
+    at::Tensor tmp = at::empty(dense.sizes(), src.options());
+    device_strided_copy(tmp, dense);
+    dense = tmp;
+  }
+  const size_t nbytes = static_cast<size_t>(dense.numel()) * dense.dtype().itemsize();
+  if (nbytes == 0) return;
+  if (dst.is_contiguous() && dst.scalar_type() == src.scalar_type()) {
+    // non_blocking only takes effect for pinned destinations; the library blocks for pageable ones
+    TWG_TORCH_CHECK(twg_memcpy_d2h(dst.data_ptr(), dense.const_data_ptr(), nbytes, stream, non_blocking ? 0 : 1));
+  } else {
+    at::Tensor host = at::empty(dense.sizes(), dst.options().dtype(src.scalar_type()).memory_format(c10::MemoryFormat::Contiguous));
+    TWG_TORCH_CHECK(twg_memcpy_d2h(host.data_ptr(), dense.const_data_ptr(), nbytes, stream, 1));
+    dst.copy_(host);
+  }
+}
+
+static void device_to_device(at::Tensor& dst, const at::Tensor& src) {
+  if (dst.scalar_type() != src.scalar_type()) {
+    // dtype conversion is outside the accelerated path: convert on the host
+    at::Tensor host = src.cpu().to(dst.scalar_type());
+    host_to_device(dst, host, false);
+    return;
+  }
+  if (dev_of(dst) != dev_of(src)) {
+    at::Tensor dense = src.contiguous();
+    at::Tensor landed = at::empty(dense.sizes(), dst.options());
+    const size_t nbytes = static_cast<size_t>(dense.numel()) * dense.dtype().itemsize();
+    // order the peer copy after the producer on the source device
+    TWG_TORCH_CHECK(twg_stream_sync(core::current_stream(dev_of(src))));
+    core::DeviceScope scope(dev_of(dst));
+    TWG_TORCH_CHECK(twg_memcpy_d2d(landed.data_ptr(), dense.const_data_ptr(), nbytes, core::current_stream(dev_of(dst))));
+    device_strided_copy(dst, landed);
+    return;
+  }
+  device_strided_copy(dst, src);
+}
+
+at::Tensor& copy_(at::Tensor& self, const at::Tensor& src, bool non_blocking) {
+  if (self.is_same(src)) return self;
+  TORCH_CHECK(self.defined() && src.defined(), "copy_: undefined tensor");
+  if (src.device().is_cpu() && self.device().is_privateuseone()) {
+    host_to_device(self, src, non_blocking);
+  } else if (src.device().is_privateuseone() && self.device().is_cpu()) {
+    device_to_host(self, src, non_blocking);
+  } else if (src.device().is_privateuseone() && self.device().is_privateuseone()) {
+    device_to_device(self, src);
+  } else {
+    TORCH_CHECK(false, "torch_webgpu: copy_ between ", src.device(), " and ", self.device(), " is not supported");
+  }
+  return self;
+}
+
+at::Tensor _copy_from(const at::Tensor& self, const at::Tensor& dst, bool non_blocking) {
+  at::Tensor& out = const_cast<at::Tensor&>(dst);
+  copy_(out, self, non_blocking);
+  return dst;
+}
+
+at::Tensor _copy_from_and_resize(const at::Tensor& self, const at::Tensor& dst) {
+  dst.resize_(self.sizes());
+  at::Tensor& out = const_cast<at::Tensor&>(dst);
+  copy_(out, self, false);
+  return dst;
+}
+
+at::Tensor to_device(const at::Tensor& self, at::Device device, at::ScalarType dtype, bool non_blocking, bool copy,
+                     std::optional<c10::MemoryFormat> memory_format) {
+  return at::native::to(self, device, dtype, non_blocking, copy, memory_format);
+}
+
+TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
+  m.impl("copy_", TORCH_FN(copy_));
+  m.impl("_copy_from", TORCH_FN(_copy_from));
+  m.impl("_copy_from_and_resize", TORCH_FN(_copy_from_and_resize));
+  m.impl("to.device", TORCH_FN(to_device));
+}
+
+}  // namespace ops
+}  // namespace torch_webgpu

@@ -1,0 +1,115 @@
+// The `webgpu::` custom-op library the compile backend's runtime calls.
+//
+// Schemas kept from the reference (csrc/ops/webgpu_ops.cpp:47-62): create_buffer, write_buffer,
+// fused_add_relu, plus the global AutogradPrivateUse1 fallthrough.  Added for the fused-pointwise
+// backend: compile_fused (SSA program -> kernel handle) and run_fused (one launch for a whole
+// pointwise subgraph).
+#include <torch/library.h>
+
+#include "twg_host.h"
+
+namespace torch_webgpu {
+namespace ops {
+
+at::Tensor create_buffer(c10::IntArrayRef size, c10::IntArrayRef stride, std::optional<at::ScalarType> dtype_opt) {
+  return at::empty_strided(size, stride, at::TensorOptions().dtype(dtype_opt).device(c10::Device(c10::kPrivateUse1)));
+}
+
+at::Tensor write_buffer(at::Tensor& self, const at::Tensor& src) {
+  self.copy_(src);
+  return self;
+}
+
+at::Tensor fused_add_relu(const at::Tensor& self, const at::Tensor& other) {
+  const auto shape = at::infer_size(self.sizes(), other.sizes());
+  at::Tensor out = at::empty(shape, self.options());
+  at::TensorIteratorConfig config;
+  config.set_check_mem_overlap(true);
+  config.add_output(out);
+  config.add_const_input(self);
+  config.add_const_input(other);
+  config.check_all_same_dtype(true);
+  auto iter = config.build();
+  binary_kernel(TWG_BINARY_FUSED_ADD_RELU, iter, 1.0f);
+  return out;
+}
+
+// Program encoding: four parallel lists, one entry per SSA instruction (TwgFusedInstr fields).
+int64_t compile_fused(c10::IntArrayRef opcodes, c10::IntArrayRef a, c10::IntArrayRef b, c10::ArrayRef<double> imm) {
+  const size_t n = opcodes.size();
+  TORCH_CHECK(a.size() == n && b.size() == n && imm.size() == n, "compile_fused: the four lists must have one length");
+  std::vector<TwgFusedInstr> prog(n);
+  for (size_t i = 0; i < n; ++i) {
+    prog[i].opcode = static_cast<int32_t>(opcodes[i]);
+    prog[i].a = static_cast<int32_t>(a[i]);
+    prog[i].b = static_cast<int32_t>(b[i]);
+    prog[i].imm = static_cast<float>(imm[i]);
+  }
+  TwgFusedProgram* handle = nullptr;
+  TWG_TORCH_CHECK(twg_fused_compile(prog.data(), static_cast<int>(n), &handle));
+  return static_cast<int64_t>(reinterpret_cast<intptr_t>(handle));
+}
+
+int64_t fused_kind(int64_t handle) {
+  int kind = 0;
+  TWG_TORCH_CHECK(twg_fused_kind(reinterpret_cast<TwgFusedProgram*>(static_cast<intptr_t>(handle)), &kind));
+  return kind;
+}
+
+// Inputs broadcast against each other; outputs are freshly allocated dense tensors of the
+// broadcast shape with the dtypes in `out_dtypes` (float32 or bool).
+std::vector<at::Tensor> run_fused(int64_t handle, at::TensorList inputs, c10::IntArrayRef out_dtypes) {
+  TORCH_CHECK(!inputs.empty() && !out_dtypes.empty(), "run_fused: needs at least one input and one output");
+  const c10::Device device = inputs[0].device();
+  std::vector<int64_t> shape(inputs[0].sizes().begin(), inputs[0].sizes().end());
+  for (size_t i = 1; i < inputs.size(); ++i) shape = at::infer_size(shape, inputs[i].sizes());
+  std::vector<at::Tensor> outs;
+  at::TensorIteratorConfig config;
+  config.set_check_mem_overlap(true).check_all_same_dtype(false);
+  for (auto dt : out_dtypes) {
+    const auto st = static_cast<at::ScalarType>(dt);
+    TORCH_CHECK(st == at::kFloat || st == at::kBool, "run_fused: outputs are float32 or bool");
+    outs.push_back(at::empty(shape, inputs[0].options().dtype(st)));
+  }
+  for (auto& o : outs) config.add_output(o);
+  for (const auto& in : inputs) {
+    TORCH_CHECK(in.device() == device, "run_fused: inputs live on different devices");
+    TORCH_CHECK(in.scalar_type() == at::kFloat || in.scalar_type() == at::kBool, "run_fused: inputs are float32 or bool");
+    config.add_const_input(in);
+  }
+  auto iter = config.build();
+  if (iter.numel() == 0) return outs;
+  const c10::DeviceIndex dev = iter_device(iter);
+  core::DeviceScope scope(dev);
+  TwgIterDesc desc = desc_from_iter(iter);
+  std::vector<void*> ptrs(iter.ntensors());
+  for (int t = 0; t < iter.ntensors(); ++t) ptrs[t] = iter.data_ptr(t);
+  TWG_TORCH_CHECK(twg_fused_launch(reinterpret_cast<TwgFusedProgram*>(static_cast<intptr_t>(handle)), &desc, ptrs.data(),
+                                   core::current_stream(dev)));
+  return outs;
+}
+
+}  // namespace ops
+
+TORCH_LIBRARY(webgpu, m) {
+  m.def("create_buffer(int[] size, int[] stride, ScalarType? dtype=None) -> Tensor");
+  m.def("write_buffer(Tensor self, Tensor src) -> Tensor");
+  m.def("fused_add_relu(Tensor self, Tensor src) -> Tensor");
+  m.def("compile_fused(int[] opcodes, int[] a, int[] b, float[] imm) -> int");
+  m.def("fused_kind(int handle) -> int");
+  m.def("run_fused(int handle, Tensor[] inputs, int[] out_dtypes) -> Tensor[]");
+}
+TORCH_LIBRARY_IMPL(webgpu, PrivateUse1, m) {
+  m.impl("create_buffer", TORCH_FN(ops::create_buffer));
+  m.impl("write_buffer", TORCH_FN(ops::write_buffer));
+  m.impl("fused_add_relu", TORCH_FN(ops::fused_add_relu));
+  m.impl("run_fused", TORCH_FN(ops::run_fused));
+}
+TORCH_LIBRARY_IMPL(webgpu, CatchAll, m) {
+  m.impl("create_buffer", TORCH_FN(ops::create_buffer));
+  m.impl("compile_fused", TORCH_FN(ops::compile_fused));
+  m.impl("fused_kind", TORCH_FN(ops::fused_kind));
+}
+TORCH_LIBRARY_IMPL(_, AutogradPrivateUse1, m) { m.fallback(torch::CppFunction::makeFallthrough()); }
+
+}  // namespace torch_webgpu

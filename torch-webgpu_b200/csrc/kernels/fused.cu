@@ -279,7 +279,6 @@ typedef int CUresult;
 
 struct Dyn {
   std::mutex mu;
-  bool loaded = false;
   std::string nvrtc_path;
   void* nvrtc = nullptr;
   void* cuda = nullptr;
@@ -306,32 +305,42 @@ static bool sym(void* lib, const char* name, T* out) {
   return *out != nullptr;
 }
 
-static int load_dyn() {
+static int load_nvrtc() {
   Dyn& d = g_dyn;
   std::lock_guard<std::mutex> lock(d.mu);
-  if (d.loaded) return TWG_OK;
+  if (d.nvrtc) return TWG_OK;
   std::vector<std::string> candidates;
   if (!d.nvrtc_path.empty()) candidates.push_back(d.nvrtc_path);
   if (const char* env = getenv("TWG_NVRTC_PATH")) candidates.push_back(env);
   candidates.push_back("libnvrtc.so.12");
   candidates.push_back("/usr/local/cuda/lib64/libnvrtc.so.12");
   candidates.push_back("libnvrtc.so");
+  void* lib = nullptr;
   for (const auto& c : candidates) {
-    d.nvrtc = dlopen(c.c_str(), RTLD_NOW | RTLD_LOCAL);
-    if (d.nvrtc) break;
+    lib = dlopen(c.c_str(), RTLD_NOW | RTLD_LOCAL);
+    if (lib) break;
   }
-  if (!d.nvrtc) return set_error(TWG_ERR_UNSUPPORTED, "cannot load NVRTC (libnvrtc.so.12): %s", dlerror());
-  d.cuda = dlopen("libcuda.so.1", RTLD_NOW | RTLD_LOCAL);
-  if (!d.cuda) return set_error(TWG_ERR_CUDA, "cannot load the CUDA driver library libcuda.so.1: %s", dlerror());
-  bool ok = sym(d.nvrtc, "nvrtcCreateProgram", &d.CreateProgram) && sym(d.nvrtc, "nvrtcDestroyProgram", &d.DestroyProgram) &&
-            sym(d.nvrtc, "nvrtcCompileProgram", &d.CompileProgram) && sym(d.nvrtc, "nvrtcGetCUBINSize", &d.GetCUBINSize) &&
-            sym(d.nvrtc, "nvrtcGetCUBIN", &d.GetCUBIN) && sym(d.nvrtc, "nvrtcGetProgramLogSize", &d.GetProgramLogSize) &&
-            sym(d.nvrtc, "nvrtcGetProgramLog", &d.GetProgramLog) && sym(d.nvrtc, "nvrtcGetErrorString", &d.GetErrorString) &&
-            sym(d.cuda, "cuModuleLoadData", &d.ModuleLoadData) && sym(d.cuda, "cuModuleUnload", &d.ModuleUnload) &&
-            sym(d.cuda, "cuModuleGetFunction", &d.ModuleGetFunction) && sym(d.cuda, "cuLaunchKernel", &d.LaunchKernel) &&
-            sym(d.cuda, "cuGetErrorString", &d.CuGetErrorString);
-  if (!ok) return set_error(TWG_ERR_UNSUPPORTED, "NVRTC / driver library lacks a required entry point");
-  d.loaded = true;
+  if (!lib) return set_error(TWG_ERR_UNSUPPORTED, "cannot load NVRTC (libnvrtc.so.12): %s", dlerror());
+  bool ok = sym(lib, "nvrtcCreateProgram", &d.CreateProgram) && sym(lib, "nvrtcDestroyProgram", &d.DestroyProgram) &&
+            sym(lib, "nvrtcCompileProgram", &d.CompileProgram) && sym(lib, "nvrtcGetCUBINSize", &d.GetCUBINSize) &&
+            sym(lib, "nvrtcGetCUBIN", &d.GetCUBIN) && sym(lib, "nvrtcGetProgramLogSize", &d.GetProgramLogSize) &&
+            sym(lib, "nvrtcGetProgramLog", &d.GetProgramLog) && sym(lib, "nvrtcGetErrorString", &d.GetErrorString);
+  if (!ok) return set_error(TWG_ERR_UNSUPPORTED, "the NVRTC library lacks a required entry point");
+  d.nvrtc = lib;
+  return TWG_OK;
+}
+
+static int load_driver() {
+  Dyn& d = g_dyn;
+  std::lock_guard<std::mutex> lock(d.mu);
+  if (d.cuda) return TWG_OK;
+  void* lib = dlopen("libcuda.so.1", RTLD_NOW | RTLD_LOCAL);
+  if (!lib) return set_error(TWG_ERR_CUDA, "cannot load the CUDA driver library libcuda.so.1: %s", dlerror());
+  bool ok = sym(lib, "cuModuleLoadData", &d.ModuleLoadData) && sym(lib, "cuModuleUnload", &d.ModuleUnload) &&
+            sym(lib, "cuModuleGetFunction", &d.ModuleGetFunction) && sym(lib, "cuLaunchKernel", &d.LaunchKernel) &&
+            sym(lib, "cuGetErrorString", &d.CuGetErrorString);
+  if (!ok) return set_error(TWG_ERR_UNSUPPORTED, "the CUDA driver library lacks a required entry point");
+  d.cuda = lib;
   return TWG_OK;
 }
 
@@ -342,7 +351,7 @@ static int cu_fail(CUresult r, const char* what) {
 }
 
 static int nvrtc_compile(const std::string& source, std::vector<char>* cubin) {
-  if (int rc = load_dyn()) return rc;
+  if (int rc = load_nvrtc()) return rc;
   Dyn& d = g_dyn;
   nvrtcProgram prog = nullptr;
   const char* headers[] = {kPointwiseHeader};
@@ -393,6 +402,7 @@ struct TwgFusedProgram {
 namespace twg {
 
 static int get_module(TwgFusedProgram* p, DeviceModule** out) {
+  if (int rc = load_driver()) return rc;
   int dev = 0;
   TWG_CUDA(cudaGetDevice(&dev));
   std::lock_guard<std::mutex> lock(p->mu);

@@ -149,9 +149,9 @@ struct PwPtrs {
 template <class F>
 struct PwTraits {
   static constexpr int NIN = F::NIN, NOUT = F::NOUT, NT = F::NIN + F::NOUT;
-  static constexpr bool in_byte(int k) { return (F::kInByteMask >> k) & 1u; }
-  static constexpr bool out_byte(int k) { return (F::kOutByteMask >> k) & 1u; }
-  static constexpr bool all_bytes() {
+  __host__ __device__ static constexpr bool in_byte(int k) { return (F::kInByteMask >> k) & 1u; }
+  __host__ __device__ static constexpr bool out_byte(int k) { return (F::kOutByteMask >> k) & 1u; }
+  __host__ __device__ static constexpr bool all_bytes() {
     return F::kInByteMask == ((1u << F::NIN) - 1u) && F::kOutByteMask == ((1u << F::NOUT) - 1u);
   }
   static constexpr int VEC = all_bytes() ? 16 : 4;

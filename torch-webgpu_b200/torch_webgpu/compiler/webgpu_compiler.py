@@ -1,0 +1,202 @@
+"""`webgpu_backend`: the torch.compile entry point (reference:
+python/torch_webgpu/compiler/webgpu_compiler.py:22-62).
+
+The reference lowers FX -> HighIR -> LowIR, runs the lowered program once at compile time,
+prints it and then returns the *unfused* `gm.forward`; it accepts only graphs without inputs.
+This backend keeps the entry point and does the job for real:
+
+  1. dynamo's graph is normalised to ATen ops with `aot_autograd`, so `a + b`, `torch.add`,
+     `operator.add`, `F.relu` ... all arrive as the same few overloads, with FakeTensor metadata;
+  2. maximal runs of supported pointwise ops over one iteration shape are cut out of the graph
+     (`partition`), each becomes one SSA program (`program.Program`) and one call to
+     `torch.ops.webgpu.run_fused` - one kernel, no intermediate tensor touches HBM;
+  3. everything else (views, copies, masked_select, ops the library has no fused form for) stays
+     in the graph and runs through the dispatcher on the same device - there is no CPU fallback.
+"""
+from __future__ import annotations
+
+import operator
+from typing import Callable, List
+
+import torch
+from torch import fx
+from torch._dynamo import register_backend
+from torch._dynamo.backends.common import aot_autograd
+
+from . import program as P
+
+aten = torch.ops.aten
+
+# Set by tests / users to watch what the backend did with the last graph it compiled.
+last_compile_report: dict = {}
+
+
+def _val(node):
+    return node.meta.get("val") if isinstance(node, fx.Node) else None
+
+
+def _is_webgpu_tensor(v) -> bool:
+    return isinstance(v, torch.Tensor) and v.device.type == "webgpu"
+
+
+def _dtype_tag(v):
+    if v.dtype == torch.float32:
+        return P.F32
+    if v.dtype == torch.bool:
+        return P.BOOL
+    return None
+
+
+def _fusible(node: fx.Node) -> bool:
+    if node.op != "call_function" or node.target not in P.supported_targets():
+        return False
+    out = _val(node)
+    if not _is_webgpu_tensor(out) or _dtype_tag(out) is None:
+        return False
+    t = node.target
+    for arg in node.args:
+        if isinstance(arg, fx.Node):
+            v = _val(arg)
+            if not _is_webgpu_tensor(v) or _dtype_tag(v) is None:
+                return False
+        elif not isinstance(arg, (int, float, bool)):
+            return False
+    tensor_args = [a for a in node.args if isinstance(a, fx.Node)]
+    if t in P.UNARY_OPS or t is aten.gelu.default:
+        return _dtype_tag(_val(tensor_args[0])) == P.F32
+    if t in P.BINARY_OPS or t in P.COMPARE_OPS:
+        return all(_dtype_tag(_val(a)) == P.F32 for a in tensor_args) and out.dtype in (torch.float32, torch.bool)
+    if t in (aten.bitwise_and.Tensor, aten.logical_and.default):
+        return len(tensor_args) == 2 and all(_dtype_tag(_val(a)) == P.BOOL for a in tensor_args)
+    return False
+
+
+def partition(graph: fx.Graph) -> list[list[fx.Node]]:
+    """Split the graph's fusible nodes into groups that can each become one kernel.
+
+    One group is open at a time.  A fusible node joins it when it iterates over the same shape;
+    a different shape closes the group, and so does any other node that reads a value the open
+    group produces (the value has to exist before that node runs).  Nodes that do not touch the
+    group pass by without closing it, so independent ops in between do not break a chain.
+    """
+    groups: list[list[fx.Node]] = []
+    open_group: list[fx.Node] = []
+    open_shape = None
+
+    def close():
+        nonlocal open_group, open_shape
+        if open_group:
+            groups.append(open_group)
+        open_group, open_shape = [], None
+
+    for node in graph.nodes:
+        if _fusible(node):
+            shape = tuple(_val(node).shape)
+            if open_group and shape != open_shape:
+                close()
+            open_group.append(node)
+            open_shape = shape
+        elif open_group and any(inp in open_group for inp in node.all_input_nodes):
+            close()
+    close()
+    return [g for g in groups if len(g) >= 2]
+
+
+def build_program(group: list[fx.Node]):
+    """SSA program of a group plus the fx nodes that feed it and the group nodes it must output."""
+    prog = P.Program()
+    value_of: dict[fx.Node, int] = {}
+    in_group = set(group)
+
+    # external inputs, in first-use order
+    for node in group:
+        for arg in node.args:
+            if isinstance(arg, fx.Node) and arg not in in_group and arg not in value_of:
+                value_of[arg] = prog.add_input(arg, _dtype_tag(_val(arg)))
+
+    def operand(arg) -> int:
+        if isinstance(arg, fx.Node):
+            return value_of[arg]
+        return prog.const(float(arg))
+
+    for node in group:
+        t = node.target
+        if t in P.UNARY_OPS:
+            value_of[node] = prog.op(P.UNARY_OPS[t], operand(node.args[0]))
+        elif t is aten.gelu.default:
+            approximate = node.kwargs.get("approximate", node.args[1] if len(node.args) > 1 else "none")
+            value_of[node] = prog.op(P.GELU_TANH if approximate == "tanh" else P.GELU_ERF, operand(node.args[0]))
+        elif t in P.BINARY_OPS:
+            a, b = operand(node.args[0]), operand(node.args[1])
+            alpha = node.kwargs.get("alpha", node.args[2] if len(node.args) > 2 else 1)
+            value_of[node] = prog.op(P.BINARY_OPS[t], a, b, float(alpha) if P.BINARY_OPS[t] == P.ADD else 0.0)
+        elif t in P.COMPARE_OPS:
+            a, b = operand(node.args[0]), operand(node.args[1])
+            value_of[node] = prog.op(P.COMPARE_OPS[t], a, b)
+        else:  # bitwise_and / logical_and on bool
+            value_of[node] = prog.op(P.AND, operand(node.args[0]), operand(node.args[1]))
+
+    out_nodes = [n for n in group if any(u not in in_group for u in n.users)]
+    for n in out_nodes:
+        prog.add_output(value_of[n])
+    return prog, list(prog.inputs), out_nodes
+
+
+class FusedKernel:
+    """Callable placed in the rewritten graph: one launch of a compiled program."""
+
+    def __init__(self, prog: P.Program):
+        self.program = prog
+        self.handle = torch.ops.webgpu.compile_fused(*prog.columns())
+        self.kind = "aot" if torch.ops.webgpu.fused_kind(self.handle) == 0 else "nvrtc"
+        self.out_dtypes = prog.out_dtypes()
+        self.__name__ = f"webgpu_fused_{len(prog.instrs)}"
+
+    def __call__(self, *inputs):
+        return torch.ops.webgpu.run_fused(self.handle, list(inputs), self.out_dtypes)
+
+
+def fuse_graph(gm: fx.GraphModule) -> fx.GraphModule:
+    graph = gm.graph
+    kernels = []
+    for group in partition(graph):
+        prog, inputs, out_nodes = build_program(group)
+        if not out_nodes:
+            continue
+        kernel = FusedKernel(prog)
+        kernels.append(kernel)
+        with graph.inserting_after(group[-1]):
+            call = graph.call_function(kernel, tuple(inputs))
+        prev = call
+        for slot, n in enumerate(out_nodes):
+            with graph.inserting_after(prev):
+                item = graph.call_function(operator.getitem, (call, slot))
+            item.meta = dict(n.meta)
+            n.replace_all_uses_with(item)
+            prev = item
+        for n in reversed(group):
+            graph.erase_node(n)
+    graph.lint()
+    gm.recompile()
+    last_compile_report.clear()
+    last_compile_report.update(
+        fused_kernels=len(kernels),
+        kinds=[k.kind for k in kernels],
+        instructions=[len(k.program.instrs) for k in kernels],
+        programs=[str(k.program) for k in kernels],
+        remaining_ops=[str(n.target) for n in graph.nodes if n.op == "call_function" and not isinstance(n.target, FusedKernel)
+                       and n.target is not operator.getitem],
+    )
+    return gm
+
+
+def _fw_compiler(gm: fx.GraphModule, example_inputs):
+    return fuse_graph(gm).forward
+
+
+_aot_backend = aot_autograd(fw_compiler=_fw_compiler)
+
+
+@register_backend
+def webgpu_backend(gm: fx.GraphModule, example_inputs: List[torch.Tensor], **kwargs) -> Callable:
+    return _aot_backend(gm, example_inputs, **kwargs)
