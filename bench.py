@@ -1,0 +1,545 @@
+#!/usr/bin/env python
+"""Benchmark of the data-parallel op path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (the torch.compile configuration of BASELINE.json): a batch of 64 f32 [4096,4096] tensors
+a, b, c ~ N(0,1); one step computes  y = relu(silu(a + b) + c),  m = (y == 0) & (a != 0)  and
+masked_select(a, m)  over the whole batch.  The batch is cut by its leading dimension over the N
+ranks (one process per GPU); the only exchange is an all-gather of one int64 count per rank.
+Total work is fixed, so scaling is "strong".  Inputs are synthetic: every [4096,4096] slab is
+drawn with its own seed so that a rank can build its shard without generating the others.
+
+One JSON line is printed by rank 0.  `value` is whole-job Gelem/s with the inputs resident in HBM;
+`e2e` is the same metric through the public PyTorch API with pinned HOST buffers, upload of a, b, c
+and read-back of the selected values inside the timed region.  `roofline` describes the dominant
+kernel (the fused pointwise chain, 13 algorithmic bytes per element); `ops` lists achieved GB/s of
+every single op of the other configurations.  `--impl reference` times the CPU implementation of
+the same path on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+REPO = Path(__file__).resolve().parent
+sys.path.insert(0, str(REPO / "torch-webgpu_b200"))
+sys.path.insert(0, str(REPO))
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+BATCH, ROWS, COLS = 64, 4096, 4096
+SLAB = ROWS * COLS
+SEED = 4
+FALLBACK_HBM_GBS = 6650.0
+CHAIN_BYTES_PER_ELEM = 13  # read a, b, c (3 x 4 B), write the bool mask (1 B)
+
+
+def slab_seed(tensor_id: int, batch_index: int) -> int:
+    return SEED * 1_000_003 + tensor_id * BATCH + batch_index
+
+
+def fill_shard(dst: torch.Tensor, tensor_id: int, lo: int, hi: int) -> None:
+    """dst[i - lo] = N(0,1) slab i of tensor `tensor_id`, each slab from its own generator."""
+    def one(i: int) -> None:
+        g = torch.Generator().manual_seed(slab_seed(tensor_id, i))
+        torch.randn(ROWS, COLS, generator=g, out=dst[i - lo])
+    with ThreadPoolExecutor(max_workers=min(16, os.cpu_count() or 1)) as ex:
+        list(ex.map(one, range(lo, hi)))
+
+
+def measured_peak() -> tuple[float, str]:
+    p = REPO / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self) -> None:
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in Path(self.path).read_text().splitlines():
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1])); smax.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            # under load = the upper half of the samples (the sampler also sees idle gaps)
+            load = sorted(sm)[len(sm) // 2:]
+            out.update(sm_mhz=statistics.median(load), sm_max_mhz=max(smax), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU implementation of the path (oracle port) - cpu_baseline leg and the reference arm
+# ---------------------------------------------------------------------------------------------
+def cpu_chain_step(oracle, a: np.ndarray, b: np.ndarray, c: np.ndarray) -> int:
+    m = oracle.chain_mask(a, b, c)
+    return int(oracle.masked_select(a.reshape(-1), m.reshape(-1)).size)
+
+
+def cpu_sample(nslabs: int) -> tuple[np.ndarray, np.ndarray, np.ndarray]:
+    bufs = [torch.empty(nslabs, ROWS, COLS) for _ in range(3)]
+    for t, buf in enumerate(bufs):
+        fill_shard(buf, t, 0, nslabs)
+    return tuple(x.numpy() for x in bufs)
+
+
+def run_cpu_baseline(target_seconds: float = 12.0) -> dict:
+    from oracle import oracle
+    oracle.build()
+    oracle.set_num_threads(os.cpu_count() or 1)
+    a, b, c = cpu_sample(1)
+    cpu_chain_step(oracle, a, b, c)  # warm-up
+    t0 = time.perf_counter()
+    cpu_chain_step(oracle, a, b, c)
+    per_slab = max(time.perf_counter() - t0, 1e-4)
+    nslabs = int(max(1, min(16, target_seconds / per_slab / 3)))
+    if nslabs > 1:
+        a, b, c = cpu_sample(nslabs)
+    times = []
+    for _ in range(3):
+        t0 = time.perf_counter()
+        cpu_chain_step(oracle, a, b, c)
+        times.append(time.perf_counter() - t0)
+    best = min(times)
+    out = {"value": nslabs * SLAB / best / 1e9, "unit": "Gelem/s", "cores": oracle.num_threads(), "kind": "port",
+           "sample": f"{nslabs} of {BATCH} [4096,4096] slabs of the chain (seeded like the GPU run), best of 3, "
+                     f"C restatement with OpenMP on {oracle.num_threads()} threads"}
+    # the same sample through the PyTorch CPU kernels the reference's fallback ops execute
+    torch.set_num_threads(os.cpu_count() or 1)
+    ta, tb, tc = (torch.from_numpy(x) for x in (a, b, c))
+    def aten():
+        y = torch.relu(torch.nn.functional.silu(ta + tb) + tc)
+        m = torch.bitwise_and(torch.eq(y, 0), torch.ne(ta, 0))
+        return torch.masked_select(ta, m)
+    aten()
+    t0 = time.perf_counter()
+    aten()
+    out["aten_cpu_gelem_s"] = nslabs * SLAB / (time.perf_counter() - t0) / 1e9
+    return out
+
+
+def run_reference_arm(args) -> None:
+    """The path on the host cores: the C restatement of the reference's CPU-side algorithm
+    (its fallback ops are PyTorch CPU kernels; its shaders cannot run here)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle
+    oracle.build()
+    oracle.set_num_threads(os.cpu_count() or 1)
+    nslabs = 2
+    a, b, c = cpu_sample(nslabs)
+    for _ in range(max(args.warmup, 1)):
+        cpu_chain_step(oracle, a, b, c)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_chain_step(oracle, a, b, c)
+    dt = time.perf_counter() - t0
+    value = args.steps * nslabs * SLAB / dt / 1e9
+    sample = f"each step = {nslabs} of {BATCH} [4096,4096] slabs of the chain on the host cores"
+    line = {
+        "impl": "reference", "metric": "Gelem/s of the compiled chain + masked_select", "value": value, "unit": "Gelem/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "Gelem/s", "cores": oracle.num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "Gelem/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus: int) -> dict:
+    return {"workload": "cfg5: y=relu(silu(a+b)+c); m=(y==0)&(a!=0); masked_select(a,m) over 64 x f32[4096,4096], "
+                        "torch.compile(backend=webgpu_backend) fused chain + single-pass compaction",
+            "global_batch": BATCH, "elements_per_step": BATCH * SLAB, "parallelism": f"batch-sharded x{n_gpus}",
+            "l2": "inputs (>= 1.5 GiB per rank) are larger than the 126 MB L2; no flush needed"}
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+class Events:
+    def __init__(self, abi, n: int):
+        self.abi = abi
+        self.ev = []
+        for _ in range(n):
+            e = ctypes.c_void_p()
+            abi.check(abi.lib().twg_event_create(ctypes.byref(e)))
+            self.ev.append(e)
+
+    def record(self, i: int, stream) -> None:
+        self.abi.check(self.abi.lib().twg_event_record(self.ev[i], stream))
+
+    def elapsed(self, i: int, j: int) -> float:
+        ms = ctypes.c_float()
+        self.abi.check(self.abi.lib().twg_event_elapsed_ms(self.ev[i], self.ev[j], ctypes.byref(ms)))
+        return float(ms.value)
+
+    def sync(self, i: int) -> None:
+        self.abi.check(self.abi.lib().twg_event_sync(self.ev[i]))
+
+
+def time_op(abi, stream, fn, iters: int = 20, warmup: int = 3) -> float:
+    """Median device time (ms) of fn() on `stream`, CUDA events around each call."""
+    ev = Events(abi, 2 * iters)
+    for _ in range(warmup):
+        fn()
+    for i in range(iters):
+        ev.record(2 * i, stream)
+        fn()
+        ev.record(2 * i + 1, stream)
+    abi.check(abi.lib().twg_stream_sync(stream))
+    return statistics.median(ev.elapsed(2 * i, 2 * i + 1) for i in range(iters))
+
+
+def per_op_table(abi, stream, peak: float) -> dict:
+    """Achieved algorithmic GB/s of every single op at the sizes of configurations 1-4."""
+    L = abi.lib()
+    table: dict = {}
+
+    def put(name, nbytes, ms, note=None):
+        gbs = nbytes / ms / 1e6
+        table[name] = {"ms": round(ms, 4), "gbs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 3)}
+        if note:
+            table[name]["note"] = note
+
+    def dense_desc(nt, n):
+        d = abi.IterDesc()
+        abi.check(L.twg_iter_contiguous(ctypes.byref(d), nt, n))
+        return d
+
+    # configuration 1: add [4096,4096], rotating over 4 buffer sets (> L2), and [16384,16384]
+    n1 = 4096 * 4096
+    g = torch.Generator().manual_seed(0)
+    a1, b1 = torch.randn(n1, generator=g).numpy(), torch.randn(n1, generator=g).numpy()
+    sets = []
+    for _ in range(4):
+        da, db, do = abi.DeviceBuffer(4 * n1), abi.DeviceBuffer(4 * n1), abi.DeviceBuffer(4 * n1)
+        da.upload(a1, stream); db.upload(b1, stream)
+        sets.append((da, db, do))
+    d3 = dense_desc(3, n1)
+    turn = [0]
+    def add_small():
+        da, db, do = sets[turn[0] % 4]
+        turn[0] += 1
+        abi.check(L.twg_binary_f32(0, ctypes.byref(d3), da.ptr, db.ptr, 1.0, do.ptr, stream))
+    put("add_4096x4096", 12 * n1, time_op(abi, stream, add_small, iters=40), "4 rotating buffer sets (768 MiB)")
+    del sets
+
+    # configuration 2: activations on 2^28 elements
+    n2 = 1 << 28
+    g = torch.Generator().manual_seed(1)
+    x = (torch.rand(n2, generator=g) * 16 - 8).numpy()
+    dx, dy, dz = abi.DeviceBuffer(4 * n2), abi.DeviceBuffer(4 * n2), abi.DeviceBuffer(4 * n2)
+    dx.upload(x, stream)
+    abi.check(L.twg_memcpy_d2d(dy.ptr, dx.ptr, 4 * n2, stream))
+    d2 = dense_desc(2, n2)
+    d3 = dense_desc(3, n2)
+    put("add_16384x16384", 12 * n2, time_op(abi, stream, lambda: abi.check(
+        L.twg_binary_f32(0, ctypes.byref(d3), dx.ptr, dy.ptr, 1.0, dz.ptr, stream))))
+    for name, op in (("relu", 1), ("silu", 3), ("gelu_erf", 4), ("gelu_tanh", 2)):
+        put(f"{name}_2^28", 8 * n2, time_op(abi, stream, lambda op=op: abi.check(
+            L.twg_unary_f32(op, ctypes.byref(d2), dx.ptr, dz.ptr, stream))))
+    # true transpose: input viewed as [16384,16384].t(), dense output
+    r = 16384
+    dt = abi.make_desc((r, r), [((r, r), (r, 1)), ((r, r), (1, r))])
+    for name, op in (("relu", 1), ("silu", 3), ("gelu_erf", 4)):
+        put(f"{name}_transposed_into_dense", 8 * n2, time_op(abi, stream, lambda op=op: abi.check(
+            L.twg_unary_f32(op, ctypes.byref(dt), dx.ptr, dz.ptr, stream)), iters=10), "2-D tile kernel")
+    ds = abi.make_desc((r, r // 2), [((r, r // 2), (r // 2, 1)), ((r, r // 2), (r, 2))])
+    put("relu_stride2_slice", 8 * (n2 // 2), time_op(abi, stream, lambda: abi.check(
+        L.twg_unary_f32(1, ctypes.byref(ds), dx.ptr, dz.ptr, stream)), iters=10),
+        "strided index path; the stride-2 read drags in whole sectors (real traffic ~12 B/elem)")
+
+    # configuration 3: comparisons and masks on [8192,8192]
+    n3 = 8192 * 8192
+    g = torch.Generator().manual_seed(2)
+    p = torch.randint(-2, 3, (n3,), generator=g).float().numpy()
+    q = torch.randint(-2, 3, (n3,), generator=g).float().numpy()
+    dx.upload(p, stream); dy.upload(q, stream)
+    m1, m2, m3 = abi.DeviceBuffer(n3), abi.DeviceBuffer(n3), abi.DeviceBuffer(n3)
+    d2 = dense_desc(2, n3)
+    d3 = dense_desc(3, n3)
+    put("eq_tensor_8192x8192", 9 * n3, time_op(abi, stream, lambda: abi.check(
+        L.twg_compare_f32(0, ctypes.byref(d3), dx.ptr, dy.ptr, 0.0, m1.ptr, stream)), iters=40))
+    put("ne_scalar_8192x8192", 5 * n3, time_op(abi, stream, lambda: abi.check(
+        L.twg_compare_f32(1, ctypes.byref(d2), dx.ptr, None, 0.0, m2.ptr, stream)), iters=40))
+    put("bitwise_and_bool_8192x8192", 3 * n3, time_op(abi, stream, lambda: abi.check(
+        L.twg_bitwise_and(ctypes.byref(d3), 1, 1, m1.ptr, m2.ptr, m3.ptr, stream)), iters=40),
+        "192 MiB footprint: partly L2-resident")
+    del m1, m2, m3
+
+    # configuration 4: masked_select on [16384,16384]
+    g = torch.Generator().manual_seed(3)
+    src = torch.randn(n2, generator=g).numpy()
+    dx.upload(src, stream)
+    dm = abi.DeviceBuffer(n2)
+    res = abi.DeviceBuffer(16)
+    ws_bytes = L.twg_masked_select_workspace_bytes(n2)
+    ws = abi.DeviceBuffer(ws_bytes)
+    dsel = dense_desc(2, n2)
+    for prob in (0.01, 0.5, 0.99):
+        mask = (torch.rand(n2, generator=g) < prob).numpy().view(np.uint8)
+        dm.upload(mask, stream)
+        run = lambda: abi.check(L.twg_masked_select_f32(ctypes.byref(dsel), dx.ptr, dm.ptr, dz.ptr, res.ptr, ws.ptr, ws_bytes, stream))
+        ms = time_op(abi, stream, run, iters=10)
+        k = int(res.download(np.int64, 2, stream)[0])
+        put(f"masked_select_p{prob}", 5 * n2 + 4 * k, ms, f"k={k}; includes the workspace clear")
+    rowmask = (torch.rand(r, generator=g) < 0.5).numpy().view(np.uint8)
+    dm.upload(rowmask, stream)
+    drow = abi.make_desc((r, r), [((r, r), (r, 1)), ((r, 1), (1, 1))])
+    run = lambda: abi.check(L.twg_masked_select_f32(ctypes.byref(drow), dx.ptr, dm.ptr, dz.ptr, res.ptr, ws.ptr, ws_bytes, stream))
+    ms = time_op(abi, stream, run, iters=10)
+    k = int(res.download(np.int64, 2, stream)[0])
+    put("masked_select_rowmask_16384x1", 4 * n2 + r + 4 * k, ms, f"k={k}; broadcast mask through the strided path")
+    return table
+
+
+def run_gpu_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus != world and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; this benchmark has no CPU fallback (use --impl reference for the CPU arm)")
+
+    import torch.distributed as dist
+    import torch_webgpu
+    from torch_webgpu import abi, webgpu_backend
+    from torch_webgpu.sharding import global_segment, shard_range
+
+    torch.cuda.set_device(local_rank)
+    torch.webgpu.set_device(local_rank)
+    cuda_dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=cuda_dev)
+    L = abi.lib()
+    stream = ctypes.c_void_p(torch.webgpu.current_stream_handle(local_rank))
+    peak, peak_kind = measured_peak()
+
+    lo, hi = shard_range(BATCH, rank, world)
+    nb = hi - lo
+    n = nb * SLAB
+
+    # ---- synthetic inputs in pinned host memory --------------------------------------------
+    host = [torch.empty(nb, ROWS, COLS, pin_memory=True) for _ in range(3)]
+    for t, buf in enumerate(host):
+        fill_shard(buf, t, lo, hi)
+
+    def barrier():
+        abi.check(L.twg_stream_sync(stream))
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    # ---- leg 1: inputs resident in HBM, C ABI calls ----------------------------------------
+    dev_in = [abi.DeviceBuffer(4 * n, local_rank, stream) for _ in range(3)]
+    for buf, h in zip(dev_in, host):
+        abi.check(L.twg_memcpy_h2d(buf.ptr, h.data_ptr(), 4 * n, stream))
+    d_mask = abi.DeviceBuffer(n, local_rank, stream)
+    d_out = abi.DeviceBuffer(4 * n, local_rank, stream)
+    d_res = abi.DeviceBuffer(16, local_rank, stream)
+    ws_bytes = L.twg_masked_select_workspace_bytes(n)
+    d_ws = abi.DeviceBuffer(ws_bytes, local_rank, stream)
+    h_res = torch.zeros(2, dtype=torch.int64, pin_memory=True)
+    program = abi.fused_compile(abi.CHAIN_MASK_PROGRAM)
+    assert abi.fused_kind(program) == "aot"
+    desc4 = abi.IterDesc()
+    abi.check(L.twg_iter_contiguous(ctypes.byref(desc4), 4, n))
+    desc2 = abi.IterDesc()
+    abi.check(L.twg_iter_contiguous(ctypes.byref(desc2), 2, n))
+    ptrs = (ctypes.c_void_p * 4)(d_mask.ptr, dev_in[0].ptr, dev_in[1].ptr, dev_in[2].ptr)
+
+    steps, warmup = args.steps, args.warmup
+    ev = Events(abi, 2 + 2 * steps)
+    counts_seen = []
+
+    def step(i: int | None) -> None:
+        if i is not None:
+            ev.record(2 + 2 * i, stream)
+        abi.check(L.twg_fused_launch(program, ctypes.byref(desc4), ptrs, stream))
+        if i is not None:
+            ev.record(3 + 2 * i, stream)
+        abi.check(L.twg_masked_select_f32(ctypes.byref(desc2), dev_in[0].ptr, d_mask.ptr, d_out.ptr, d_res.ptr, d_ws.ptr,
+                                          ws_bytes, stream))
+        abi.check(L.twg_memcpy_d2h(h_res.data_ptr(), d_res.ptr, 16, stream, 1))
+        if int(h_res[1]) != 0:
+            raise RuntimeError(f"masked_select reported device status {int(h_res[1])}")
+        offset, total, counts = global_segment(int(h_res[0]), cuda_dev)
+        counts_seen.append((offset, total))
+
+    for _ in range(warmup):
+        step(None)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    L.twg_reset_launch_count()
+    ev.record(0, stream)
+    for i in range(steps):
+        step(i)
+    ev.record(1, stream)
+    ev.sync(1)
+    launches = int(L.twg_launch_count())
+    barrier()
+    clocks = sampler.stop() if rank == 0 else {}
+    ms_total = ev.elapsed(0, 1)
+    fused_ms = statistics.mean(ev.elapsed(2 + 2 * i, 3 + 2 * i) for i in range(steps))
+    t = torch.tensor([ms_total, fused_ms], dtype=torch.float64, device=cuda_dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, fused_ms_max = float(t[0]), float(t[1])
+    ms_per_step = ms_total / steps
+    value = BATCH * SLAB / (ms_per_step * 1e-3) / 1e9
+    local_k, total_k = int(h_res[0]), counts_seen[-1][1]
+
+    # ---- per-op table (single GPU only) -----------------------------------------------------
+    del d_out, d_mask, d_ws
+    for b_ in dev_in:
+        b_.free()
+    ops = per_op_table(abi, stream, peak) if world == 1 and not args.no_ops else None
+    abi.check(L.twg_empty_cache(local_rank))
+
+    # ---- leg 2: end to end through the public API with host buffers ---------------------------
+    def chain(a, b, c):
+        y = torch.relu(torch.nn.functional.silu(a + b) + c)
+        m = torch.bitwise_and(torch.eq(y, 0), torch.ne(a, 0))
+        return torch.masked_select(a, m)
+
+    compiled = torch.compile(chain, backend=webgpu_backend)
+    dev_name = f"webgpu:{local_rank}"
+    h_sel = torch.empty(n, pin_memory=True)
+    e2e_steps = max(1, min(steps, 4))
+    d2h_bytes = [0]
+
+    def e2e_step():
+        da, db, dc = (h.to(dev_name, non_blocking=True) for h in host)
+        sel = compiled(da, db, dc)
+        k = sel.numel()
+        h_sel[:k].copy_(sel)                       # blocking read-back of the result
+        d2h_bytes[0] = 4 * k + 16
+        global_segment(k, cuda_dev)
+
+    e2e_step()  # compile + warm the allocator
+    barrier()
+    ev2 = Events(abi, 2)
+    ev2.record(0, stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    ev2.record(1, stream)
+    ev2.sync(1)
+    barrier()
+    t = torch.tensor([ev2.elapsed(0, 1)], dtype=torch.float64, device=cuda_dev)
+    tb = torch.tensor([3 * 4 * n, d2h_bytes[0]], dtype=torch.int64, device=cuda_dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tb, op=dist.ReduceOp.SUM)
+    e2e_ms = float(t[0]) / e2e_steps
+    e2e = {"value": BATCH * SLAB / (e2e_ms * 1e-3) / 1e9, "unit": "Gelem/s", "ms_per_step": e2e_ms, "steps": e2e_steps,
+           "h2d_bytes_per_step": int(tb[0]), "d2h_bytes_per_step": int(tb[1]),
+           "api": "x.to('webgpu') from pinned tensors, torch.compile(backend=webgpu_backend) chain, pinned read-back"}
+
+    if rank == 0:
+        achieved = CHAIN_BYTES_PER_ELEM * n / (fused_ms_max * 1e-3) / 1e9
+        traffic = None
+        tfile = REPO / "profiles" / "chain_kernel_traffic.json"
+        if tfile.exists():
+            try:
+                traffic = float(json.loads(tfile.read_text())["dram_bytes_per_element"]) * n
+            except Exception:
+                traffic = None
+        line = {
+            "metric": "Gelem/s of the compiled chain + masked_select", "value": value, "unit": "Gelem/s", "n_gpus": world,
+            "steps": steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(world),
+            "selected_elements": total_k,
+            "roofline": {"bound": "hbm", "kernel": "pw_contig_kernel<AotChainMask> (fused chain, 13 B/elem)",
+                         "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": traffic, "ms_per_launch": fused_ms_max,
+                         "algorithmic_bytes_per_launch": CHAIN_BYTES_PER_ELEM * n},
+            "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+        }
+        if ops is not None:
+            line["ops"] = ops
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = run_cpu_baseline()
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=int(os.environ.get("WORLD_SIZE", "1")))
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-ops", action="store_true", help="skip the per-op GB/s table")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -176,7 +176,10 @@ int twg_bitwise_and(const TwgIterDesc* desc, int itemsize, int is_bool, const vo
 size_t twg_masked_select_workspace_bytes(int64_t numel);
 int twg_masked_select_f32(const TwgIterDesc* desc, const float* src, const uint8_t* mask, float* out,
                           int64_t* result_dev, void* workspace, size_t workspace_bytes, void* stream);
-/* Test hook: make every look-back wait give up after `polls` polls (0 restores the default). */
+/* Test hook for the bounded wait.  polls > 0: every look-back wait gives up after `polls` polls.
+ * polls < 0: additionally the first tile never publishes its count (a flag nothing sets), so the
+ * tiles that depend on it run out of polls after |polls| and result[1] becomes TWG_ERR_TIMEOUT;
+ * the kernel still terminates and the context stays usable.  0 restores the default budget. */
 int twg_masked_select_set_poll_budget(int64_t polls);
 
 /* ---- fused pointwise programs for the torch.compile backend ---------------------------------

@@ -1,0 +1,469 @@
+"""Parity of the CUDA path with the CPU oracle, driven through the C ABI (ctypes -> libtwg.so).
+
+Every case uploads seeded inputs, makes ONE library call and compares the download with
+oracle/twg_oracle.c on the same inputs: bit-exact for add / mul / relu / abs / comparisons /
+bitwise_and / masked_select / copies, max(2 ulp, 1e-6 relative) for silu, the same plus a 2e-6
+absolute floor for GELU.  The golden PyTorch-ATen fixtures are checked as well.
+"""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+from oracle import oracle
+from util import assert_bit_equal, assert_close_ulp
+
+pytestmark = pytest.mark.gpu
+
+SIZES = [0, 1, 2, 3, 4, 5, 63, 64, 65, 1023, 4095, 4096, 4097, 100003]
+
+
+@pytest.fixture(scope="module")
+def abi():
+    from torch_webgpu import abi as _abi
+    assert _abi.device_count() >= 1, "no CUDA device visible"
+    return _abi
+
+
+def rnd(n, seed, lo=-8.0, hi=8.0):
+    rng = np.random.default_rng(seed)
+    return (rng.random(n, dtype=np.float32) * (hi - lo) + lo).astype(np.float32)
+
+
+def small_ints(n, seed):
+    return np.random.default_rng(seed).integers(-2, 3, n).astype(np.float32)
+
+
+def b(a):
+    return a.view(np.bool_)
+
+
+# ------------------------------------------------------------------------------------------
+# golden fixtures (PyTorch CPU ATen outputs, reference-test known answers)
+# ------------------------------------------------------------------------------------------
+def test_known_answers_of_the_reference_tests(abi, golden):
+    out = abi.binary("add", golden["kat_add_a"], golden["kat_add_b"])
+    assert np.allclose(out, golden["kat_add_expected_handwritten"])          # tests/ops/test_add.py:10
+    assert_bit_equal(out, golden["kat_add_out"], "add")
+    out = abi.binary("fused_add_relu", golden["kat_add_a"], golden["kat_add_b"])
+    assert np.allclose(out, golden["kat_fused_add_relu_expected_handwritten"])  # tests/test_dev.py:18
+    for i in range(4):
+        x = golden[f"kat_act{i}_x"]
+        assert np.allclose(abi.unary("gelu_tanh", x), golden[f"kat_act{i}_gelu"], atol=1e-3)  # test_gelu.py:14
+        assert np.allclose(abi.unary("silu", x), golden[f"kat_act{i}_silu"], atol=1e-6)       # test_silu.py:13
+        assert_close_ulp(abi.unary("gelu_erf", x), golden[f"kat_act{i}_gelu"], abs_floor=2e-6, what="gelu")
+        assert_close_ulp(abi.unary("silu", x), golden[f"kat_act{i}_silu"], what="silu")
+        assert_bit_equal(abi.unary("relu", x), golden[f"kat_act{i}_relu"], "relu")
+
+
+def test_edge_values_against_aten(abi, golden):
+    x, y = golden["edge_x"], golden["edge_y"]
+    assert_bit_equal(abi.binary("add", x, y), golden["edge_add"], "edge add")
+    assert_bit_equal(abi.binary("add", x, y, alpha=2.5), golden["edge_add_alpha"], "edge add alpha")
+    assert_bit_equal(abi.unary("relu", x), golden["edge_relu"], "edge relu")
+    assert_bit_equal(abi.compare("eq", x, y), b(golden["edge_eq"]), "edge eq")
+    assert_bit_equal(abi.compare("ne", x, 0.0), b(golden["edge_ne0"]), "edge ne0")
+    assert_bit_equal(abi.compare("eq", x, 0.0), b(golden["edge_eq0"]), "edge eq0")
+    keep = (np.abs(x) <= 1e4) | np.isnan(x)
+    assert_close_ulp(abi.unary("silu", x[keep]), golden["edge_silu"][keep], what="edge silu")
+
+
+def test_random_cases_against_aten(abi, golden):
+    x, y = golden["rnd_x"], golden["rnd_y"]
+    assert_bit_equal(abi.binary("add", x, y), golden["rnd_add"], "add")
+    assert_bit_equal(abi.binary("add", x, y, alpha=-0.75), golden["rnd_add_alpha"], "add alpha")
+    assert_bit_equal(abi.binary("mul", x, y), golden["rnd_mul"], "mul")
+    assert_bit_equal(abi.unary("relu", x), golden["rnd_relu"], "relu")
+    assert_bit_equal(abi.unary("abs", x), golden["rnd_abs"], "abs")
+    assert_close_ulp(abi.unary("silu", x), golden["rnd_silu"], what="silu")
+    assert_close_ulp(abi.unary("gelu_erf", x), golden["rnd_gelu"], abs_floor=2e-6, what="gelu erf")
+    assert_close_ulp(abi.unary("gelu_tanh", x), golden["rnd_gelu_tanh"], abs_floor=2e-6, what="gelu tanh")
+    p, q = golden["rnd_p"], golden["rnd_q"]
+    m1, m2 = abi.compare("eq", p, q), abi.compare("ne", p, 0.0)
+    assert_bit_equal(m1, b(golden["rnd_eq"]), "eq")
+    assert_bit_equal(m2, b(golden["rnd_ne0"]), "ne")
+    assert_bit_equal(abi.bitwise_and(m1, m2), b(golden["rnd_and"]), "and")
+    assert_bit_equal(abi.bitwise_and(golden["rnd_i1"], golden["rnd_i2"]), golden["rnd_and_i32"], "and i32")
+    s = golden["lay_s"]
+    assert_bit_equal(abi.unary("relu", s.T), golden["lay_relu_t"], "relu transposed")
+    assert_bit_equal(abi.binary("add", s, golden["lay_row"]), golden["lay_add_row"], "add row")
+    assert_bit_equal(abi.binary("add", s, golden["lay_col"], alpha=3.0), golden["lay_add_col"], "add col")
+    assert_bit_equal(abi.binary("add", golden["lay_row"], golden["lay_col"]), golden["lay_add_outer"], "add outer")
+    src = golden["ms_src"]
+    for tag in ("001", "05", "099"):
+        mk = b(golden[f"ms_mask_{tag}"])
+        assert_bit_equal(abi.masked_select(src, mk), golden[f"ms_out_{tag}"], f"masked_select {tag}")
+        assert_bit_equal(abi.masked_select(src.T, mk.T), golden[f"ms_out_t_{tag}"], f"masked_select T {tag}")
+    assert_bit_equal(abi.masked_select(src, b(golden["ms_mask_row"])), golden["ms_out_row"], "row mask")
+    assert_bit_equal(abi.masked_select(src, b(golden["ms_mask_col"])), golden["ms_out_col"], "col mask")
+    assert_bit_equal(abi.masked_select(src[:, :1], b(golden["ms_mask_col"])), golden["ms_out_bsrc"], "bcast self")
+
+
+# ------------------------------------------------------------------------------------------
+# dense path: every size around the vector / chunk boundaries, aligned and misaligned
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("n", SIZES)
+@pytest.mark.parametrize("pad", [0, 1, 3])
+def test_dense_ops_all_sizes(abi, n, pad):
+    x, y = rnd(n, 10 + n), rnd(n, 20 + n)
+    assert_bit_equal(abi.binary("add", x, y, pad=pad), oracle.binary("add", x, y), "add")
+    assert abi.last_path() == ("none" if n == 0 else "dense" if pad == 0 else "strided32")
+    assert_bit_equal(abi.binary("add", x, y, alpha=0.3, pad=pad), oracle.binary("add", x, y, 0.3), "add alpha")
+    assert_bit_equal(abi.unary("relu", x, pad=pad), oracle.unary("relu", x), "relu")
+    assert_close_ulp(abi.unary("silu", x, pad=pad), oracle.unary("silu", x), what="silu")
+    assert_close_ulp(abi.unary("gelu_erf", x, pad=pad), oracle.unary("gelu_erf", x), abs_floor=2e-6, what="gelu")
+    p, q = small_ints(n, 30 + n), small_ints(n, 40 + n)
+    m1, m2 = abi.compare("eq", p, q, pad=pad), abi.compare("ne", p, 0.0, pad=pad)
+    assert_bit_equal(m1, oracle.compare("eq", p, q), "eq")
+    assert_bit_equal(m2, oracle.compare("ne", p, 0.0), "ne")
+    assert_bit_equal(abi.bitwise_and(m1, m2, pad=pad), oracle.bitwise_and(m1, m2), "and bool")
+
+
+@pytest.mark.parametrize("op", ["lt", "le", "gt", "ge", "eq", "ne"])
+def test_all_comparisons(abi, op):
+    p, q = small_ints(5001, 1), small_ints(5001, 2)
+    p[::97] = np.nan
+    assert_bit_equal(abi.compare(op, p, q), oracle.compare(op, p, q), op)
+    assert_bit_equal(abi.compare(op, p, 1.0), oracle.compare(op, p, 1.0), op + " scalar")
+
+
+@pytest.mark.parametrize("dtype", [np.uint8, np.int16, np.int32, np.int64])
+def test_integer_bitwise_and(abi, dtype):
+    rng = np.random.default_rng(3)
+    info = np.iinfo(dtype)
+    a = rng.integers(info.min, info.max, 10007, dtype=dtype)
+    c = rng.integers(info.min, info.max, 10007, dtype=dtype)
+    assert_bit_equal(abi.bitwise_and(a, c), a & c, "and int")
+    a2, c2 = a[:9999].reshape(99, 101), c[:9999].reshape(99, 101)
+    assert_bit_equal(abi.bitwise_and(a2.T, c2.T), a2.T & c2.T, "and int transposed")
+    assert_bit_equal(abi.bitwise_and(a2[:, ::3], c2[:, ::3]), a2[:, ::3] & c2[:, ::3], "and int sliced")
+
+
+# ------------------------------------------------------------------------------------------
+# strided / broadcast / permuted layouts
+# ------------------------------------------------------------------------------------------
+def test_true_transpose_uses_the_tile_kernel(abi):
+    for rows, cols in [(33, 65), (128, 96), (1000, 1031), (17, 4096)]:
+        x = rnd(rows * cols, rows).reshape(rows, cols)
+        got = abi.unary("relu", x.T)  # output dense in the transposed logical shape
+        assert abi.last_path() == "tile", (rows, cols)
+        assert_bit_equal(got, oracle.unary("relu", x.T), "relu transpose")
+        got = abi.unary("silu", x.T)
+        assert_close_ulp(got, oracle.unary("silu", x.T), what="silu transpose")
+        y = rnd(rows * cols, cols).reshape(cols, rows)
+        assert_bit_equal(abi.binary("add", x.T, y), oracle.binary("add", x.T, y), "add transposed + dense")
+        assert abi.last_path() == "tile"
+        p, q = small_ints(rows * cols, 5).reshape(rows, cols), small_ints(rows * cols, 6).reshape(cols, rows)
+        assert_bit_equal(abi.compare("eq", p.T, q), oracle.compare("eq", p.T, q), "eq transposed")
+        m = (p > 0)
+        assert_bit_equal(abi.bitwise_and(m.T, (q < 1)), oracle.bitwise_and(m.T, (q < 1)), "and transposed")
+        assert_bit_equal(abi.copy(x.T), np.ascontiguousarray(x.T), "copy transposed")
+        assert abi.last_path() == "tile"
+
+
+def test_transposed_output_layout(abi):
+    x = rnd(96 * 80, 7).reshape(96, 80)
+    out_like = np.empty((80, 96), np.float32).T  # logical [96,80], dense along dimension 0
+    got = abi.unary("relu", x, out_like=out_like)
+    assert abi.last_path() == "tile"
+    assert_bit_equal(got, oracle.unary("relu", x), "relu into transposed out")
+
+
+def test_slices_broadcasts_and_many_dims(abi):
+    x = rnd(64 * 130, 8).reshape(64, 130)
+    assert_bit_equal(abi.unary("relu", x[:, ::2]), oracle.unary("relu", x[:, ::2]), "stride-2 slice")
+    assert abi.last_path() == "strided32"
+    assert_bit_equal(abi.unary("relu", x[3:, 5:77]), oracle.unary("relu", x[3:, 5:77]), "offset window")
+    row, col = rnd(64, 9).reshape(64, 1), rnd(130, 10).reshape(1, 130)
+    assert_bit_equal(abi.binary("add", x, row), oracle.binary("add", x, row), "row broadcast")
+    assert_bit_equal(abi.binary("add", x, col, alpha=2.0), oracle.binary("add", x, col, 2.0), "col broadcast")
+    assert_bit_equal(abi.binary("add", row, col), oracle.binary("add", row, col), "outer broadcast")
+    scalar = rnd(1, 11).reshape(1, 1)
+    assert_bit_equal(abi.binary("mul", x, scalar), oracle.binary("mul", x, scalar), "scalar broadcast")
+    # negative strides take the 64-bit index path
+    assert_bit_equal(abi.unary("relu", x[::-1, ::-1]), oracle.unary("relu", x[::-1, ::-1]), "flipped")
+    assert abi.last_path() == "strided64"
+    assert_bit_equal(abi.copy(x[::-1, ::3]), np.ascontiguousarray(x[::-1, ::3]), "copy flipped slice")
+    for ndim in range(1, 9):
+        shape = [3, 2, 4, 2, 3, 2, 2, 3][:ndim]
+        base = rnd(int(np.prod(shape)), 100 + ndim).reshape(shape)
+        perm = list(reversed(range(ndim)))
+        v = base.transpose(perm)
+        assert_bit_equal(abi.unary("relu", v), oracle.unary("relu", v), f"permuted {ndim}-d")
+        w = rnd(int(np.prod(shape)), 200 + ndim).reshape(v.shape)
+        assert_bit_equal(abi.binary("add", v, w[..., ::1]), oracle.binary("add", v, w), f"permuted add {ndim}-d")
+        assert_bit_equal(abi.copy(v), np.ascontiguousarray(v), f"permuted copy {ndim}-d")
+    with pytest.raises(abi.TwgError):
+        abi.unary("relu", np.zeros((1,) * 9, np.float32))
+
+
+def test_copy_every_element_size(abi):
+    rng = np.random.default_rng(12)
+    for dtype in (np.uint8, np.uint16, np.float32, np.float64, np.complex128):
+        a = rng.integers(0, 255, 50 * 70 * np.dtype(dtype).itemsize, dtype=np.uint8).view(dtype).reshape(50, 70)
+        for v in (a.T, a[:, ::2], a[::3, 1:], a):
+            assert_bit_equal(abi.copy(v).view(np.uint8), np.ascontiguousarray(v).view(np.uint8), f"copy {dtype}")
+
+
+def test_byte_operands_far_apart_use_64bit_offsets(abi):
+    # a bool view whose rows are 2^30 bytes apart: offsets no longer fit 32 bits
+    big = np.zeros((1 << 31) + 64, np.uint8)
+    rng = np.random.default_rng(13)
+    view = np.lib.stride_tricks.as_strided(big, (3, 40), (1 << 30, 1))
+    view[...] = rng.integers(0, 2, (3, 40))
+    other = rng.integers(0, 2, (3, 40)).astype(np.uint8)
+    got = abi.bitwise_and(view.view(np.bool_), other.view(np.bool_))
+    assert abi.last_path() == "strided64"
+    assert_bit_equal(got, (view & other).view(np.bool_), "far-apart rows")
+
+
+# ------------------------------------------------------------------------------------------
+# masked_select
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("n", [0, 1, 5, 4095, 4096, 4097, 3 * 4096 + 17, 1 << 20, (1 << 22) + 3])
+@pytest.mark.parametrize("p", [0.0, 0.01, 0.5, 0.99, 1.0])
+def test_masked_select_dense(abi, n, p):
+    x = rnd(n, 50 + n)
+    mask = np.random.default_rng(60 + n).random(n) < p
+    got = abi.masked_select(x, mask)
+    assert_bit_equal(got, oracle.masked_select(x, mask), f"masked_select n={n} p={p}")
+    if n:
+        assert abi.last_path() == "dense"
+
+
+@pytest.mark.parametrize("pad", [1, 2, 3])
+def test_masked_select_misaligned(abi, pad):
+    n = 5 * 4096 + 123
+    x = rnd(n, 70)
+    mask = np.random.default_rng(71).random(n) < 0.4
+    assert_bit_equal(abi.masked_select(x, mask, pad=pad), oracle.masked_select(x, mask), "misaligned")
+    assert abi.last_path() == "strided32"
+
+
+def test_masked_select_broadcast_and_strided(abi):
+    rng = np.random.default_rng(72)
+    x = rnd(300 * 517, 73).reshape(300, 517)
+    full = rng.random((300, 517)) < 0.5
+    rowm = rng.random((300, 1)) < 0.5
+    colm = rng.random((1, 517)) < 0.5
+    assert_bit_equal(abi.masked_select(x, rowm), oracle.masked_select(x, rowm), "row mask")
+    assert_bit_equal(abi.masked_select(x, colm), oracle.masked_select(x, colm), "col mask")
+    assert_bit_equal(abi.masked_select(x.T, full.T), oracle.masked_select(x.T, full.T), "both transposed")
+    assert_bit_equal(abi.masked_select(x.T, np.ascontiguousarray(full.T)), oracle.masked_select(x.T, full.T), "self transposed")
+    assert_bit_equal(abi.masked_select(x[:, :1], colm), oracle.masked_select(x[:, :1], colm), "self broadcast")
+    assert_bit_equal(abi.masked_select(x[::2, ::3], full[::2, ::3]), oracle.masked_select(x[::2, ::3], full[::2, ::3]), "sliced")
+    x4 = rnd(6 * 5 * 7 * 9, 74).reshape(6, 5, 7, 9)
+    m4 = rng.random((6, 1, 7, 1)) < 0.5
+    assert_bit_equal(abi.masked_select(x4, m4), oracle.masked_select(x4, m4), "4-d broadcast mask")
+    with pytest.raises(RuntimeError):
+        abi.masked_select(x, np.ones(x.shape, np.uint8))
+
+
+def test_masked_select_nonzero_bytes_count_as_true(abi):
+    x = rnd(9000, 75)
+    raw = np.random.default_rng(76).integers(0, 256, 9000).astype(np.uint8)
+    raw[::3] = 0
+    got = abi.masked_select(x, raw.view(np.bool_))
+    assert_bit_equal(got, x[raw != 0], "non 0/1 mask bytes")
+
+
+def test_masked_select_bounded_wait_reports_timeout(abi):
+    """The look-back wait must run out and report, never hang: tile 0 withholds its count."""
+    n = 64 * 4096
+    x = rnd(n, 77)
+    mask = np.random.default_rng(78).random(n) < 0.5
+    try:
+        abi.check(abi.lib().twg_masked_select_set_poll_budget(-200))
+        _, status = abi.masked_select(x, mask, return_status=True)
+        assert status == abi.TWG_ERR_TIMEOUT
+        with pytest.raises(abi.TwgError):
+            abi.masked_select(x, mask)
+    finally:
+        abi.check(abi.lib().twg_masked_select_set_poll_budget(0))
+    # the context is still usable and the next call is correct
+    assert_bit_equal(abi.masked_select(x, mask), oracle.masked_select(x, mask), "after timeout")
+
+
+def test_masked_select_workspace_is_validated(abi):
+    import ctypes
+    x = abi.DeviceArray(rnd(10000, 79))
+    m = abi.DeviceArray(np.ones(10000, np.uint8))
+    d = abi.make_desc((10000,), [x, m])
+    out, res, ws = abi.DeviceBuffer(40000), abi.DeviceBuffer(16), abi.DeviceBuffer(256)
+    rc = abi.lib().twg_masked_select_f32(ctypes.byref(d), x.ptr, m.ptr, out.ptr, res.ptr, ws.ptr, 8, None)
+    assert rc == abi.TWG_ERR_INVALID
+    assert b"workspace" in abi.lib().twg_last_error()
+
+
+# ------------------------------------------------------------------------------------------
+# fused programs
+# ------------------------------------------------------------------------------------------
+def test_fused_chain_ahead_of_time_kernel(abi, golden):
+    a, bb, c = golden["chain_a"], golden["chain_b"], golden["chain_c"]
+    (m,), kind = abi.fused(abi.CHAIN_MASK_PROGRAM, [a, bb, c], [np.bool_])
+    assert kind == "aot"
+    assert_bit_equal(m, oracle.chain_mask(a, bb, c), "chain mask vs oracle")
+    assert_bit_equal(m, b(golden["chain_m"]), "chain mask vs ATen")
+    assert_bit_equal(abi.masked_select(a, m), golden["chain_sel"], "chain select")
+    n = 1 << 20
+    a, bb, c = rnd(n, 80, -3, 3), rnd(n, 81, -3, 3), rnd(n, 82, -3, 3)
+    a[::5] = 0.0
+    (m,), _ = abi.fused(abi.CHAIN_MASK_PROGRAM, [a, bb, c], [np.bool_])
+    y_ref, m_ref = oracle.chain_mask(a, bb, c, want_y=True)
+    # silu may differ by an ulp, which can flip relu's "exactly zero" only next to zero
+    diff = m != m_ref
+    assert diff.sum() <= 4
+    assert np.all(np.abs(y_ref[diff]) < 1e-6)
+
+
+def test_fused_program_compiled_at_run_time(abi):
+    F = abi
+    prog = [(F.F_INPUT_F32, 0, 0, 0.0), (F.F_INPUT_F32, 1, 0, 0.0), (F.F_GELU_ERF, 0, 0, 0.0), (F.F_MUL, 2, 1, 0.0),
+            (F.F_CONST_F32, 0, 0, 0.5), (F.F_GT, 3, 4, 0.0), (F.F_ABS, 3, 0, 0.0), (F.F_OUTPUT, 6, 0, 0.0),
+            (F.F_OUTPUT, 5, 1, 0.0)]
+    for shape_x, shape_y in [((100003,), (100003,)), ((257, 130), (257, 1)), ((64, 96), (96, 64))]:
+        x = rnd(int(np.prod(shape_x)), 83).reshape(shape_x)
+        y = rnd(int(np.prod(shape_y)), 84).reshape(shape_y)
+        if shape_y == (96, 64):
+            y = y.T
+        (val, flag), kind = abi.fused(prog, [x, y], [np.float32, np.bool_])
+        assert kind == "nvrtc"
+        g = oracle.unary("gelu_erf", x)
+        ref = oracle.binary("mul", g, np.broadcast_to(y, x.shape).copy())
+        # the product is computed from this build's gelu, so compare against what it implies
+        got_g = abi.unary("gelu_erf", x)
+        exact = oracle.unary("abs", oracle.binary("mul", got_g, np.broadcast_to(y, x.shape).copy()))
+        assert_bit_equal(val, exact, "fused abs(gelu*y)")
+        assert_close_ulp(val, np.abs(ref), abs_floor=2e-5, what="fused vs oracle")
+        assert_bit_equal(flag, oracle.compare("gt", oracle.binary("mul", got_g, np.broadcast_to(y, x.shape).copy()), 0.5), "fused flag")
+
+
+def test_fused_rejects_malformed_programs(abi):
+    F = abi
+    with pytest.raises(abi.TwgError):
+        abi.fused_compile([(F.F_INPUT_F32, 0, 0, 0.0), (F.F_AND, 0, 0, 0.0), (F.F_OUTPUT, 1, 0, 0.0)])
+    with pytest.raises(abi.TwgError):
+        abi.fused_compile([(F.F_INPUT_F32, 0, 0, 0.0), (F.F_RELU, 5, 0, 0.0), (F.F_OUTPUT, 1, 0, 0.0)])
+    with pytest.raises(abi.TwgError):
+        abi.fused_compile([(F.F_INPUT_F32, 0, 0, 0.0), (F.F_RELU, 0, 0, 0.0)])
+
+
+# ------------------------------------------------------------------------------------------
+# allocator, copies, events
+# ------------------------------------------------------------------------------------------
+def test_allocator_caches_splits_trims_and_reports(abi):
+    import ctypes
+    L = abi.lib()
+
+    def stats():
+        s = abi.MemStats()
+        abi.check(L.twg_memory_stats(0, ctypes.byref(s)))
+        return s
+
+    abi.check(L.twg_empty_cache(0))
+    s0 = stats()
+    a = abi.DeviceBuffer(64 << 20)
+    s1 = stats()
+    assert s1.num_device_mallocs == s0.num_device_mallocs + 1
+    assert s1.allocated_bytes - s0.allocated_bytes == 64 << 20
+    ptr = a.ptr
+    a.free()
+    a2 = abi.DeviceBuffer(64 << 20)          # served from the cache, same block
+    s2 = stats()
+    assert a2.ptr == ptr and s2.num_device_mallocs == s1.num_device_mallocs
+    assert s2.num_cache_hits == s1.num_cache_hits + 1
+    abi.check(L.twg_trim(a2.ptr, 8 << 20))   # give 56 MiB back
+    s3 = stats()
+    assert s2.allocated_bytes - s3.allocated_bytes == 56 << 20
+    tail = abi.DeviceBuffer(40 << 20)        # fits in the returned tail: no new cudaMalloc
+    assert stats().num_device_mallocs == s2.num_device_mallocs
+    assert tail.ptr == ptr + (8 << 20)
+    small = [abi.DeviceBuffer(1000) for _ in range(100)]  # carved from one 2 MiB segment
+    assert stats().num_device_mallocs <= s2.num_device_mallocs + 1
+    assert all(sm.ptr % 512 == 0 for sm in small)
+    for sm in small:
+        sm.free()
+    tail.free(); a2.free()
+    abi.check(L.twg_empty_cache(0))
+    s4 = stats()
+    assert s4.reserved_bytes <= s0.reserved_bytes
+    assert abi.DeviceBuffer(0).ptr == 0
+    assert L.twg_free(12345) == abi.TWG_ERR_INVALID
+
+
+def test_allocator_budget_injects_out_of_memory(abi):
+    L = abi.lib()
+    import ctypes
+    abi.check(L.twg_empty_cache(0))
+    s = abi.MemStats()
+    abi.check(L.twg_memory_stats(0, ctypes.byref(s)))
+    abi.check(L.twg_set_memory_budget(0, s.reserved_bytes + (32 << 20)))
+    try:
+        with pytest.raises(abi.TwgError) as e:
+            abi.DeviceBuffer(256 << 20)
+        assert e.value.code == abi.TWG_ERR_OOM
+        ok = abi.DeviceBuffer(4 << 20)       # still serviceable below the cap
+        ok.free()
+    finally:
+        abi.check(L.twg_set_memory_budget(0, 0))
+    abi.DeviceBuffer(256 << 20).free()
+
+
+def test_blocks_used_on_a_second_stream_wait_for_it(abi):
+    import ctypes
+    L = abi.lib()
+    s2 = ctypes.c_void_p()
+    abi.check(L.twg_get_stream(0, 2, ctypes.byref(s2)))
+    buf = abi.DeviceBuffer(48 << 20)
+    ptr = buf.ptr
+    abi.check(L.twg_record_stream(buf.ptr, s2))
+    abi.check(L.twg_memset(buf.ptr, 1, 48 << 20, s2))
+    buf.free()                                # deferred behind an event on the second stream
+    abi.check(L.twg_stream_sync(s2))
+    again = abi.DeviceBuffer(48 << 20)        # after the event completed the block is reusable
+    assert again.ptr == ptr
+    again.free()
+
+
+@pytest.mark.parametrize("nbytes", [1, 4097, (16 << 20) - 1, (16 << 20) + 5, (40 << 20) + 3])
+def test_pageable_and_pinned_round_trips(abi, nbytes):
+    import ctypes
+    L = abi.lib()
+    host = np.random.default_rng(nbytes % 1000).integers(0, 256, nbytes, dtype=np.uint8)
+    dev = abi.DeviceBuffer(nbytes)
+    dev.upload(host)
+    assert np.array_equal(dev.download(np.uint8, nbytes), host)
+    pinned = ctypes.c_void_p()
+    abi.check(L.twg_host_alloc_pinned(ctypes.byref(pinned), nbytes))
+    try:
+        view = np.ctypeslib.as_array(ctypes.cast(pinned, ctypes.POINTER(ctypes.c_uint8)), shape=(nbytes,))
+        view[:] = host[::-1]
+        abi.check(L.twg_memcpy_h2d(dev.ptr, pinned, nbytes, None))
+        abi.check(L.twg_stream_sync(None))
+        view[:] = 0
+        abi.check(L.twg_memcpy_d2h(pinned, dev.ptr, nbytes, None, 1))
+        assert np.array_equal(view, host[::-1])
+    finally:
+        abi.check(L.twg_host_free_pinned(pinned))
+
+
+def test_events_and_launch_accounting(abi):
+    import ctypes
+    L = abi.lib()
+    e0, e1 = ctypes.c_void_p(), ctypes.c_void_p()
+    abi.check(L.twg_event_create(ctypes.byref(e0)))
+    abi.check(L.twg_event_create(ctypes.byref(e1)))
+    x = rnd(1 << 20, 90)
+    L.twg_reset_launch_count()
+    abi.check(L.twg_event_record(e0, None))
+    abi.unary("relu", x)
+    abi.check(L.twg_event_record(e1, None))
+    abi.check(L.twg_event_sync(e1))
+    ms = ctypes.c_float()
+    abi.check(L.twg_event_elapsed_ms(e0, e1, ctypes.byref(ms)))
+    assert ms.value > 0
+    assert L.twg_launch_count() == 1
+    done = ctypes.c_int()
+    abi.check(L.twg_event_query(e1, ctypes.byref(done)))
+    assert done.value == 1
+    abi.check(L.twg_event_destroy(e0)); abi.check(L.twg_event_destroy(e1))

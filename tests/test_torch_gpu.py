@@ -1,0 +1,276 @@
+"""The drop-in surface on a real GPU: `import torch_webgpu`, `device="webgpu"`, the registered ATen
+ops, `torch.compile(backend=webgpu_backend)`.  The first block restates the reference's own tests
+(tests/ops/test_add.py, test_gelu.py, test_silu.py, tests/test_dev.py, tests/test_compile_dev.py);
+the rest runs the benchmark configurations at full size against the PyTorch CPU kernels, which are
+the reference's implementation of its fallback ops and the oracle of all its tests.
+"""
+from __future__ import annotations
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def backend():
+    import torch_webgpu
+    assert torch.webgpu.is_available(), "no CUDA device behind the webgpu backend"
+    return torch_webgpu
+
+
+def close(got: torch.Tensor, ref: torch.Tensor, abs_floor: float = 0.0) -> None:
+    """|got-ref| <= max(2 ulp(ref), 1e-6 |ref|, abs_floor), evaluated in float64 with torch."""
+    assert got.shape == ref.shape and got.dtype == ref.dtype == torch.float32
+    for g, r in zip(got.reshape(-1).split(1 << 24), ref.reshape(-1).split(1 << 24)):
+        finite = torch.isfinite(r)
+        assert torch.equal(torch.isnan(g), torch.isnan(r))
+        r64, g64 = r[finite].double(), g[finite].double()
+        ulp = (torch.nextafter(r[finite].abs(), torch.tensor(float("inf"))) - r[finite].abs()).double()
+        tol = torch.maximum(torch.maximum(2 * ulp, 1e-6 * r64.abs()), torch.tensor(abs_floor, dtype=torch.float64))
+        bad = (g64 - r64).abs() > tol
+        assert not bool(bad.any()), f"{int(bad.sum())} elements outside tolerance, worst {float(((g64 - r64).abs() - tol).max()):.3e}"
+
+
+# ------------------------------------------------------------------------------------------
+# the reference's tests, restated
+# ------------------------------------------------------------------------------------------
+def test_add_happy_path():  # tests/ops/test_add.py:5-10
+    a = torch.tensor([-1.5, 2.7, 1.0, 2.0], device="webgpu")
+    b = torch.tensor([-1.0, 0.9, 1.1, -2.1], device="webgpu")
+    result = a + b
+    expected = torch.tensor([-2.5, 3.6, 2.1, -0.1], device="cpu")
+    assert result.device.type == "webgpu"
+    assert torch.allclose(result.to("cpu"), expected)
+
+
+@pytest.mark.parametrize("values", [[-1.0, 0.0, 1.0, 2.0], [[0.5, -0.5], [1.5, -1.5]], [2.0], [0.0]])
+def test_gelu_and_silu_reference_cases(values):  # tests/ops/test_gelu.py, tests/ops/test_silu.py
+    cpu = torch.tensor(values, dtype=torch.float32)
+    dev = cpu.to(device="webgpu")
+    assert torch.allclose(F.gelu(dev).to("cpu"), F.gelu(cpu), atol=1e-3)   # the reference's bar
+    assert torch.allclose(F.silu(dev).to("cpu"), F.silu(cpu), atol=1e-6)
+    close(F.gelu(dev).cpu(), F.gelu(cpu), abs_floor=2e-6)                    # this build's bar
+    close(F.gelu(dev, approximate="tanh").cpu(), F.gelu(cpu, approximate="tanh"), abs_floor=2e-6)
+    close(F.silu(dev).cpu(), F.silu(cpu))
+
+
+def test_empty_tensors_and_dtype_errors():  # disabled in the reference: segfault / no clean error
+    e = torch.tensor([], dtype=torch.float32).to("webgpu")
+    assert F.gelu(e).cpu().numel() == 0 and F.silu(e).cpu().numel() == 0 and (e + e).cpu().numel() == 0
+    assert torch.masked_select(e, e > 0).cpu().numel() == 0
+    i = torch.tensor([1, 2, 3], dtype=torch.int32).to("webgpu")
+    with pytest.raises(RuntimeError):
+        F.gelu(i)
+    with pytest.raises(RuntimeError):
+        F.silu(i)
+    with pytest.raises(RuntimeError):
+        torch.masked_select(torch.ones(3, device="webgpu"), torch.ones(3, device="webgpu"))
+
+
+def test_compile_add_relu_flow():  # tests/test_dev.py:6-20
+    from torch_webgpu import webgpu_backend
+    from torch_webgpu.compiler import webgpu_compiler as wc
+
+    @torch.compile(backend=webgpu_backend)
+    def fn(x):
+        a = torch.tensor([-1.5, 2.7, 1.0, 2.0], device="webgpu")
+        b = torch.tensor([-1.0, 0.9, 1.1, -2.1], device="webgpu")
+        result = a + b
+        result = torch.relu(result)
+        return result.to("cpu")
+
+    result = fn(None)
+    assert torch.allclose(result, torch.tensor([0, 3.6, 2.1, 0]))
+    assert wc.last_compile_report["fused_kernels"] == 1 and wc.last_compile_report["kinds"] == ["aot"]
+
+    @torch.compile(backend=webgpu_backend)
+    def fn2(x):  # tests/test_compile_dev.py:6-8, which the reference cannot compile
+        return x + x
+
+    assert torch.equal(fn2(torch.tensor([2.0, 3.0, 4.0], device="webgpu")).cpu(), torch.tensor([4.0, 6.0, 8.0]))
+
+
+def test_custom_ops_of_the_reference_runtime():  # csrc/ops/webgpu_ops.cpp:47-52
+    buf = torch.ops.webgpu.create_buffer([2, 3], [3, 1], torch.float32)
+    assert buf.device.type == "webgpu" and buf.shape == (2, 3)
+    src = torch.arange(6, dtype=torch.float32).reshape(2, 3) - 2.5
+    torch.ops.webgpu.write_buffer(buf, src)
+    assert torch.equal(buf.cpu(), src)
+    out = torch.ops.webgpu.fused_add_relu(buf, buf)
+    assert torch.equal(out.cpu(), torch.relu(src + src))
+
+
+# ------------------------------------------------------------------------------------------
+# copies and views
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bool, torch.int64, torch.float64, torch.uint8, torch.bfloat16])
+def test_round_trip_every_dtype(dtype):
+    g = torch.Generator().manual_seed(1)
+    x = (torch.randn(7, 9, generator=g) * 3)
+    x = (x > 0) if dtype == torch.bool else x.to(dtype)
+    d = x.to("webgpu")
+    assert torch.equal(d.cpu(), x)
+    assert torch.equal(d.t().cpu(), x.t())                       # strided read-back
+    assert torch.equal(d[2:, 1::2].contiguous().cpu(), x[2:, 1::2])
+    assert torch.equal(d[3:].cpu(), x[3:])                       # storage offset honoured
+    dst = torch.empty(9, 7, dtype=x.dtype, device="webgpu").t()  # upload into a non-contiguous tensor
+    dst.copy_(x)
+    assert torch.equal(dst.cpu(), x)
+    assert torch.equal(d.clone().cpu(), x) and torch.equal(d.reshape(9, 7).cpu(), x.reshape(9, 7))
+    assert torch.equal(d.t().reshape(7, 9).cpu(), x.t().reshape(7, 9))
+
+
+def test_scalars_inplace_and_out_variants():
+    x = torch.randn(1000, generator=torch.Generator().manual_seed(2))
+    d = x.to("webgpu")
+    assert torch.equal((d + 2.0).cpu(), x + 2.0)
+    assert torch.equal(torch.add(d, d, alpha=2.5).cpu(), torch.add(x, x, alpha=2.5))
+    assert torch.equal((d * d).cpu(), x * x) and torch.equal(torch.abs(d).cpu(), torch.abs(x))
+    assert torch.equal(torch.eq(d, 0.5).cpu(), torch.eq(x, 0.5)) and torch.equal((d != 0).cpu(), x != 0)
+    assert torch.equal((d < 0.25).cpu(), x < 0.25)
+    out = torch.empty(1000, device="webgpu")
+    torch.ops.aten.relu.out(d, out=out)
+    assert torch.equal(out.cpu(), torch.relu(x))
+    e = d.clone()
+    e.relu_()
+    e.add_(d)
+    assert torch.equal(e.cpu(), torch.relu(x) + x)
+    assert float(d[3].item()) == float(x[3])
+    z = torch.zeros(5, device="webgpu")
+    assert torch.equal(z.cpu(), torch.zeros(5))
+    m = torch.empty(0, dtype=torch.float32, device="webgpu")
+    torch.masked_select(d, d > 0, out=m)
+    assert torch.equal(m.cpu(), torch.masked_select(x, x > 0))
+
+
+def test_allocator_statistics_through_the_device_module():
+    torch.webgpu.synchronize()
+    torch.webgpu.empty_cache()
+    before = torch.webgpu.memory_stats()
+    t = torch.empty(64 << 20, dtype=torch.uint8, device="webgpu")
+    mid = torch.webgpu.memory_stats()
+    assert mid["allocated_bytes"] - before["allocated_bytes"] == 64 << 20
+    del t
+    after = torch.webgpu.memory_stats()
+    assert after["allocated_bytes"] == before["allocated_bytes"]
+    assert after["reserved_bytes"] >= mid["reserved_bytes"] - 0      # cached, not returned to the driver
+    t2 = torch.empty(64 << 20, dtype=torch.uint8, device="webgpu")
+    assert torch.webgpu.memory_stats()["num_device_mallocs"] == mid["num_device_mallocs"]
+    del t2
+    assert torch.webgpu.max_memory_allocated() >= 64 << 20
+
+
+# ------------------------------------------------------------------------------------------
+# the benchmark configurations at full size
+# ------------------------------------------------------------------------------------------
+def test_config1_add_4096():
+    g = torch.Generator().manual_seed(0)
+    a, b = torch.randn(4096, 4096, generator=g), torch.randn(4096, 4096, generator=g)
+    out = torch.add(a.to("webgpu"), b.to("webgpu")).cpu()       # result copied back through _copy_from
+    assert torch.equal(out, torch.add(a, b))
+
+
+def test_config2_activations():
+    g = torch.Generator().manual_seed(1)
+    x = torch.rand(2 ** 28, generator=g) * 16 - 8
+    d = x.to("webgpu")
+    assert torch.equal(torch.relu(d).cpu(), torch.relu(x))
+    close(F.silu(d).cpu(), F.silu(x))
+    close(F.gelu(d, approximate="none").cpu(), F.gelu(x, approximate="none"), abs_floor=2e-6)
+    # non-contiguous view: transpose of [16384,16384]
+    xt, dt = x.view(16384, 16384).t(), d.view(16384, 16384).t()
+    r = torch.relu(dt)
+    assert r.stride() == (1, 16384)                              # empty_like keeps the layout
+    assert torch.equal(r.cpu(), torch.relu(xt))
+    # a true transpose: transposed input into a contiguous output (tile kernel)
+    out = torch.empty(16384, 16384, device="webgpu")
+    torch.ops.aten.relu.out(dt, out=out)
+    assert torch_last_path() == "tile"
+    assert torch.equal(out.cpu(), torch.relu(xt).contiguous())
+    torch.ops.aten.silu.out(dt, out=out)
+    close(out.cpu(), F.silu(xt).contiguous())
+    torch.ops.aten.gelu.out(dt, approximate="none", out=out)
+    close(out.cpu(), F.gelu(xt).contiguous(), abs_floor=2e-6)
+    del out
+    # stride-2 read
+    s, ds = x.view(16384, 16384)[:, ::2], d.view(16384, 16384)[:, ::2]
+    assert torch.equal(torch.relu(ds).cpu(), torch.relu(s))
+    assert torch_last_path() == "strided32"
+
+
+def torch_last_path() -> str:
+    import torch_webgpu
+    return {0: "none", 1: "dense", 2: "tile", 3: "strided32", 4: "strided64"}[torch_webgpu._C.last_launch_path()]
+
+
+def test_config3_comparisons_and_masks():
+    g = torch.Generator().manual_seed(2)
+    p = torch.randint(-2, 3, (8192, 8192), generator=g).float()
+    q = torch.randint(-2, 3, (8192, 8192), generator=g).float()
+    dp, dq = p.to("webgpu"), q.to("webgpu")
+    m1, m2 = torch.eq(dp, dq), torch.ne(dp, 0.0)
+    assert m1.dtype == torch.bool and m1.device.type == "webgpu"
+    assert torch.equal(m1.cpu(), torch.eq(p, q)) and torch.equal(m2.cpu(), torch.ne(p, 0.0))
+    both = torch.bitwise_and(m1, m2)
+    assert torch.equal(both.cpu(), torch.bitwise_and(torch.eq(p, q), torch.ne(p, 0.0)))
+    assert abs(float(m1.cpu().float().mean()) - 0.2) < 0.01
+
+
+def test_config4_masked_select():
+    g = torch.Generator().manual_seed(3)
+    src = torch.randn(16384, 16384, generator=g)
+    d = src.to("webgpu")
+    for p in (0.01, 0.5, 0.99):
+        mask = torch.rand(16384, 16384, generator=g) < p
+        got = torch.masked_select(d, mask.to("webgpu"))
+        ref = torch.masked_select(src, mask)
+        assert got.dim() == 1 and got.shape == ref.shape
+        assert torch.equal(got.cpu(), ref), f"p={p}"
+        del got, ref, mask
+    mask_b = torch.rand(16384, 1, generator=g) < 0.5
+    got = torch.masked_select(d, mask_b.to("webgpu"))
+    assert torch.equal(got.cpu(), torch.masked_select(src, mask_b))
+
+
+def test_config5_compiled_chain():
+    from torch_webgpu import webgpu_backend
+    from torch_webgpu.compiler import webgpu_compiler as wc
+
+    def chain(a, b, c):
+        y = torch.relu(F.silu(a + b) + c)
+        m = torch.bitwise_and(torch.eq(y, 0), torch.ne(a, 0))
+        return torch.masked_select(a, m), m
+
+    g = torch.Generator().manual_seed(4)
+    a, b, c = (torch.randn(8, 4096, 4096, generator=g) for _ in range(3))   # 8 of the 64 batches
+    da, db, dc = a.to("webgpu"), b.to("webgpu"), c.to("webgpu")
+    import torch_webgpu
+    torch_webgpu._C.reset_launch_count()
+    sel, m = torch.compile(chain, backend=webgpu_backend)(da, db, dc)
+    assert wc.last_compile_report["fused_kernels"] == 1 and wc.last_compile_report["kinds"] == ["aot"]
+    assert torch_webgpu._C.launch_count() == 2                   # one fused kernel + one compaction
+    y_ref = torch.relu(F.silu(a + b) + c)
+    m_ref = torch.bitwise_and(torch.eq(y_ref, 0), torch.ne(a, 0))
+    m_cpu = m.cpu()
+    # silu may differ from the CPU kernel by an ulp; that can only change "y == 0" where the
+    # pre-relu sum is within rounding of zero
+    flipped = m_cpu != m_ref
+    assert int(flipped.sum()) <= 64
+    pre = (F.silu(a + b) + c)[flipped]
+    assert bool((pre.abs() < 1e-6).all())
+    # given the mask, the selection is exact
+    assert torch.equal(sel.cpu(), torch.masked_select(a, m_cpu))
+    # and eager mode gives the same mask as the fused kernel
+    y = torch.relu(F.silu(da + db) + dc)
+    assert torch.equal(torch.bitwise_and(torch.eq(y, 0), torch.ne(da, 0)).cpu(), m_cpu)
+
+
+@pytest.mark.skipif("torch.cuda.device_count() < 2")
+def test_second_device():
+    x = torch.randn(1 << 20)
+    d1 = x.to("webgpu:1")
+    assert d1.device.index == 1
+    assert torch.equal(torch.relu(d1).cpu(), torch.relu(x))
+    assert torch.equal(d1.to("webgpu:0").cpu(), x)

@@ -28,7 +28,9 @@ BUILD = ROOT / "build"
 INCLUDE = REPO / "include"
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-CXX = os.environ.get("CXX", "g++")
+# The system compiler, not $CXX: a wrapper compiler exported by the environment produced an
+# extension whose C++ exceptions could not be caught (every TORCH_CHECK became a crash).
+CXX = os.environ.get("TWG_CXX", "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

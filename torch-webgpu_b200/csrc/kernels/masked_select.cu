@@ -55,8 +55,12 @@ struct MsShared {
 // elements in all earlier tiles, publishes the inclusive prefix and returns the exclusive one.
 __device__ __forceinline__ i64 lookback(i64 tile, u32 tile_total, u64* desc, i64* result, i64 poll_budget) {
   const int lane = threadIdx.x & 31;
+  // A negative budget is the test hook "tile 0 never publishes": every wait that depends on it
+  // must run out after |budget| polls and report TWG_ERR_TIMEOUT instead of hanging.
+  const bool withhold_first = poll_budget < 0;
+  if (withhold_first) poll_budget = -poll_budget;
   if (tile == 0) {
-    if (lane == 0) st_relaxed_u64(desc, kMsPrefix | (u64)tile_total);
+    if (lane == 0 && !withhold_first) st_relaxed_u64(desc, kMsPrefix | (u64)tile_total);
     return 0;
   }
   if (lane == 0) st_relaxed_u64(desc + tile, kMsAggregate | (u64)tile_total);
@@ -253,7 +257,7 @@ extern "C" size_t twg_masked_select_workspace_bytes(int64_t numel) {
 }
 
 extern "C" int twg_masked_select_set_poll_budget(int64_t polls) {
-  g_poll_budget.store(polls > 0 ? polls : 4000000);
+  g_poll_budget.store(polls != 0 ? polls : 4000000);
   return TWG_OK;
 }
 
