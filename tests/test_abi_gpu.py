@@ -58,9 +58,9 @@ def test_known_answers_of_the_reference_tests(abi, golden):
 
 def test_edge_values_against_aten(abi, golden):
     x, y = golden["edge_x"], golden["edge_y"]
-    assert_bit_equal(abi.binary("add", x, y), golden["edge_add"], "edge add")
-    assert_bit_equal(abi.binary("add", x, y, alpha=2.5), golden["edge_add_alpha"], "edge add alpha")
-    assert_bit_equal(abi.unary("relu", x), golden["edge_relu"], "edge relu")
+    assert_bit_equal(abi.binary("add", x, y), golden["edge_add"], "edge add", any_nan=True)
+    assert_bit_equal(abi.binary("add", x, y, alpha=2.5), golden["edge_add_alpha"], "edge add alpha", any_nan=True)
+    assert_bit_equal(abi.unary("relu", x), golden["edge_relu"], "edge relu")  # relu passes NaN through untouched
     assert_bit_equal(abi.compare("eq", x, y), b(golden["edge_eq"]), "edge eq")
     assert_bit_equal(abi.compare("ne", x, 0.0), b(golden["edge_ne0"]), "edge ne0")
     assert_bit_equal(abi.compare("eq", x, 0.0), b(golden["edge_eq0"]), "edge eq0")
@@ -207,9 +207,9 @@ def test_copy_every_element_size(abi):
 
 def test_byte_operands_far_apart_use_64bit_offsets(abi):
     # a bool view whose rows are 2^30 bytes apart: offsets no longer fit 32 bits
-    big = np.zeros((1 << 31) + 64, np.uint8)
+    big = np.zeros(3 << 30, np.uint8)
     rng = np.random.default_rng(13)
-    view = np.lib.stride_tricks.as_strided(big, (3, 40), (1 << 30, 1))
+    view = big.reshape(3, 1 << 30)[:, :40]
     view[...] = rng.integers(0, 2, (3, 40))
     other = rng.integers(0, 2, (3, 40)).astype(np.uint8)
     got = abi.bitwise_and(view.view(np.bool_), other.view(np.bool_))

@@ -13,10 +13,18 @@ def bits(a: np.ndarray) -> np.ndarray:
     return a
 
 
-def assert_bit_equal(got: np.ndarray, ref: np.ndarray, what: str = "") -> None:
+def assert_bit_equal(got: np.ndarray, ref: np.ndarray, what: str = "", *, any_nan: bool = False) -> None:
+    """Bit-for-bit equality.  any_nan=True is for results of floating-point ARITHMETIC: which NaN
+    bit pattern an operation produces is a property of the executing hardware (x86 propagates an
+    input NaN's payload, NVIDIA GPUs return the canonical 0x7fffffff), so there every NaN matches
+    every NaN; everything else, including the sign of zero, is still compared bit for bit."""
     got = np.asarray(got)
     ref = np.asarray(ref)
     assert got.shape == ref.shape, f"{what}: shape {got.shape} != {ref.shape}"
+    if any_nan and got.dtype == np.float32:
+        assert np.array_equal(np.isnan(got), np.isnan(ref)), f"{what}: NaN positions differ"
+        got = np.where(np.isnan(got), np.float32(0), got)
+        ref = np.where(np.isnan(ref), np.float32(0), ref)
     g, r = bits(got), bits(ref)
     if not np.array_equal(g, r):
         bad = np.flatnonzero(g.ravel() != r.ravel())

@@ -109,7 +109,7 @@ __global__ void __launch_bounds__(kTile* kTileRows)
 // Dense and over raw bytes: 128-bit words plus a byte tail.
 __global__ void __launch_bounds__(kBlock)
     and_dense_kernel(uint4* out, const uint4* a, const uint4* b, i64 nvec, i64 nbytes) {
-  constexpr int U = kDenseUnroll;
+  constexpr int U = kDenseUnrollBytes;
   const i64 chunk = (i64)kBlock * U;
   const i64 nchunks = (nvec + chunk - 1) / chunk;
   for (i64 c = blockIdx.x; c < nchunks; c += gridDim.x) {
@@ -223,7 +223,7 @@ extern "C" int twg_bitwise_and(const TwgIterDesc* desc, int itemsize, int is_boo
   if (int rc = twg_iter_coalesce(&d)) return rc;
   if (all_dense(d, 3) && is_aligned(a, 16) && is_aligned(b, 16) && is_aligned(out, 16)) {
     const int64_t nbytes = d.numel * itemsize, nvec = nbytes / 16;
-    const int64_t chunk = (int64_t)kBlock * kDenseUnroll;
+    const int64_t chunk = (int64_t)kBlock * kDenseUnrollBytes;
     const int64_t grid = std::min<int64_t>(std::max<int64_t>(1, (nvec + chunk - 1) / chunk), 0x7fffffff);
     and_dense_kernel<<<(unsigned)grid, kBlock, 0, s>>>(static_cast<uint4*>(out), static_cast<const uint4*>(a),
                                                         static_cast<const uint4*>(b), nvec, nbytes);

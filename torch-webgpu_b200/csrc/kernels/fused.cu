@@ -172,7 +172,7 @@ static std::string generate_source(const TwgFusedInstr* prog, int n, const Analy
   s += line;
   snprintf(line, sizeof(line),
            "extern \"C\" __global__ void __launch_bounds__(kBlock) twg_fused_dense(PwPtrs<NT> p, i64 nunits, i64 n) "
-           "{ pw_contig_body<Prog, %d>(p, Prog{}, nunits, n); }\n", kDenseUnroll);
+           "{ pw_contig_body<Prog, %d>(p, Prog{}, nunits, n); }\n", dense_unroll(a.nin));
   s += line;
   s += "extern \"C\" __global__ void __launch_bounds__(kTile * kTileRows) twg_fused_tile(PwPtrs<NT> p, TileDesc<NT> d) "
        "{ pw_tile_body<Prog>(p, Prog{}, d); }\n";

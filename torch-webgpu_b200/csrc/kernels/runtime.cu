@@ -145,7 +145,7 @@ int plan_pointwise(const PwSig& sig, const TwgIterDesc* desc, void* const* ptrs,
   }
   if (dense) {
     plan->nunits = d.numel / vec;
-    const int64_t chunk = (int64_t)kBlock * kDenseUnroll;
+    const int64_t chunk = (int64_t)kBlock * dense_unroll(sig.nin);
     plan->grid = (unsigned)std::min<int64_t>(std::max<int64_t>(1, (plan->nunits + chunk - 1) / chunk), 0x7fffffff);
     plan->path = kPathDense;
     return TWG_OK;

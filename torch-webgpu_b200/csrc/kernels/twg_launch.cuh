@@ -17,7 +17,11 @@ namespace twg {
 enum PwPath { kPathNone = 0, kPathDense = 1, kPathTile = 2, kPathStrided32 = 3, kPathStrided64 = 4 };
 extern thread_local int g_last_path;
 
-constexpr int kDenseUnroll = 4;    // 128-bit requests in flight per input per thread
+// 128-bit units a thread keeps in flight per operand on the dense path.  Measured on B200: two
+// outstanding 16-byte loads per thread saturate HBM and more only cost occupancy, so kernels with
+// two or more inputs take one unit per operand, single-input kernels two.
+constexpr int dense_unroll(int nin) { return nin >= 2 ? 1 : 2; }
+constexpr int kDenseUnrollBytes = 2;  // raw-byte kernels of copy.cu
 constexpr int kStridedUnroll = 4;
 
 inline bool is_aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
@@ -88,7 +92,7 @@ int launch_pointwise(const F& f, const TwgIterDesc* desc, void* const* ptrs_in, 
   for (int t = 0; t < NT; ++t) ptrs.p[t] = ptrs_in[t];
   switch (plan.path) {
     case kPathDense:
-      pw_contig_kernel<F, kDenseUnroll><<<plan.grid, kBlock, 0, stream>>>(ptrs, f, plan.nunits, plan.d.numel);
+      pw_contig_kernel<F, dense_unroll(F::NIN)><<<plan.grid, kBlock, 0, stream>>>(ptrs, f, plan.nunits, plan.d.numel);
       break;
     case kPathTile: {
       TileDesc<NT> td;
