@@ -350,6 +350,89 @@ def per_op_table(abi, stream, peak: float) -> dict:
     return table
 
 
+def run_case(args) -> None:
+    """One kernel on a small case (a few GB at most, still larger than L2): the command the ncu
+    captures under profiles/ are taken with.  Prints its own JSON line; not the benchmark."""
+    from torch_webgpu import abi
+    L = abi.lib()
+    n = args.case_elems
+    stream = None
+    peak, _ = measured_peak()
+    rng = np.random.default_rng(11)
+
+    def host(count):
+        return (rng.random(count, dtype=np.float32) * 4 - 2).astype(np.float32)
+
+    def dense(nt, count):
+        d = abi.IterDesc()
+        abi.check(L.twg_iter_contiguous(ctypes.byref(d), nt, count))
+        return d
+
+    bufs = []
+    if args.case == "chain":
+        ins = [abi.DeviceBuffer(4 * n) for _ in range(3)]
+        for b_ in ins:
+            b_.upload(host(n))
+        m = abi.DeviceBuffer(n)
+        prog = abi.fused_compile(abi.CHAIN_MASK_PROGRAM)
+        d = dense(4, n)
+        ptrs = (ctypes.c_void_p * 4)(m.ptr, ins[0].ptr, ins[1].ptr, ins[2].ptr)
+        fn = lambda: abi.check(L.twg_fused_launch(prog, ctypes.byref(d), ptrs, stream))
+        nbytes = 13 * n
+        bufs = ins + [m]
+    elif args.case in ("relu", "silu", "gelu_erf"):
+        x, y = abi.DeviceBuffer(4 * n), abi.DeviceBuffer(4 * n)
+        x.upload(host(n))
+        d = dense(2, n)
+        op = abi.UNARY[args.case]
+        fn = lambda: abi.check(L.twg_unary_f32(op, ctypes.byref(d), x.ptr, y.ptr, stream))
+        nbytes = 8 * n
+        bufs = [x, y]
+    elif args.case == "add":
+        x, y, z = abi.DeviceBuffer(4 * n), abi.DeviceBuffer(4 * n), abi.DeviceBuffer(4 * n)
+        x.upload(host(n)); y.upload(host(n))
+        d = dense(3, n)
+        fn = lambda: abi.check(L.twg_binary_f32(0, ctypes.byref(d), x.ptr, y.ptr, 1.0, z.ptr, stream))
+        nbytes = 12 * n
+        bufs = [x, y, z]
+    elif args.case == "relu_transposed":
+        r = int(round(n ** 0.5))
+        n = r * r
+        x, y = abi.DeviceBuffer(4 * n), abi.DeviceBuffer(4 * n)
+        x.upload(host(n))
+        d = abi.make_desc((r, r), [((r, r), (r, 1)), ((r, r), (1, r))])
+        fn = lambda: abi.check(L.twg_unary_f32(1, ctypes.byref(d), x.ptr, y.ptr, stream))
+        nbytes = 8 * n
+        bufs = [x, y]
+    elif args.case in ("masked_select", "masked_select_rowmask"):
+        x, out = abi.DeviceBuffer(4 * n), abi.DeviceBuffer(4 * n)
+        x.upload(host(n))
+        res = abi.DeviceBuffer(16)
+        wsb = L.twg_masked_select_workspace_bytes(n)
+        ws = abi.DeviceBuffer(wsb)
+        if args.case == "masked_select":
+            mk = abi.DeviceBuffer(n)
+            mk.upload((rng.random(n) < args.case_density).astype(np.uint8))
+            d = dense(2, n)
+        else:
+            r = int(round(n ** 0.5))
+            n = r * r
+            mk = abi.DeviceBuffer(r)
+            mk.upload((rng.random(r) < args.case_density).astype(np.uint8))
+            d = abi.make_desc((r, r), [((r, r), (r, 1)), ((r, 1), (1, 1))])
+        fn = lambda: abi.check(L.twg_masked_select_f32(ctypes.byref(d), x.ptr, mk.ptr, out.ptr, res.ptr, ws.ptr, wsb, stream))
+        fn()
+        k = int(res.download(np.int64, 2)[0])
+        nbytes = (5 if args.case == "masked_select" else 4) * n + 4 * k
+        bufs = [x, out, res, ws, mk]
+    else:
+        raise SystemExit(f"unknown case {args.case}")
+    ms = time_op(abi, stream, fn, iters=max(args.steps, 1), warmup=max(args.warmup, 0))
+    print(json.dumps({"case": args.case, "elements": n, "ms": ms, "algorithmic_bytes": nbytes,
+                      "gbs": nbytes / ms / 1e6, "frac_of_peak": nbytes / ms / 1e6 / peak, "path": abi.last_path()}), flush=True)
+    del bufs
+
+
 def run_gpu_arm(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -534,8 +617,13 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-ops", action="store_true", help="skip the per-op GB/s table")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--case", default=None, help="run one kernel on a small case (for ncu captures) and exit")
+    ap.add_argument("--case-elems", type=int, default=1 << 27)
+    ap.add_argument("--case-density", type=float, default=0.5)
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.case:
+        run_case(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_gpu_arm(args)
