@@ -1,10 +1,10 @@
 // masked_select as a single-pass stream compaction.
 //
-// One CTA owns one tile of consecutive logical elements.  Inside the tile, selected elements are
-// ranked with popc on the packed mask bytes plus a warp scan (dense path) or with warp ballots
-// (strided path); the tile's base offset in the output comes from a decoupled look-back over the
-// preceding tiles' published counts, so the input is read exactly once and no second pass or
-// global scan is needed.  Selected values are first packed into shared memory in output order and
+// One CTA owns a run of consecutive logical elements (a chunk of tiles on the dense path, one tile
+// on the strided path).  Inside a tile, selected elements are ranked with popc on the packed mask
+// bytes plus a warp scan (dense path) or with warp ballots (strided path); the run's base offset in
+// the output comes from a decoupled look-back over the preceding runs' published counts, so one
+// launch does everything, src is read exactly once and no global scan kernel is needed.  Selected values are first packed into shared memory in output order and
 // then written as contiguous runs.
 //
 // Forward progress: a tile's index is a ticket drawn from a global counter when its CTA starts,
@@ -16,13 +16,14 @@
 
 #include <atomic>
 #include <cstdlib>
+#include <string>
 
 namespace twg {
 
 constexpr int kMsThreads = 256;
 constexpr int kMsWarps = kMsThreads / 32;
 constexpr int kMsRound = kMsThreads * 16;           // 4096 elements: what one staging pass holds
-constexpr int kMsMaxRounds = 4;                     // dense tiles are 1, 2 or 4 rounds
+constexpr int kMsMaxRounds = 2;                     // double-buffered per-warp totals
 constexpr size_t kMsHeaderBytes = 256;              // ticket counter, padded
 
 constexpr u64 kMsAggregate = 1ull << 62;
@@ -48,15 +49,18 @@ __device__ __forceinline__ u64 warp_sum_u64(u64 v) {
 struct MsShared {
   float stage[kMsRound];
   u32 warp_total[kMsMaxRounds][kMsWarps];
+  u32 reduce[kMsWarps];
   i64 tile;
   i64 excl;
 };
 
-// Executed by warp 0 only.  Publishes this tile's count, resolves the number of selected
-// elements in all earlier tiles, publishes the inclusive prefix and returns the exclusive one.
+// Decoupled look-back, executed by warp 0.  Publishes this chunk's count, resolves the number of
+// selected elements in all earlier chunks, publishes the inclusive prefix and returns the
+// exclusive one.  Each poll reads the 32 nearest unresolved predecessors; published aggregates
+// in front of the first unpublished descriptor are consumed at once.
 __device__ __forceinline__ i64 lookback(i64 tile, u32 tile_total, u64* desc, i64* result, i64 poll_budget) {
   const int lane = threadIdx.x & 31;
-  // A negative budget is the test hook "tile 0 never publishes": every wait that depends on it
+  // A negative budget is the test hook "chunk 0 never publishes": every wait that depends on it
   // must run out after |budget| polls and report TWG_ERR_TIMEOUT instead of hanging.
   const bool withhold_first = poll_budget < 0;
   if (withhold_first) poll_budget = -poll_budget;
@@ -71,11 +75,10 @@ __device__ __forceinline__ i64 lookback(i64 tile, u32 tile_total, u64* desc, i64
   bool timed_out = false;
   while (true) {
     const i64 idx = look - lane;
-    const u64 d = idx >= 0 ? ld_relaxed_u64(desc + idx) : kMsPrefix;  // before tile 0: prefix of 0
+    const u64 d = idx >= 0 ? ld_relaxed_u64(desc + idx) : kMsPrefix;  // before chunk 0: prefix of 0
     const u32 status = (u32)(d >> 62);
     const u32 invalid = __ballot_sync(0xffffffffu, status == 0u);
     const u32 prefix = __ballot_sync(0xffffffffu, status == 2u);
-    // lanes nearer than the first unpublished tile can be consumed right away
     const int first_invalid = invalid ? __ffs(invalid) - 1 : 32;
     const int first_prefix = prefix ? __ffs(prefix) - 1 : 32;
     if (first_prefix < first_invalid) {
@@ -83,13 +86,12 @@ __device__ __forceinline__ i64 lookback(i64 tile, u32 tile_total, u64* desc, i64
       break;
     }
     if (first_invalid > 0) {
-      // consume the published aggregates in front of the gap and continue from the gap
       excl += warp_sum_u64(lane < first_invalid ? (d & kMsValueMask) : 0ull);
       look -= first_invalid;
-      if (first_invalid == 32) continue;
+      if (first_invalid == 32) continue;  // 32 aggregates, no prefix yet: keep walking
     }
     if (++polls > poll_budget) { timed_out = true; break; }
-    if (polls > 32) __nanosleep(64);
+    if (polls > 64) __nanosleep(64);
   }
   if (timed_out) {
     excl = 0;
@@ -116,117 +118,150 @@ __device__ __forceinline__ void flush_stage(const float* stage, float* out, i64 
 }
 
 // ------------------------------------------------------------------------------------------
-// Dense path: src contiguous and 16-byte aligned; the mask is either a dense bool array (4-byte
+// Dense path: src contiguous and 16-byte aligned; the mask is either a dense bool array (16-byte
 // aligned) or, with ROWMASK, one bool per row of `row_len` elements (a [R,1] mask broadcast over
-// [R,C] with C % 4 == 0).  A tile is ROUNDS rounds of 4096 elements.  In a round a warp covers
-// 512 consecutive elements as 4 sub-rounds of 32 quads; lane l owns quad j*32+l of sub-round j, so
-// the mask is read as 128-byte runs and src as 512-byte runs.  Every load of the tile is issued
-// before the first use: with a dense mask src does not wait for the mask; with a row mask the
-// (cached) row flag is read first and unselected rows are never fetched.
+// [R,C] with C % 4 == 0).
+//
+// A CTA owns a chunk of CH consecutive tiles of 4096 elements.
+//   Phase A  counts the selected elements of the whole chunk from the mask alone (1 byte per
+//            element, so the chunk's count is known after one short read), publishes it and
+//            starts the look-back.  The chain of dependent tiles therefore has one link per
+//            chunk, not per tile, and its latency is amortised over CH tiles of streaming.
+//   Phase B  walks the tiles with a running offset.  The mask is read again - the chunk's mask
+//            (CH x 4 KB) was just fetched and is still in L2, so DRAM sees it once - together
+//            with src; the next tile's loads are issued before the current tile is ranked.
+// In a tile a warp covers 512 consecutive elements as 4 sub-rounds of 32 quads; lane l owns quad
+// j*32+l of sub-round j, so the mask is read as 128-byte runs and src as 512-byte runs.  With a
+// row mask, rows whose flag is 0 are never fetched.
 // ------------------------------------------------------------------------------------------
-template <int ROUNDS, bool ROWMASK>
-__global__ void __launch_bounds__(kMsThreads)
-    ms_dense_kernel(const float* src, const u8* mask, float* out, i64 n, i64 ntiles, u64* ticket, u64* desc,
+template <bool ROWMASK>
+__device__ __forceinline__ u32 mask_quad(const u8* mask, i64 e, i64 n, const FastDiv32& row_len) {
+  u32 w = 0;
+  if constexpr (ROWMASK) {
+    if (e < n) w = ld_b8(mask + row_len.div((u32)e)) != 0u ? 0x01010101u : 0u;  // n < 2^31 on this path
+    if (e + 3 >= n && w) w &= (e + 2 < n) ? 0x00ffffffu : (e + 1 < n) ? 0x0000ffffu : 0x000000ffu;
+  } else {
+    if (e + 3 < n) {
+      w = ld_b32(mask + e);
+    } else {
+      for (int b = 0; b < 4; ++b)
+        if (e + b < n) w |= ld_b8(mask + e + b) << (8 * b);
+    }
+    w = __vcmpne4(w, 0u) & 0x01010101u;
+  }
+  return w;
+}
+
+template <int CH, bool ROWMASK>
+__global__ void __launch_bounds__(kMsThreads, 4)
+    ms_dense_kernel(const float* src, const u8* mask, float* out, i64 n, i64 nchunks, u64* ticket, u64* desc,
                     i64* result, i64 poll_budget, FastDiv32 row_len) {
   __shared__ MsShared sm;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (threadIdx.x == 0) sm.tile = (i64)atomicAdd(ticket, 1ull);
-  __syncthreads();
-  const i64 tile = sm.tile;
-  if (tile >= ntiles) return;
-  const i64 tile_base = tile * (i64)(ROUNDS * kMsRound) + (i64)warp * 512;
+  i64 chunk = blockIdx.x;
+  if (ticket != nullptr) {
+    if (threadIdx.x == 0) sm.tile = (i64)atomicAdd(ticket, 1ull);
+    __syncthreads();
+    chunk = sm.tile;
+  }
+  if (chunk >= nchunks) return;
+  const i64 chunk_base = chunk * (i64)(CH * kMsRound);
+  const bool full_chunk = chunk_base + (i64)(CH * kMsRound) <= n;
 
-  u32 m[ROUNDS][4];
-  u32 v[ROUNDS][4][4];
+  // ---- phase A: count the chunk ----
+  u32 c = 0;
+  if (!ROWMASK && full_chunk) {
 #pragma unroll
-  for (int r = 0; r < ROUNDS; ++r) {
+    for (int i = 0; i < CH; ++i) {
+      const uint4 q = ld_v4(mask + chunk_base + (i64)i * kMsRound + threadIdx.x * 16);
+      c += __popc(__vcmpne4(q.x, 0u) & 0x01010101u) + __popc(__vcmpne4(q.y, 0u) & 0x01010101u) +
+           __popc(__vcmpne4(q.z, 0u) & 0x01010101u) + __popc(__vcmpne4(q.w, 0u) & 0x01010101u);
+    }
+  } else {
+    for (int q = threadIdx.x; q < CH * (kMsRound / 4); q += kMsThreads)
+      c += __popc(mask_quad<ROWMASK>(mask, chunk_base + (i64)q * 4, n, row_len));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+  if (lane == 0) sm.reduce[warp] = c;
+  __syncthreads();
+  if (warp == 0) {
+    u32 chunk_total = 0;
+#pragma unroll
+    for (int w = 0; w < kMsWarps; ++w) chunk_total += sm.reduce[w];
+    const i64 excl = lookback(chunk, chunk_total, desc, result, poll_budget);
+    if (lane == 0) {
+      sm.excl = excl;
+      if (chunk == nchunks - 1) result[0] = excl + (i64)chunk_total;
+    }
+  }
+
+  // ---- phase B: compact tile by tile ----
+  u32 m[4], v[4][4];
+  auto load_tile = [&](int t) {
+    const i64 tb = chunk_base + (i64)t * kMsRound + (i64)warp * 512;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const i64 e = tile_base + (i64)r * kMsRound + (i64)(j * 32 + lane) * 4;
-      u32 w = 0;
-      if constexpr (ROWMASK) {
-        if (e < n) w = ld_b8(mask + row_len.div((u32)e)) != 0u ? 0x01010101u : 0u;  // n < 2^31 here
-        if (e + 3 >= n && w) w &= (e + 2 < n) ? 0x00ffffffu : (e + 1 < n) ? 0x0000ffffu : 0x000000ffu;
-      } else {
-        if (e + 3 < n) {
-          w = ld_b32(mask + e);
-        } else {
-          for (int b = 0; b < 4; ++b)
-            if (e + b < n) w |= ld_b8(mask + e + b) << (8 * b);
-        }
-        w = __vcmpne4(w, 0u) & 0x01010101u;
-      }
-      m[r][j] = w;
-      const bool want = ROWMASK ? (w != 0u) : true;
+      const i64 e = tb + (i64)(j * 32 + lane) * 4;
+      m[j] = mask_quad<ROWMASK>(mask, e, n, row_len);
+      const bool want = ROWMASK ? (m[j] != 0u) : (e < n);
       if (want) {
         if (e + 3 < n) {
           const uint4 q = ld_v4(src + e);
-          v[r][j][0] = q.x; v[r][j][1] = q.y; v[r][j][2] = q.z; v[r][j][3] = q.w;
+          v[j][0] = q.x; v[j][1] = q.y; v[j][2] = q.z; v[j][3] = q.w;
         } else {
 #pragma unroll
-          for (int b = 0; b < 4; ++b) v[r][j][b] = (e + b < n) ? ld_b32(src + e + b) : 0u;
+          for (int b = 0; b < 4; ++b) v[j][b] = (e + b < n) ? ld_b32(src + e + b) : 0u;
         }
       }
     }
-  }
-
-  // ranks inside a round: per-sub-round counts packed into one word (each field <= 128 after
-  // the warp scan), one scan per round
-  u32 excl_w[ROUNDS], sub_base[ROUNDS][4];
+  };
+  const int tiles_here = full_chunk ? CH : (int)((n - chunk_base + kMsRound - 1) / kMsRound);
+  i64 running = 0;
+  load_tile(0);
+  for (int t = 0; t < tiles_here; ++t) {
+    u32 mm[4], vv[4][4];
 #pragma unroll
-  for (int r = 0; r < ROUNDS; ++r) {
-    const u32 cnt = __popc(m[r][0]) | (__popc(m[r][1]) << 8) | (__popc(m[r][2]) << 16) | (__popc(m[r][3]) << 24);
+    for (int j = 0; j < 4; ++j) {
+      mm[j] = m[j];
+#pragma unroll
+      for (int b = 0; b < 4; ++b) vv[j][b] = v[j][b];
+    }
+    if (t + 1 < tiles_here) load_tile(t + 1);  // in flight while this tile is ranked and flushed
+
+    // ranks: per-sub-round counts packed into one word (each field <= 128 after the warp scan)
+    const u32 cnt = __popc(mm[0]) | (__popc(mm[1]) << 8) | (__popc(mm[2]) << 16) | (__popc(mm[3]) << 24);
     u32 incl = cnt;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      const u32 t = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += t;
+      const u32 x = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += x;
     }
     const u32 tot = __shfl_sync(0xffffffffu, incl, 31);
     const u32 t0 = tot & 0xffu, t1 = (tot >> 8) & 0xffu, t2 = (tot >> 16) & 0xffu, t3 = tot >> 24;
-    excl_w[r] = incl - cnt;
-    sub_base[r][0] = 0u; sub_base[r][1] = t0; sub_base[r][2] = t0 + t1; sub_base[r][3] = t0 + t1 + t2;
-    if (lane == 0) sm.warp_total[r][warp] = t0 + t1 + t2 + t3;
-  }
-  __syncthreads();
-  u32 warp_off[ROUNDS], round_total[ROUNDS], tile_total = 0;
-#pragma unroll
-  for (int r = 0; r < ROUNDS; ++r) {
-    u32 off = 0, tot = 0;
+    const u32 excl_w = incl - cnt;
+    const u32 sub_base[4] = {0u, t0, t0 + t1, t0 + t1 + t2};
+    if (lane == 0) sm.warp_total[t & 1][warp] = t0 + t1 + t2 + t3;
+    __syncthreads();  // totals visible; the previous tile's flush has finished reading the stage
+    u32 warp_off = 0, tile_total = 0;
 #pragma unroll
     for (int w = 0; w < kMsWarps; ++w) {
-      const u32 t = sm.warp_total[r][w];
-      if (w < warp) off += t;
-      tot += t;
+      const u32 x = sm.warp_total[t & 1][w];
+      if (w < warp) warp_off += x;
+      tile_total += x;
     }
-    warp_off[r] = off;
-    round_total[r] = tot;
-    tile_total += tot;
-  }
-  if (warp == 0) {
-    const i64 excl = lookback(tile, tile_total, desc, result, poll_budget);
-    if (lane == 0) {
-      sm.excl = excl;
-      if (tile == ntiles - 1) result[0] = excl + (i64)tile_total;
-    }
-  }
-
-  u32 round_base = 0;
-#pragma unroll
-  for (int r = 0; r < ROUNDS; ++r) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      if (m[r][j] != 0u) {
-        u32 pos = warp_off[r] + sub_base[r][j] + ((excl_w[r] >> (8 * j)) & 0xffu);
+      if (mm[j] != 0u) {
+        u32 pos = warp_off + sub_base[j] + ((excl_w >> (8 * j)) & 0xffu);
 #pragma unroll
         for (int b = 0; b < 4; ++b)
-          if ((m[r][j] >> (8 * b)) & 1u) sm.stage[pos++] = __uint_as_float(v[r][j][b]);
+          if ((mm[j] >> (8 * b)) & 1u) sm.stage[pos++] = __uint_as_float(vv[j][b]);
       }
     }
-    __syncthreads();  // stage complete (and, in round 0, sm.excl published)
-    flush_stage(sm.stage, out, sm.excl + (i64)round_base, round_total[r]);
-    round_base += round_total[r];
-    if (r + 1 < ROUNDS) __syncthreads();  // stage free again
+    __syncthreads();  // stage complete; in the first iteration also: sm.excl published
+    flush_stage(sm.stage, out, sm.excl + running, tile_total);
+    running += tile_total;
   }
 }
 
@@ -242,9 +277,12 @@ __global__ void __launch_bounds__(kMsThreads)
                       u64* ticket, u64* desc, i64* result, i64 poll_budget) {
   __shared__ MsShared sm;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (threadIdx.x == 0) sm.tile = (i64)atomicAdd(ticket, 1ull);
-  __syncthreads();
-  const i64 tile = sm.tile;
+  i64 tile = blockIdx.x;
+  if (ticket != nullptr) {
+    if (threadIdx.x == 0) sm.tile = (i64)atomicAdd(ticket, 1ull);
+    __syncthreads();
+    tile = sm.tile;
+  }
   if (tile >= ntiles) return;
   const i64 warp_base = tile * kMsRound + (i64)warp * 512;
 
@@ -290,25 +328,39 @@ __global__ void __launch_bounds__(kMsThreads)
   flush_stage(sm.stage, out, sm.excl, tile_total);
 }
 
-// rounds per dense tile; TWG_MS_ROUNDS (1, 2 or 4) overrides it for experiments
-static int dense_rounds() {
-  static const int rounds = [] {
-    const char* env = getenv("TWG_MS_ROUNDS");
+// tiles per dense chunk; TWG_MS_CHUNK (4, 8, 16 or 32) overrides it for experiments
+static int dense_chunk_tiles() {
+  static const int tiles = [] {
+    const char* env = getenv("TWG_MS_CHUNK");
     const int r = env ? atoi(env) : 0;
-    return (r == 1 || r == 2 || r == 4) ? r : 2;
+    return (r == 4 || r == 8 || r == 16 || r == 32) ? r : 16;
   }();
-  return rounds;
+  return tiles;
+}
+
+// Tile order.  Default: tickets from a global counter (forward progress does not depend on the
+// order in which the hardware starts CTAs).  TWG_MS_ORDER=blockidx uses blockIdx.x instead, for
+// measuring what the ticket costs.
+static bool use_ticket() {
+  static const bool v = [] {
+    const char* env = getenv("TWG_MS_ORDER");
+    return !(env && std::string(env) == "blockidx");
+  }();
+  return v;
 }
 
 template <bool ROWMASK>
-static void launch_dense(int rounds, unsigned ntiles, cudaStream_t s, const float* src, const u8* mask, float* out, i64 n,
-                         u64* ticket, u64* tdesc, i64* result, i64 budget, FastDiv32 row_len) {
-  if (rounds == 1)
-    ms_dense_kernel<1, ROWMASK><<<ntiles, kMsThreads, 0, s>>>(src, mask, out, n, ntiles, ticket, tdesc, result, budget, row_len);
-  else if (rounds == 2)
-    ms_dense_kernel<2, ROWMASK><<<ntiles, kMsThreads, 0, s>>>(src, mask, out, n, ntiles, ticket, tdesc, result, budget, row_len);
-  else
-    ms_dense_kernel<4, ROWMASK><<<ntiles, kMsThreads, 0, s>>>(src, mask, out, n, ntiles, ticket, tdesc, result, budget, row_len);
+static void launch_dense(int chunk_tiles, unsigned nchunks, cudaStream_t s, const float* src, const u8* mask, float* out,
+                         i64 n, u64* ticket, u64* tdesc, i64* result, i64 budget, FastDiv32 row_len) {
+#define TWG_MS_LAUNCH(CH) \
+  ms_dense_kernel<CH, ROWMASK><<<nchunks, kMsThreads, 0, s>>>(src, mask, out, n, nchunks, ticket, tdesc, result, budget, row_len)
+  switch (chunk_tiles) {
+    case 4: TWG_MS_LAUNCH(4); break;
+    case 8: TWG_MS_LAUNCH(8); break;
+    case 32: TWG_MS_LAUNCH(32); break;
+    default: TWG_MS_LAUNCH(16); break;
+  }
+#undef TWG_MS_LAUNCH
 }
 
 }  // namespace twg
@@ -345,28 +397,28 @@ extern "C" int twg_masked_select_f32(const TwgIterDesc* desc, const float* src, 
   TwgIterDesc d = *desc;
   d.ntensors = 2;
   if (int rc = twg_iter_coalesce(&d)) return rc;
-  u64* ticket = static_cast<u64*>(workspace);
+  u64* ticket = use_ticket() ? static_cast<u64*>(workspace) : nullptr;
   u64* tdesc = reinterpret_cast<u64*>(static_cast<char*>(workspace) + kMsHeaderBytes);
   i64* result = reinterpret_cast<i64*>(result_dev);
   const long long budget = g_poll_budget.load();
 
   const bool dense = (d.ndim == 0 || (d.ndim == 1 && (n == 1 || (d.strides[0][0] == 1 && d.strides[1][0] == 1)))) &&
-                     is_aligned(src, 16) && is_aligned(mask, 4);
+                     is_aligned(src, 16) && is_aligned(mask, 16);
   // [R,C] source with a [R,1] mask: dimension 0 is the row (src stride 1, mask stride 0),
   // dimension 1 walks rows in both
   const bool rowmask = d.ndim == 2 && d.strides[0][0] == 1 && d.strides[1][0] == 0 && d.strides[0][1] == d.shape[0] &&
                        d.strides[1][1] == 1 && d.shape[0] % 4 == 0 && n < (int64_t(1) << 31) && is_aligned(src, 16);
   if (dense || rowmask) {
-    const int rounds = dense_rounds();
-    const int64_t tile_elems = (int64_t)rounds * kMsRound;
+    const int chunk_tiles = dense_chunk_tiles();
+    const int64_t tile_elems = (int64_t)chunk_tiles * kMsRound;
     const int64_t ntiles = (n + tile_elems - 1) / tile_elems;
     TWG_REQUIRE(ntiles <= 0x7fffffff, "twg_masked_select_f32: %lld elements exceed the tile limit", (long long)n);
     TWG_CUDA(cudaMemsetAsync(workspace, 0, kMsHeaderBytes + (size_t)ntiles * sizeof(u64), s));
     FastDiv32 row_len;
     row_len.d = rowmask ? (uint32_t)d.shape[0] : 1u;
     make_fastdiv(row_len.d, &row_len.m, &row_len.s);
-    if (rowmask) launch_dense<true>(rounds, (unsigned)ntiles, s, src, mask, out, n, ticket, tdesc, result, budget, row_len);
-    else launch_dense<false>(rounds, (unsigned)ntiles, s, src, mask, out, n, ticket, tdesc, result, budget, row_len);
+    if (rowmask) launch_dense<true>(chunk_tiles, (unsigned)ntiles, s, src, mask, out, n, ticket, tdesc, result, budget, row_len);
+    else launch_dense<false>(chunk_tiles, (unsigned)ntiles, s, src, mask, out, n, ticket, tdesc, result, budget, row_len);
     TWG_CHECK_LAUNCH();
     g_last_path = kPathDense;
     return TWG_OK;
