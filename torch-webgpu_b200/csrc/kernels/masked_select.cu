@@ -54,28 +54,33 @@ struct MsShared {
   i64 excl;
 };
 
-// Decoupled look-back, executed by warp 0.  Publishes this chunk's count, resolves the number of
-// selected elements in all earlier chunks, publishes the inclusive prefix and returns the
-// exclusive one.  Each poll reads the 32 nearest unresolved predecessors; published aggregates
-// in front of the first unpublished descriptor are consumed at once.
-__device__ __forceinline__ i64 lookback(i64 tile, u32 tile_total, u64* desc, i64* result, i64 poll_budget) {
-  const int lane = threadIdx.x & 31;
-  // A negative budget is the test hook "chunk 0 never publishes": every wait that depends on it
-  // must run out after |budget| polls and report TWG_ERR_TIMEOUT instead of hanging.
-  const bool withhold_first = poll_budget < 0;
-  if (withhold_first) poll_budget = -poll_budget;
+// Decoupled look-back in two steps.  lookback_publish (one thread) announces this run's count as
+// soon as it is known; lookback_resolve (warp 0, later) adds up the counts of all earlier runs,
+// publishes the inclusive prefix and returns the exclusive one.  Each poll reads the 32 nearest
+// unresolved predecessors; published aggregates in front of the first unpublished descriptor are
+// consumed at once.
+//
+// A negative poll budget is the test hook "run 0 never publishes": every wait that depends on it
+// must run out after |budget| polls and report TWG_ERR_TIMEOUT instead of hanging.
+__device__ __forceinline__ void lookback_publish(i64 tile, u32 tile_total, u64* desc, i64 poll_budget) {
   if (tile == 0) {
-    if (lane == 0 && !withhold_first) st_relaxed_u64(desc, kMsPrefix | (u64)tile_total);
-    return 0;
+    if (poll_budget >= 0) st_relaxed_u64(desc, kMsPrefix | (u64)tile_total);
+  } else {
+    st_relaxed_u64(desc + tile, kMsAggregate | (u64)tile_total);
   }
-  if (lane == 0) st_relaxed_u64(desc + tile, kMsAggregate | (u64)tile_total);
+}
+
+__device__ __forceinline__ i64 lookback_resolve(i64 tile, u32 tile_total, u64* desc, i64* result, i64 poll_budget) {
+  const int lane = threadIdx.x & 31;
+  if (tile == 0) return 0;
+  if (poll_budget < 0) poll_budget = -poll_budget;
   u64 excl = 0;
   i64 look = tile - 1;  // nearest predecessor not yet accounted for
   i64 polls = 0;
   bool timed_out = false;
   while (true) {
     const i64 idx = look - lane;
-    const u64 d = idx >= 0 ? ld_relaxed_u64(desc + idx) : kMsPrefix;  // before chunk 0: prefix of 0
+    const u64 d = idx >= 0 ? ld_relaxed_u64(desc + idx) : kMsPrefix;  // before run 0: prefix of 0
     const u32 status = (u32)(d >> 62);
     const u32 invalid = __ballot_sync(0xffffffffu, status == 0u);
     const u32 prefix = __ballot_sync(0xffffffffu, status == 2u);
@@ -123,16 +128,18 @@ __device__ __forceinline__ void flush_stage(const float* stage, float* out, i64 
 // [R,C] with C % 4 == 0).
 //
 // A CTA owns a chunk of CH consecutive tiles of 4096 elements.
-//   Phase A  counts the selected elements of the whole chunk from the mask alone (1 byte per
-//            element, so the chunk's count is known after one short read), publishes it and
-//            starts the look-back.  The chain of dependent tiles therefore has one link per
-//            chunk, not per tile, and its latency is amortised over CH tiles of streaming.
-//   Phase B  walks the tiles with a running offset.  The mask is read again - the chunk's mask
-//            (CH x 4 KB) was just fetched and is still in L2, so DRAM sees it once - together
-//            with src; the next tile's loads are issued before the current tile is ranked.
+//   Phase A  reads the chunk's mask (1 byte per element), keeps it in shared memory packed to one
+//            bit per element, counts its selected elements and publishes the count.  The chain of
+//            dependent CTAs therefore has one link per chunk, not per tile, and its latency is
+//            amortised over CH tiles of streaming.
+//   Phase B  walks the tiles with a running offset.  The mask comes from shared memory, so src
+//            quads whose four mask bytes are all zero are never fetched, and the next tile's src
+//            loads are issued before the current tile is ranked and flushed.  The look-back is
+//            resolved as late as possible - after the first tile is staged, right before its
+//            flush - so that most predecessors have published by then.
 // In a tile a warp covers 512 consecutive elements as 4 sub-rounds of 32 quads; lane l owns quad
-// j*32+l of sub-round j, so the mask is read as 128-byte runs and src as 512-byte runs.  With a
-// row mask, rows whose flag is 0 are never fetched.
+// j*32+l of sub-round j, so src is read as 512-byte runs.  HBM sees every mask byte and every
+// selected sector of src once.
 // ------------------------------------------------------------------------------------------
 template <bool ROWMASK>
 __device__ __forceinline__ u32 mask_quad(const u8* mask, i64 e, i64 n, const FastDiv32& row_len) {
@@ -151,12 +158,16 @@ __device__ __forceinline__ u32 mask_quad(const u8* mask, i64 e, i64 n, const Fas
   }
   return w;
 }
+// four 0/1 bytes <-> one nibble (the products have no colliding partial terms, so no carries)
+__device__ __forceinline__ u32 bytes_to_nibble(u32 w) { return ((w * 0x01020408u) >> 24) & 0xfu; }
+__device__ __forceinline__ u32 nibble_to_bytes(u32 nib) { return (nib * 0x00204081u) & 0x01010101u; }
 
 template <int CH, bool ROWMASK>
 __global__ void __launch_bounds__(kMsThreads, 4)
     ms_dense_kernel(const float* src, const u8* mask, float* out, i64 n, i64 nchunks, u64* ticket, u64* desc,
                     i64* result, i64 poll_budget, FastDiv32 row_len) {
   __shared__ MsShared sm;
+  __shared__ u32 bits[CH * (kMsRound / 32)];  // the chunk's mask, one bit per element
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   i64 chunk = blockIdx.x;
   if (ticket != nullptr) {
@@ -168,33 +179,39 @@ __global__ void __launch_bounds__(kMsThreads, 4)
   const i64 chunk_base = chunk * (i64)(CH * kMsRound);
   const bool full_chunk = chunk_base + (i64)(CH * kMsRound) <= n;
 
-  // ---- phase A: count the chunk ----
+  // ---- phase A: mask -> bits, count ----
   u32 c = 0;
   if (!ROWMASK && full_chunk) {
+    unsigned short* bits16 = reinterpret_cast<unsigned short*>(bits);
 #pragma unroll
     for (int i = 0; i < CH; ++i) {
-      const uint4 q = ld_v4(mask + chunk_base + (i64)i * kMsRound + threadIdx.x * 16);
-      c += __popc(__vcmpne4(q.x, 0u) & 0x01010101u) + __popc(__vcmpne4(q.y, 0u) & 0x01010101u) +
-           __popc(__vcmpne4(q.z, 0u) & 0x01010101u) + __popc(__vcmpne4(q.w, 0u) & 0x01010101u);
+      uint4 q = ld_v4(mask + chunk_base + (i64)i * kMsRound + threadIdx.x * 16);
+      q.x = __vcmpne4(q.x, 0u) & 0x01010101u; q.y = __vcmpne4(q.y, 0u) & 0x01010101u;
+      q.z = __vcmpne4(q.z, 0u) & 0x01010101u; q.w = __vcmpne4(q.w, 0u) & 0x01010101u;
+      c += __popc(q.x) + __popc(q.y) + __popc(q.z) + __popc(q.w);
+      bits16[i * kMsThreads + threadIdx.x] = (unsigned short)(bytes_to_nibble(q.x) | (bytes_to_nibble(q.y) << 4) |
+                                                               (bytes_to_nibble(q.z) << 8) | (bytes_to_nibble(q.w) << 12));
     }
   } else {
-    for (int q = threadIdx.x; q < CH * (kMsRound / 4); q += kMsThreads)
-      c += __popc(mask_quad<ROWMASK>(mask, chunk_base + (i64)q * 4, n, row_len));
+    for (int g = threadIdx.x; g < CH * (kMsRound / 32); g += kMsThreads) {
+      u32 word = 0;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const u32 w = mask_quad<ROWMASK>(mask, chunk_base + ((i64)g * 8 + k) * 4, n, row_len);
+        c += __popc(w);
+        word |= bytes_to_nibble(w) << (4 * k);
+      }
+      bits[g] = word;
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
   if (lane == 0) sm.reduce[warp] = c;
   __syncthreads();
-  if (warp == 0) {
-    u32 chunk_total = 0;
+  u32 chunk_total = 0;
 #pragma unroll
-    for (int w = 0; w < kMsWarps; ++w) chunk_total += sm.reduce[w];
-    const i64 excl = lookback(chunk, chunk_total, desc, result, poll_budget);
-    if (lane == 0) {
-      sm.excl = excl;
-      if (chunk == nchunks - 1) result[0] = excl + (i64)chunk_total;
-    }
-  }
+  for (int w = 0; w < kMsWarps; ++w) chunk_total += sm.reduce[w];
+  if (threadIdx.x == 0) lookback_publish(chunk, chunk_total, desc, poll_budget);
 
   // ---- phase B: compact tile by tile ----
   u32 m[4], v[4][4];
@@ -202,13 +219,13 @@ __global__ void __launch_bounds__(kMsThreads, 4)
     const i64 tb = chunk_base + (i64)t * kMsRound + (i64)warp * 512;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
+      const int q = warp * 128 + j * 32 + lane;
       const i64 e = tb + (i64)(j * 32 + lane) * 4;
-      m[j] = mask_quad<ROWMASK>(mask, e, n, row_len);
-      const bool want = ROWMASK ? (m[j] != 0u) : (e < n);
-      if (want) {
+      m[j] = nibble_to_bytes((bits[t * (kMsRound / 32) + (q >> 3)] >> ((q & 7) * 4)) & 0xfu);  // 0 beyond n
+      if (m[j] != 0u) {
         if (e + 3 < n) {
-          const uint4 q = ld_v4(src + e);
-          v[j][0] = q.x; v[j][1] = q.y; v[j][2] = q.z; v[j][3] = q.w;
+          const uint4 x = ld_v4(src + e);
+          v[j][0] = x.x; v[j][1] = x.y; v[j][2] = x.z; v[j][3] = x.w;
         } else {
 #pragma unroll
           for (int b = 0; b < 4; ++b) v[j][b] = (e + b < n) ? ld_b32(src + e + b) : 0u;
@@ -257,6 +274,15 @@ __global__ void __launch_bounds__(kMsThreads, 4)
 #pragma unroll
         for (int b = 0; b < 4; ++b)
           if ((mm[j] >> (8 * b)) & 1u) sm.stage[pos++] = __uint_as_float(vv[j][b]);
+      }
+    }
+    if (t == 0) {
+      if (warp == 0) {
+        const i64 excl = lookback_resolve(chunk, chunk_total, desc, result, poll_budget);
+        if (lane == 0) {
+          sm.excl = excl;
+          if (chunk == nchunks - 1) result[0] = excl + (i64)chunk_total;
+        }
       }
     }
     __syncthreads();  // stage complete; in the first iteration also: sm.excl published
@@ -314,8 +340,9 @@ __global__ void __launch_bounds__(kMsThreads)
     if (w < warp) warp_off += t;
     tile_total += t;
   }
+  if (threadIdx.x == 0) lookback_publish(tile, tile_total, desc, poll_budget);
   if (warp == 0) {
-    const i64 excl = lookback(tile, tile_total, desc, result, poll_budget);
+    const i64 excl = lookback_resolve(tile, tile_total, desc, result, poll_budget);
     if (lane == 0) {
       sm.excl = excl;
       if (tile == ntiles - 1) result[0] = excl + (i64)tile_total;
@@ -328,14 +355,21 @@ __global__ void __launch_bounds__(kMsThreads)
   flush_stage(sm.stage, out, sm.excl, tile_total);
 }
 
-// tiles per dense chunk; TWG_MS_CHUNK (4, 8, 16 or 32) overrides it for experiments
-static int dense_chunk_tiles() {
-  static const int tiles = [] {
+// Tiles per dense chunk: the largest power of two up to 32 that still leaves about four waves
+// of chunks on the device, so that large tensors amortise the look-back over long chunks and small
+// ones still fill every SM.  TWG_MS_CHUNK (1..32, power of two) overrides it for experiments.
+static int dense_chunk_tiles(int64_t n) {
+  static const int forced = [] {
     const char* env = getenv("TWG_MS_CHUNK");
     const int r = env ? atoi(env) : 0;
-    return (r == 4 || r == 8 || r == 16 || r == 32) ? r : 16;
+    return (r == 1 || r == 2 || r == 4 || r == 8 || r == 16 || r == 32) ? r : 0;
   }();
-  return tiles;
+  if (forced) return forced;
+  const int64_t tiles = (n + kMsRound - 1) / kMsRound;
+  const int64_t want_chunks = 4ll * 4 * sm_count();
+  int ch = 32;
+  while (ch > 1 && tiles / ch < want_chunks) ch >>= 1;
+  return ch;
 }
 
 // Tile order.  Default: tickets from a global counter (forward progress does not depend on the
@@ -355,10 +389,12 @@ static void launch_dense(int chunk_tiles, unsigned nchunks, cudaStream_t s, cons
 #define TWG_MS_LAUNCH(CH) \
   ms_dense_kernel<CH, ROWMASK><<<nchunks, kMsThreads, 0, s>>>(src, mask, out, n, nchunks, ticket, tdesc, result, budget, row_len)
   switch (chunk_tiles) {
+    case 1: TWG_MS_LAUNCH(1); break;
+    case 2: TWG_MS_LAUNCH(2); break;
     case 4: TWG_MS_LAUNCH(4); break;
     case 8: TWG_MS_LAUNCH(8); break;
-    case 32: TWG_MS_LAUNCH(32); break;
-    default: TWG_MS_LAUNCH(16); break;
+    case 16: TWG_MS_LAUNCH(16); break;
+    default: TWG_MS_LAUNCH(32); break;
   }
 #undef TWG_MS_LAUNCH
 }
@@ -409,7 +445,7 @@ extern "C" int twg_masked_select_f32(const TwgIterDesc* desc, const float* src, 
   const bool rowmask = d.ndim == 2 && d.strides[0][0] == 1 && d.strides[1][0] == 0 && d.strides[0][1] == d.shape[0] &&
                        d.strides[1][1] == 1 && d.shape[0] % 4 == 0 && n < (int64_t(1) << 31) && is_aligned(src, 16);
   if (dense || rowmask) {
-    const int chunk_tiles = dense_chunk_tiles();
+    const int chunk_tiles = dense_chunk_tiles(n);
     const int64_t tile_elems = (int64_t)chunk_tiles * kMsRound;
     const int64_t ntiles = (n + tile_elems - 1) / tile_elems;
     TWG_REQUIRE(ntiles <= 0x7fffffff, "twg_masked_select_f32: %lld elements exceed the tile limit", (long long)n);
