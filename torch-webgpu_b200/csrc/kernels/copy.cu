@@ -138,7 +138,7 @@ int launch_sized(const TwgIterDesc& d, const void* a, const void* b, void* out, 
   const T* pb = static_cast<const T*>(b);
   PwPlan plan;
   plan.d = d;
-  if (plan_tile(d, NT, &plan)) {
+  if (plan_tile(d, NT, kTile, &plan)) {
     TileDesc<NT> td;
     fill_tile_desc<NT>(plan, &td);
     sized_tile_kernel<T, NIN><<<plan.grid, dim3(kTile, kTileRows), 0, stream>>>(po, pa, pb, td);
@@ -204,6 +204,10 @@ extern "C" int twg_copy_strided(const TwgIterDesc* desc, int itemsize, const voi
   }
   TWG_REQUIRE(is_aligned(in, (size_t)itemsize) && is_aligned(out, (size_t)itemsize),
               "twg_copy_strided: operands are not aligned to the element size %d", itemsize);
+  // 4-byte elements move through the f32 functor kernels (a bit-exact 32-bit copy) and get their
+  // larger tiles; the other widths use the generic kernels of this file
+  if (itemsize == 4)
+    return twg_unary_f32(TWG_UNARY_COPY, desc, static_cast<const float*>(in), static_cast<float*>(out), stream);
   return dispatch_sized<1>(d, itemsize, in, nullptr, out, s);
 }
 

@@ -174,7 +174,7 @@ static std::string generate_source(const TwgFusedInstr* prog, int n, const Analy
            "extern \"C\" __global__ void __launch_bounds__(kBlock) twg_fused_dense(PwPtrs<NT> p, i64 nunits, i64 n) "
            "{ pw_contig_body<Prog, %d>(p, Prog{}, nunits, n); }\n", dense_unroll(a.nin));
   s += line;
-  s += "extern \"C\" __global__ void __launch_bounds__(kTile * kTileRows) twg_fused_tile(PwPtrs<NT> p, TileDesc<NT> d) "
+  s += "extern \"C\" __global__ void __launch_bounds__(kTileX * kTileRows) twg_fused_tile(PwPtrs<NT> p, TileDesc<NT> d) "
        "{ pw_tile_body<Prog>(p, Prog{}, d); }\n";
   snprintf(line, sizeof(line),
            "extern \"C\" __global__ void __launch_bounds__(kBlock) twg_fused_strided32(PwPtrs<NT> p, StridedDesc<NT, u32> d, i64 n) "
@@ -448,7 +448,7 @@ static int jit_launch(TwgFusedProgram* p, const TwgIterDesc* desc, void* const* 
       TileDesc<NT> td;
       fill_tile_desc<NT>(plan, &td);
       void* args[] = {&ptrs, &td};
-      r = g_dyn.LaunchKernel(m->tile, plan.grid, 1, 1, kTile, kTileRows, 1, 0, cs, args, nullptr);
+      r = g_dyn.LaunchKernel(m->tile, plan.grid, 1, 1, kTileX, kTileRows, 1, 0, cs, args, nullptr);
       break;
     }
     case kPathStrided32: {

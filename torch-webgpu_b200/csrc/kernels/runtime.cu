@@ -106,7 +106,7 @@ bool fits_32bit(const TwgIterDesc& d, int nt) {
   return true;
 }
 
-bool plan_tile(const TwgIterDesc& d, int nt, PwPlan* plan) {
+bool plan_tile(const TwgIterDesc& d, int nt, int tile_edge, PwPlan* plan) {
   if (d.ndim != 2 || d.shape[0] < 16 || d.shape[1] < 16) return false;
   uint32_t mask = 0;
   for (int t = 0; t < nt; ++t) {
@@ -117,8 +117,8 @@ bool plan_tile(const TwgIterDesc& d, int nt, PwPlan* plan) {
   }
   if (mask == 0) return false;
   plan->dim1_mask = mask;
-  plan->tiles0 = (d.shape[0] + kTile - 1) / kTile;
-  plan->ntiles = plan->tiles0 * ((d.shape[1] + kTile - 1) / kTile);
+  plan->tiles0 = (d.shape[0] + tile_edge - 1) / tile_edge;
+  plan->ntiles = plan->tiles0 * ((d.shape[1] + tile_edge - 1) / tile_edge);
   plan->grid = (unsigned)std::min<int64_t>(plan->ntiles, 0x7fffffff);
   return true;
 }
@@ -150,7 +150,7 @@ int plan_pointwise(const PwSig& sig, const TwgIterDesc* desc, void* const* ptrs,
     plan->path = kPathDense;
     return TWG_OK;
   }
-  if (plan_tile(d, nt, plan)) {
+  if (plan_tile(d, nt, kPwTile, plan)) {
     plan->path = kPathTile;
     return TWG_OK;
   }

@@ -52,7 +52,7 @@ struct PwPlan {
 // Decide the launch shape.  Returns TWG_OK with plan->path == kPathNone for an empty iteration.
 int plan_pointwise(const PwSig& sig, const TwgIterDesc* desc, void* const* ptrs, PwPlan* plan);
 // Shared by the element-size-generic kernels in copy.cu.
-bool plan_tile(const TwgIterDesc& d, int nt, PwPlan* plan);
+bool plan_tile(const TwgIterDesc& d, int nt, int tile_edge, PwPlan* plan);
 bool fits_32bit(const TwgIterDesc& d, int nt);
 
 template <int NT>
@@ -98,7 +98,7 @@ int launch_pointwise(const F& f, const TwgIterDesc* desc, void* const* ptrs_in, 
     case kPathTile: {
       TileDesc<NT> td;
       fill_tile_desc<NT>(plan, &td);
-      pw_tile_kernel<F><<<plan.grid, dim3(kTile, kTileRows), 0, stream>>>(ptrs, f, td);
+      pw_tile_kernel<F><<<plan.grid, dim3(kTileX, kTileRows), 0, stream>>>(ptrs, f, td);
       break;
     }
     case kPathStrided32: {

@@ -340,91 +340,105 @@ __device__ __forceinline__ void pw_strided_body(const PwPtrs<PwTraits<F>::NT>& p
 
 // ------------------------------------------------------------------------------------------
 // 2-D permuted path (a true transpose: some operands are dense along dimension 0, the others
-// along dimension 1).  A CTA of 32x8 threads owns a 32x32 tile.  Operands dense along dimension
-// 1 are moved through a padded shared-memory tile so that both their global accesses and
-// everyone else's are 128-byte runs.  bit t of `dim1_mask` set: operand t is dense along dim 1.
+// along dimension 1).  A CTA of 32x8 threads owns a 64x64 tile, 16 elements per thread, so that a
+// CTA has 16 KB per operand in flight.  In registers a thread holds the tile in "dimension-0
+// order": elements (tx + 32a, ty + 8r).  Operands dense along dimension 0 are accessed directly
+// in that order; operands dense along dimension 1 are accessed with tx running along dimension 1
+// and pass through one padded shared-memory tile (row pitch 65: both the row-wise writes and
+// the column-wise reads are conflict-free), so every global access is a 128-byte run.
+// bit t of `dim1_mask` set: operand t is dense along dimension 1.
 // ------------------------------------------------------------------------------------------
-constexpr int kTile = 32;
+constexpr int kTile = 32;      // tile edge of the element-size-generic kernels (copy.cu)
+constexpr int kPwTile = 64;    // tile edge of the functor kernels
+constexpr int kTileX = 32;
 constexpr int kTileRows = 8;
+constexpr int kTileXR = kPwTile / kTileX;     // 2
+constexpr int kTileYR = kPwTile / kTileRows;  // 8
+constexpr int kTileElems = kTileXR * kTileYR; // 16 per thread
 
 template <int NT>
 struct TileDesc {
   i64 shape0, shape1;
-  i64 tiles0;  // ceil(shape0 / kTile)
+  i64 tiles0;  // ceil(shape0 / tile edge)
   i64 ntiles;
   i64 s0[NT], s1[NT];
   u32 dim1_mask;
 };
 
+typedef u32 (*PwTileSmem)[kPwTile + 1];
+
 template <class F, int K = 0>
 __device__ __forceinline__ void tile_load_inputs(const PwPtrs<PwTraits<F>::NT>& ptrs, const TileDesc<PwTraits<F>::NT>& d,
-                                                 i64 t0, i64 t1, u32 (*smem)[kTile][kTile + 1],
-                                                 u32 (&v)[kTile / kTileRows][F::NIN > 0 ? F::NIN : 1]) {
+                                                 i64 t0, i64 t1, PwTileSmem smem,
+                                                 u32 (&v)[kTileElems][F::NIN > 0 ? F::NIN : 1]) {
   if constexpr (K < F::NIN) {
     constexpr int T = F::NOUT + K;
     constexpr bool BYTE = PwTraits<F>::in_byte(K);
     const int tx = threadIdx.x, ty = threadIdx.y;
     if ((d.dim1_mask >> T) & 1u) {
-      // read with tx along dimension 1, park as smem[i0][i1]
+      __syncthreads();  // the tile is free (previous operand gathered)
 #pragma unroll
-      for (int r = 0; r < kTile / kTileRows; ++r) {
-        const i64 i0 = t0 + ty + r * kTileRows, i1 = t1 + tx;
-        u32 x = 0;
-        if (i0 < d.shape0 && i1 < d.shape1) x = load_elem<BYTE>(ptrs.p[T], i0 * d.s0[T] + i1 * d.s1[T]);
-        smem[K][ty + r * kTileRows][tx] = x;
-      }
+      for (int a = 0; a < kTileXR; ++a)
+#pragma unroll
+        for (int r = 0; r < kTileYR; ++r) {
+          const i64 i0 = t0 + ty + r * kTileRows, i1 = t1 + tx + a * kTileX;
+          u32 x = 0;
+          if (i0 < d.shape0 && i1 < d.shape1) x = load_elem<BYTE>(ptrs.p[T], i0 * d.s0[T] + i1 * d.s1[T]);
+          smem[ty + r * kTileRows][tx + a * kTileX] = x;
+        }
+      __syncthreads();
+#pragma unroll
+      for (int a = 0; a < kTileXR; ++a)
+#pragma unroll
+        for (int r = 0; r < kTileYR; ++r) v[a * kTileYR + r][K] = smem[tx + a * kTileX][ty + r * kTileRows];
     } else {
 #pragma unroll
-      for (int r = 0; r < kTile / kTileRows; ++r) {
-        const i64 i0 = t0 + tx, i1 = t1 + ty + r * kTileRows;
-        u32 x = 0;
-        if (i0 < d.shape0 && i1 < d.shape1) x = load_elem<BYTE>(ptrs.p[T], i0 * d.s0[T] + i1 * d.s1[T]);
-        v[r][K] = x;
-      }
+      for (int a = 0; a < kTileXR; ++a)
+#pragma unroll
+        for (int r = 0; r < kTileYR; ++r) {
+          const i64 i0 = t0 + tx + a * kTileX, i1 = t1 + ty + r * kTileRows;
+          u32 x = 0;
+          if (i0 < d.shape0 && i1 < d.shape1) x = load_elem<BYTE>(ptrs.p[T], i0 * d.s0[T] + i1 * d.s1[T]);
+          v[a * kTileYR + r][K] = x;
+        }
+    }
+    if constexpr (BYTE) {
+#pragma unroll
+      for (int e = 0; e < kTileElems; ++e) v[e][K] = v[e][K] != 0u ? 1u : 0u;
     }
     tile_load_inputs<F, K + 1>(ptrs, d, t0, t1, smem, v);
   }
 }
 template <class F, int K = 0>
-__device__ __forceinline__ void tile_gather_inputs(const TileDesc<PwTraits<F>::NT>& d, u32 (*smem)[kTile][kTile + 1],
-                                                   u32 (&v)[kTile / kTileRows][F::NIN > 0 ? F::NIN : 1]) {
-  if constexpr (K < F::NIN) {
-    constexpr int T = F::NOUT + K;
-    if ((d.dim1_mask >> T) & 1u) {
-#pragma unroll
-      for (int r = 0; r < kTile / kTileRows; ++r) v[r][K] = smem[K][threadIdx.x][threadIdx.y + r * kTileRows];
-    }
-    if constexpr (PwTraits<F>::in_byte(K)) {
-#pragma unroll
-      for (int r = 0; r < kTile / kTileRows; ++r) v[r][K] = v[r][K] != 0u ? 1u : 0u;
-    }
-    tile_gather_inputs<F, K + 1>(d, smem, v);
-  }
-}
-template <class F, int K = 0>
 __device__ __forceinline__ void tile_store_outputs(const PwPtrs<PwTraits<F>::NT>& ptrs, const TileDesc<PwTraits<F>::NT>& d,
-                                                   i64 t0, i64 t1, u32 (*smem)[kTile][kTile + 1],
-                                                   const u32 (&v)[kTile / kTileRows][F::NOUT]) {
+                                                   i64 t0, i64 t1, PwTileSmem smem, const u32 (&v)[kTileElems][F::NOUT]) {
   if constexpr (K < F::NOUT) {
     constexpr bool BYTE = PwTraits<F>::out_byte(K);
     const int tx = threadIdx.x, ty = threadIdx.y;
     if ((d.dim1_mask >> K) & 1u) {
-      __syncthreads();  // previous use of smem[0] is finished
+      __syncthreads();  // previous use of the tile is finished
 #pragma unroll
-      for (int r = 0; r < kTile / kTileRows; ++r) smem[0][tx][ty + r * kTileRows] = v[r][K];
+      for (int a = 0; a < kTileXR; ++a)
+#pragma unroll
+        for (int r = 0; r < kTileYR; ++r) smem[tx + a * kTileX][ty + r * kTileRows] = v[a * kTileYR + r][K];
       __syncthreads();
 #pragma unroll
-      for (int r = 0; r < kTile / kTileRows; ++r) {
-        const i64 i0 = t0 + ty + r * kTileRows, i1 = t1 + tx;
-        if (i0 < d.shape0 && i1 < d.shape1)
-          store_elem<BYTE>(ptrs.p[K], i0 * d.s0[K] + i1 * d.s1[K], smem[0][ty + r * kTileRows][tx]);
-      }
+      for (int a = 0; a < kTileXR; ++a)
+#pragma unroll
+        for (int r = 0; r < kTileYR; ++r) {
+          const i64 i0 = t0 + ty + r * kTileRows, i1 = t1 + tx + a * kTileX;
+          if (i0 < d.shape0 && i1 < d.shape1)
+            store_elem<BYTE>(ptrs.p[K], i0 * d.s0[K] + i1 * d.s1[K], smem[ty + r * kTileRows][tx + a * kTileX]);
+        }
     } else {
 #pragma unroll
-      for (int r = 0; r < kTile / kTileRows; ++r) {
-        const i64 i0 = t0 + tx, i1 = t1 + ty + r * kTileRows;
-        if (i0 < d.shape0 && i1 < d.shape1) store_elem<BYTE>(ptrs.p[K], i0 * d.s0[K] + i1 * d.s1[K], v[r][K]);
-      }
+      for (int a = 0; a < kTileXR; ++a)
+#pragma unroll
+        for (int r = 0; r < kTileYR; ++r) {
+          const i64 i0 = t0 + tx + a * kTileX, i1 = t1 + ty + r * kTileRows;
+          if (i0 < d.shape0 && i1 < d.shape1)
+            store_elem<BYTE>(ptrs.p[K], i0 * d.s0[K] + i1 * d.s1[K], v[a * kTileYR + r][K]);
+        }
     }
     tile_store_outputs<F, K + 1>(ptrs, d, t0, t1, smem, v);
   }
@@ -433,18 +447,14 @@ __device__ __forceinline__ void tile_store_outputs(const PwPtrs<PwTraits<F>::NT>
 template <class F>
 __device__ __forceinline__ void pw_tile_body(const PwPtrs<PwTraits<F>::NT>& ptrs, const F& f,
                                              const TileDesc<PwTraits<F>::NT>& d) {
-  constexpr int R = kTile / kTileRows;
   constexpr int NS = F::NIN > 0 ? F::NIN : 1;
-  __shared__ u32 smem[NS][kTile][kTile + 1];
+  __shared__ u32 smem[kPwTile][kPwTile + 1];
   for (i64 tile = blockIdx.x; tile < d.ntiles; tile += gridDim.x) {
-    const i64 t0 = (tile % d.tiles0) * kTile, t1 = (tile / d.tiles0) * kTile;
-    u32 vin[R][NS], vout[R][F::NOUT];
-    __syncthreads();  // smem free again (previous tile)
+    const i64 t0 = (tile % d.tiles0) * kPwTile, t1 = (tile / d.tiles0) * kPwTile;
+    u32 vin[kTileElems][NS], vout[kTileElems][F::NOUT];
     tile_load_inputs<F>(ptrs, d, t0, t1, smem, vin);
-    __syncthreads();
-    tile_gather_inputs<F>(d, smem, vin);
 #pragma unroll
-    for (int r = 0; r < R; ++r) f(vin[r], vout[r]);
+    for (int e = 0; e < kTileElems; ++e) f(vin[e], vout[e]);
     tile_store_outputs<F>(ptrs, d, t0, t1, smem, vout);
   }
 }
@@ -460,7 +470,7 @@ __global__ void __launch_bounds__(kBlock)
   pw_strided_body<F, U, IDX>(ptrs, f, d, n);
 }
 template <class F>
-__global__ void __launch_bounds__(kTile* kTileRows)
+__global__ void __launch_bounds__(kTileX* kTileRows)
     pw_tile_kernel(PwPtrs<PwTraits<F>::NT> ptrs, F f, TileDesc<PwTraits<F>::NT> d) {
   pw_tile_body<F>(ptrs, f, d);
 }
