@@ -118,7 +118,13 @@ bool plan_tile(const TwgIterDesc& d, int nt, int tile_edge, PwPlan* plan) {
   if (mask == 0) return false;
   plan->dim1_mask = mask;
   plan->tiles0 = (d.shape[0] + tile_edge - 1) / tile_edge;
-  plan->ntiles = plan->tiles0 * ((d.shape[1] + tile_edge - 1) / tile_edge);
+  plan->tiles1 = (d.shape[1] + tile_edge - 1) / tile_edge;
+  plan->ntiles = plan->tiles0 * plan->tiles1;
+  if (tile_edge == kPwTile) {
+    // the functor kernels walk tiles in 8x8 super-blocks; partial super-blocks leave idle slots
+    plan->sb0 = (plan->tiles0 + kTileSuper - 1) / kTileSuper;
+    plan->ntiles = plan->sb0 * ((plan->tiles1 + kTileSuper - 1) / kTileSuper) * kTileSuper * kTileSuper;
+  }
   plan->grid = (unsigned)std::min<int64_t>(plan->ntiles, 0x7fffffff);
   return true;
 }

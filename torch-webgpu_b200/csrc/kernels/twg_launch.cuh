@@ -45,7 +45,7 @@ struct PwPlan {
   TwgIterDesc d;         // coalesced
   int64_t nunits = 0;    // dense path
   uint32_t dim1_mask = 0;
-  int64_t tiles0 = 0, ntiles = 0;
+  int64_t tiles0 = 0, tiles1 = 0, sb0 = 1, ntiles = 0;
   unsigned grid = 1;
 };
 
@@ -60,6 +60,8 @@ void fill_tile_desc(const PwPlan& p, TileDesc<NT>* td) {
   td->shape0 = p.d.shape[0];
   td->shape1 = p.d.shape[1];
   td->tiles0 = p.tiles0;
+  td->tiles1 = p.tiles1;
+  td->sb0 = p.sb0;
   td->ntiles = p.ntiles;
   for (int t = 0; t < NT; ++t) { td->s0[t] = p.d.strides[t][0]; td->s1[t] = p.d.strides[t][1]; }
   td->dim1_mask = p.dim1_mask;

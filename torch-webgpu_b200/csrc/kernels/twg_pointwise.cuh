@@ -355,19 +355,23 @@ constexpr int kTileRows = 8;
 constexpr int kTileXR = kPwTile / kTileX;     // 2
 constexpr int kTileYR = kPwTile / kTileRows;  // 8
 constexpr int kTileElems = kTileXR * kTileYR; // 16 per thread
+constexpr int kTileSuper = 8;                 // tiles per super-block edge
 
 template <int NT>
 struct TileDesc {
   i64 shape0, shape1;
-  i64 tiles0;  // ceil(shape0 / tile edge)
-  i64 ntiles;
+  i64 tiles0, tiles1;  // ceil(shape / tile edge) along dimension 0 / 1
+  i64 sb0;             // super-blocks along dimension 0 (functor kernels)
+  i64 ntiles;          // CTAs' worth of work: tiles, or padded super-block slots
   i64 s0[NT], s1[NT];
   u32 dim1_mask;
 };
 
 typedef u32 (*PwTileSmem)[kPwTile + 1];
 
-template <class F, int K = 0>
+// INTERIOR: the whole 64x64 tile lies inside the tensor, so no element needs a bounds check.
+// Offsets advance by precomputed per-step deltas instead of two 64-bit multiplies per element.
+template <class F, bool INTERIOR, int K = 0>
 __device__ __forceinline__ void tile_load_inputs(const PwPtrs<PwTraits<F>::NT>& ptrs, const TileDesc<PwTraits<F>::NT>& d,
                                                  i64 t0, i64 t1, PwTileSmem smem,
                                                  u32 (&v)[kTileElems][F::NIN > 0 ? F::NIN : 1]) {
@@ -375,15 +379,19 @@ __device__ __forceinline__ void tile_load_inputs(const PwPtrs<PwTraits<F>::NT>& 
     constexpr int T = F::NOUT + K;
     constexpr bool BYTE = PwTraits<F>::in_byte(K);
     const int tx = threadIdx.x, ty = threadIdx.y;
+    const i64 s0 = d.s0[T], s1 = d.s1[T];
     if ((d.dim1_mask >> T) & 1u) {
-      __syncthreads();  // the tile is free (previous operand gathered)
+      // tx runs along dimension 1: element (i0 = t0 + ty + 8r, i1 = t1 + tx + 32a)
+      const i64 base = (t0 + ty) * s0 + (t1 + tx) * s1;
+      const i64 step_r = kTileRows * s0, step_a = kTileX * s1;
+      __syncthreads();  // the tile is free (previous operand gathered, previous tile stored)
 #pragma unroll
       for (int a = 0; a < kTileXR; ++a)
 #pragma unroll
         for (int r = 0; r < kTileYR; ++r) {
-          const i64 i0 = t0 + ty + r * kTileRows, i1 = t1 + tx + a * kTileX;
           u32 x = 0;
-          if (i0 < d.shape0 && i1 < d.shape1) x = load_elem<BYTE>(ptrs.p[T], i0 * d.s0[T] + i1 * d.s1[T]);
+          if (INTERIOR || (t0 + ty + r * kTileRows < d.shape0 && t1 + tx + a * kTileX < d.shape1))
+            x = load_elem<BYTE>(ptrs.p[T], base + r * step_r + a * step_a);
           smem[ty + r * kTileRows][tx + a * kTileX] = x;
         }
       __syncthreads();
@@ -392,13 +400,16 @@ __device__ __forceinline__ void tile_load_inputs(const PwPtrs<PwTraits<F>::NT>& 
 #pragma unroll
         for (int r = 0; r < kTileYR; ++r) v[a * kTileYR + r][K] = smem[tx + a * kTileX][ty + r * kTileRows];
     } else {
+      // tx runs along dimension 0: element (i0 = t0 + tx + 32a, i1 = t1 + ty + 8r)
+      const i64 base = (t0 + tx) * s0 + (t1 + ty) * s1;
+      const i64 step_a = kTileX * s0, step_r = kTileRows * s1;
 #pragma unroll
       for (int a = 0; a < kTileXR; ++a)
 #pragma unroll
         for (int r = 0; r < kTileYR; ++r) {
-          const i64 i0 = t0 + tx + a * kTileX, i1 = t1 + ty + r * kTileRows;
           u32 x = 0;
-          if (i0 < d.shape0 && i1 < d.shape1) x = load_elem<BYTE>(ptrs.p[T], i0 * d.s0[T] + i1 * d.s1[T]);
+          if (INTERIOR || (t0 + tx + a * kTileX < d.shape0 && t1 + ty + r * kTileRows < d.shape1))
+            x = load_elem<BYTE>(ptrs.p[T], base + a * step_a + r * step_r);
           v[a * kTileYR + r][K] = x;
         }
     }
@@ -406,16 +417,19 @@ __device__ __forceinline__ void tile_load_inputs(const PwPtrs<PwTraits<F>::NT>& 
 #pragma unroll
       for (int e = 0; e < kTileElems; ++e) v[e][K] = v[e][K] != 0u ? 1u : 0u;
     }
-    tile_load_inputs<F, K + 1>(ptrs, d, t0, t1, smem, v);
+    tile_load_inputs<F, INTERIOR, K + 1>(ptrs, d, t0, t1, smem, v);
   }
 }
-template <class F, int K = 0>
+template <class F, bool INTERIOR, int K = 0>
 __device__ __forceinline__ void tile_store_outputs(const PwPtrs<PwTraits<F>::NT>& ptrs, const TileDesc<PwTraits<F>::NT>& d,
                                                    i64 t0, i64 t1, PwTileSmem smem, const u32 (&v)[kTileElems][F::NOUT]) {
   if constexpr (K < F::NOUT) {
     constexpr bool BYTE = PwTraits<F>::out_byte(K);
     const int tx = threadIdx.x, ty = threadIdx.y;
+    const i64 s0 = d.s0[K], s1 = d.s1[K];
     if ((d.dim1_mask >> K) & 1u) {
+      const i64 base = (t0 + ty) * s0 + (t1 + tx) * s1;
+      const i64 step_r = kTileRows * s0, step_a = kTileX * s1;
       __syncthreads();  // previous use of the tile is finished
 #pragma unroll
       for (int a = 0; a < kTileXR; ++a)
@@ -425,37 +439,49 @@ __device__ __forceinline__ void tile_store_outputs(const PwPtrs<PwTraits<F>::NT>
 #pragma unroll
       for (int a = 0; a < kTileXR; ++a)
 #pragma unroll
-        for (int r = 0; r < kTileYR; ++r) {
-          const i64 i0 = t0 + ty + r * kTileRows, i1 = t1 + tx + a * kTileX;
-          if (i0 < d.shape0 && i1 < d.shape1)
-            store_elem<BYTE>(ptrs.p[K], i0 * d.s0[K] + i1 * d.s1[K], smem[ty + r * kTileRows][tx + a * kTileX]);
-        }
+        for (int r = 0; r < kTileYR; ++r)
+          if (INTERIOR || (t0 + ty + r * kTileRows < d.shape0 && t1 + tx + a * kTileX < d.shape1))
+            store_elem<BYTE>(ptrs.p[K], base + r * step_r + a * step_a, smem[ty + r * kTileRows][tx + a * kTileX]);
     } else {
+      const i64 base = (t0 + tx) * s0 + (t1 + ty) * s1;
+      const i64 step_a = kTileX * s0, step_r = kTileRows * s1;
 #pragma unroll
       for (int a = 0; a < kTileXR; ++a)
 #pragma unroll
-        for (int r = 0; r < kTileYR; ++r) {
-          const i64 i0 = t0 + tx + a * kTileX, i1 = t1 + ty + r * kTileRows;
-          if (i0 < d.shape0 && i1 < d.shape1)
-            store_elem<BYTE>(ptrs.p[K], i0 * d.s0[K] + i1 * d.s1[K], v[a * kTileYR + r][K]);
-        }
+        for (int r = 0; r < kTileYR; ++r)
+          if (INTERIOR || (t0 + tx + a * kTileX < d.shape0 && t1 + ty + r * kTileRows < d.shape1))
+            store_elem<BYTE>(ptrs.p[K], base + a * step_a + r * step_r, v[a * kTileYR + r][K]);
     }
-    tile_store_outputs<F, K + 1>(ptrs, d, t0, t1, smem, v);
+    tile_store_outputs<F, INTERIOR, K + 1>(ptrs, d, t0, t1, smem, v);
   }
+}
+
+template <class F, bool INTERIOR>
+__device__ __forceinline__ void pw_tile_one(const PwPtrs<PwTraits<F>::NT>& ptrs, const F& f,
+                                            const TileDesc<PwTraits<F>::NT>& d, i64 t0, i64 t1, PwTileSmem smem) {
+  constexpr int NS = F::NIN > 0 ? F::NIN : 1;
+  u32 vin[kTileElems][NS], vout[kTileElems][F::NOUT];
+  tile_load_inputs<F, INTERIOR>(ptrs, d, t0, t1, smem, vin);
+#pragma unroll
+  for (int e = 0; e < kTileElems; ++e) f(vin[e], vout[e]);
+  tile_store_outputs<F, INTERIOR>(ptrs, d, t0, t1, smem, vout);
 }
 
 template <class F>
 __device__ __forceinline__ void pw_tile_body(const PwPtrs<PwTraits<F>::NT>& ptrs, const F& f,
                                              const TileDesc<PwTraits<F>::NT>& d) {
-  constexpr int NS = F::NIN > 0 ? F::NIN : 1;
   __shared__ u32 smem[kPwTile][kPwTile + 1];
-  for (i64 tile = blockIdx.x; tile < d.ntiles; tile += gridDim.x) {
-    const i64 t0 = (tile % d.tiles0) * kPwTile, t1 = (tile / d.tiles0) * kPwTile;
-    u32 vin[kTileElems][NS], vout[kTileElems][F::NOUT];
-    tile_load_inputs<F>(ptrs, d, t0, t1, smem, vin);
-#pragma unroll
-    for (int e = 0; e < kTileElems; ++e) f(vin[e], vout[e]);
-    tile_store_outputs<F>(ptrs, d, t0, t1, smem, vout);
+  for (i64 slot = blockIdx.x; slot < d.ntiles; slot += gridDim.x) {
+    // Tiles are walked in super-blocks of 8x8, so that the CTAs running side by side touch
+    // neighbouring pieces of the rows they share along dimension 0 and dimension 1 alike.
+    const i64 sb = slot / (kTileSuper * kTileSuper);
+    const int within = (int)(slot % (kTileSuper * kTileSuper));
+    const i64 b0 = (sb % d.sb0) * kTileSuper + within % kTileSuper;
+    const i64 b1 = (sb / d.sb0) * kTileSuper + within / kTileSuper;
+    if (b0 >= d.tiles0 || b1 >= d.tiles1) continue;
+    const i64 t0 = b0 * kPwTile, t1 = b1 * kPwTile;
+    if (t0 + kPwTile <= d.shape0 && t1 + kPwTile <= d.shape1) pw_tile_one<F, true>(ptrs, f, d, t0, t1, smem);
+    else pw_tile_one<F, false>(ptrs, f, d, t0, t1, smem);
   }
 }
 
@@ -470,7 +496,7 @@ __global__ void __launch_bounds__(kBlock)
   pw_strided_body<F, U, IDX>(ptrs, f, d, n);
 }
 template <class F>
-__global__ void __launch_bounds__(kTileX* kTileRows)
+__global__ void __launch_bounds__(kTileX* kTileRows, 5)
     pw_tile_kernel(PwPtrs<PwTraits<F>::NT> ptrs, F f, TileDesc<PwTraits<F>::NT> d) {
   pw_tile_body<F>(ptrs, f, d);
 }
