@@ -69,56 +69,56 @@ def measured_peak() -> tuple[float, str]:
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """SM clock and throttle-reason samples taken while the timed region runs (read-only NVML
+    queries from a background thread every few milliseconds)."""
+    REASONS = {"hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40, "sw_power_cap": 0x4}
 
-    def __init__(self, gpu_index: int):
-        self.gpu = gpu_index
-        self.proc = None
-        self.path = None
+    def __init__(self, cuda_index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.stop_flag = False
+        self.thread = None
+        self.handle = None
+        try:
+            import pynvml
+            self.nvml = pynvml
+            pynvml.nvmlInit()
+            try:
+                uuid = str(torch.cuda.get_device_properties(cuda_index).uuid)
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(cuda_index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.handle = None
+
+    def _run(self) -> None:
+        nv = self.nvml
+        while not self.stop_flag:
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)))
+                query = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+                bits = int(query(self.handle))
+                for name, bit in self.REASONS.items():
+                    if bits & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
 
     def start(self) -> None:
-        try:
-            fd, self.path = tempfile.mkstemp(suffix=".csv")
-            os.close(fd)
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
-                 "-i", str(self.gpu)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
-        except Exception:
-            self.proc = None
+        if self.handle is None:
+            return
+        import threading
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
 
     def stop(self) -> dict:
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.proc is None:
-            return out
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        sm, smax, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        try:
-            for line in Path(self.path).read_text().splitlines():
-                f = [x.strip() for x in line.split(",")]
-                if len(f) < 9:
-                    continue
-                try:
-                    sm.append(float(f[1])); smax.append(float(f[2]))
-                except ValueError:
-                    continue
-                for name, val in zip(names, f[5:9]):
-                    if val.lower().startswith("active"):
-                        reasons.add(name)
-            os.unlink(self.path)
-        except Exception:
-            pass
-        if sm:
-            # under load = the upper half of the samples (the sampler also sees idle gaps)
-            load = sorted(sm)[len(sm) // 2:]
-            out.update(sm_mhz=statistics.median(load), sm_max_mhz=max(smax), reasons=sorted(reasons), samples=len(sm))
+        self.stop_flag = True
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+        out = {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+        if self.samples:
+            out["sm_mhz"] = statistics.median(self.samples)
         return out
 
 
@@ -443,17 +443,26 @@ def run_gpu_arm(args) -> None:
         raise SystemExit("bench.py: no CUDA device; this benchmark has no CPU fallback (use --impl reference for the CPU arm)")
 
     import torch.distributed as dist
+
+    torch.cuda.set_device(local_rank)
+    cuda_dev = torch.device("cuda", local_rank)
+    if world > 1:
+        # NCCL is set up before the webgpu backend is imported: once PrivateUse1 is registered,
+        # torch.accelerator reports "webgpu" and init_process_group rejects a cuda device_id.
+        dist.init_process_group("nccl")
+        warm = torch.zeros(1, device=cuda_dev)
+        dist.all_reduce(warm)
+        torch.cuda.synchronize()
+
     import torch_webgpu
     from torch_webgpu import abi, webgpu_backend
     from torch_webgpu.sharding import global_segment, shard_range
 
-    torch.cuda.set_device(local_rank)
     torch.webgpu.set_device(local_rank)
-    cuda_dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=cuda_dev)
     L = abi.lib()
-    stream = ctypes.c_void_p(torch.webgpu.current_stream_handle(local_rank))
+    # Leg 1 drives the C ABI on torch's current CUDA stream, so the NCCL all-gather of the counts
+    # is ordered after the compaction kernel without a host round trip in between.
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     peak, peak_kind = measured_peak()
 
     lo, hi = shard_range(BATCH, rank, world)
@@ -465,11 +474,13 @@ def run_gpu_arm(args) -> None:
     for t, buf in enumerate(host):
         fill_shard(buf, t, lo, hi)
 
+    token = torch.zeros(1, device=cuda_dev)
+
     def barrier():
         abi.check(L.twg_stream_sync(stream))
         torch.cuda.synchronize()
         if world > 1:
-            dist.barrier()
+            dist.all_reduce(token)  # a barrier that names its device explicitly
             torch.cuda.synchronize()
 
     # ---- leg 1: inputs resident in HBM, C ABI calls ----------------------------------------
@@ -478,7 +489,9 @@ def run_gpu_arm(args) -> None:
         abi.check(L.twg_memcpy_h2d(buf.ptr, h.data_ptr(), 4 * n, stream))
     d_mask = abi.DeviceBuffer(n, local_rank, stream)
     d_out = abi.DeviceBuffer(4 * n, local_rank, stream)
-    d_res = abi.DeviceBuffer(16, local_rank, stream)
+    t_res = torch.zeros(2, dtype=torch.int64, device=cuda_dev)       # [count, status], written by the kernel
+    t_all = torch.zeros(2 * world, dtype=torch.int64, device=cuda_dev)  # every rank's [count, status]
+    h_all = torch.zeros(2 * world, dtype=torch.int64, pin_memory=True)
     ws_bytes = L.twg_masked_select_workspace_bytes(n)
     d_ws = abi.DeviceBuffer(ws_bytes, local_rank, stream)
     h_res = torch.zeros(2, dtype=torch.int64, pin_memory=True)
@@ -500,13 +513,19 @@ def run_gpu_arm(args) -> None:
         abi.check(L.twg_fused_launch(program, ctypes.byref(desc4), ptrs, stream))
         if i is not None:
             ev.record(3 + 2 * i, stream)
-        abi.check(L.twg_masked_select_f32(ctypes.byref(desc2), dev_in[0].ptr, d_mask.ptr, d_out.ptr, d_res.ptr, d_ws.ptr,
-                                          ws_bytes, stream))
-        abi.check(L.twg_memcpy_d2h(h_res.data_ptr(), d_res.ptr, 16, stream, 1))
-        if int(h_res[1]) != 0:
-            raise RuntimeError(f"masked_select reported device status {int(h_res[1])}")
-        offset, total, counts = global_segment(int(h_res[0]), cuda_dev)
-        counts_seen.append((offset, total))
+        abi.check(L.twg_masked_select_f32(ctypes.byref(desc2), dev_in[0].ptr, d_mask.ptr, d_out.ptr, t_res.data_ptr(),
+                                          d_ws.ptr, ws_bytes, stream))
+        if world > 1:
+            dist.all_gather_into_tensor(t_all, t_res)   # 16 bytes per rank over NVLink
+        else:
+            t_all.copy_(t_res)
+        h_all.copy_(t_all, non_blocking=True)
+        torch.cuda.current_stream().synchronize()        # the step's one host sync: counts are needed on the host
+        counts = h_all[0::2].tolist()
+        if any(int(v) != 0 for v in h_all[1::2].tolist()):
+            raise RuntimeError(f"masked_select reported device status {h_all[1::2].tolist()}")
+        h_res[0] = counts[rank]
+        counts_seen.append((sum(counts[:rank]), sum(counts)))
 
     for _ in range(warmup):
         step(None)
@@ -538,6 +557,7 @@ def run_gpu_arm(args) -> None:
     for b_ in dev_in:
         b_.free()
     ops = per_op_table(abi, stream, peak) if world == 1 and not args.no_ops else None
+    stream = ctypes.c_void_p(torch.webgpu.current_stream_handle(local_rank))  # leg 2 runs on the backend's own stream
     abi.check(L.twg_empty_cache(local_rank))
 
     # ---- leg 2: end to end through the public API with host buffers ---------------------------
@@ -605,7 +625,7 @@ def run_gpu_arm(args) -> None:
             line["cpu_baseline"] = run_cpu_baseline()
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.barrier()
+        barrier()
         dist.destroy_process_group()
 
 

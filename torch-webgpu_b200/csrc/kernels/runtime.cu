@@ -724,7 +724,14 @@ struct Staging {
   bool ready = false;
   int next = 0;
 };
-static Staging g_stage;
+// one ring per device: CUDA events belong to the device they were created on
+static Staging g_stage[kMaxDevices];
+
+static Staging& staging_for_current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = 0;
+  return g_stage[dev];
+}
 
 static int staging_init(Staging& st) {
   if (st.ready) return TWG_OK;
@@ -756,7 +763,7 @@ extern "C" int twg_memcpy_h2d(void* dst_dev, const void* src_host, size_t nbytes
     TWG_CUDA(cudaMemcpyAsync(dst_dev, src_host, nbytes, cudaMemcpyHostToDevice, s));
     return TWG_OK;
   }
-  Staging& st = g_stage;
+  Staging& st = staging_for_current_device();
   std::lock_guard<std::mutex> lock(st.mu);
   if (int rc = staging_init(st)) return rc;
   const char* src = static_cast<const char*>(src_host);
@@ -783,7 +790,7 @@ extern "C" int twg_memcpy_d2h(void* dst_host, const void* src_dev, size_t nbytes
     if (blocking) TWG_CUDA(cudaStreamSynchronize(s));
     return TWG_OK;
   }
-  Staging& st = g_stage;
+  Staging& st = staging_for_current_device();
   std::lock_guard<std::mutex> lock(st.mu);
   if (int rc = staging_init(st)) return rc;
   const char* src = static_cast<const char*>(src_dev);
