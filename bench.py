@@ -43,6 +43,10 @@ SLAB = ROWS * COLS
 SEED = 4
 FALLBACK_HBM_GBS = 6650.0
 CHAIN_BYTES_PER_ELEM = 13  # read a, b, c (3 x 4 B), write the bool mask (1 B)
+# dram__bytes_read.sum + dram__bytes_write.sum of the fused-chain kernel per element, from the ncu
+# capture summarised in profiles/chain_kernel_ncu.md (2^27 elements; DRAM traffic of this streaming
+# kernel is proportional to the element count, so it is scaled to the elements of a launch)
+CHAIN_DRAM_BYTES_PER_ELEM = 12.89
 
 
 def slab_seed(tensor_id: int, batch_index: int) -> int:
@@ -601,13 +605,7 @@ def run_gpu_arm(args) -> None:
 
     if rank == 0:
         achieved = CHAIN_BYTES_PER_ELEM * n / (fused_ms_max * 1e-3) / 1e9
-        traffic = None
-        tfile = REPO / "profiles" / "chain_kernel_traffic.json"
-        if tfile.exists():
-            try:
-                traffic = float(json.loads(tfile.read_text())["dram_bytes_per_element"]) * n
-            except Exception:
-                traffic = None
+        traffic = CHAIN_DRAM_BYTES_PER_ELEM * n
         line = {
             "metric": "Gelem/s of the compiled chain + masked_select", "value": value, "unit": "Gelem/s", "n_gpus": world,
             "steps": steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
