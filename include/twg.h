@@ -176,6 +176,24 @@ int twg_bitwise_and(const TwgIterDesc* desc, int itemsize, int is_bool, const vo
 size_t twg_masked_select_workspace_bytes(int64_t numel);
 int twg_masked_select_f32(const TwgIterDesc* desc, const float* src, const uint8_t* mask, float* out,
                           int64_t* result_dev, void* workspace, size_t workspace_bytes, void* stream);
+/* No counterpart in the reference.  masked_select for callers that cannot allocate device memory
+ * and therefore have no workspace to hand to twg_masked_select_f32: a host framework whose own
+ * allocator owns the whole device and rejects a foreign cudaMalloc, a plugin that receives input
+ * and output buffers and nothing else, a latency-critical loop that must stay clear of
+ * cudaMalloc's implicit synchronisation.  The scratch is a fixed array inside the library image
+ * (about 513 KB of every GPU that loads the library, held until the process exits), sized for at
+ * most twg_masked_select_static_max_numel() = 2^28 broadcast elements; larger requests fail with
+ * TWG_ERR_UNSUPPORTED and a message naming the limit.  The call allocates nothing (no cudaMalloc,
+ * no cudaFree, no allocating library routine); inputs, `out` (room for numel elements) and
+ * `result_dev` (two int64) still come from the caller, with the same meaning as above.
+ * The first call on a device looks up the array's device address; make that first call outside
+ * any stream capture.  All calls on a device share the one array, which keeps the previous
+ * call's contents: each call clears what it needs on `stream` before its kernel, so calls that
+ * are ordered on the GPU are fine, while two calls that can overlap on the GPU (different
+ * streams without a dependency, different host threads) race on it and corrupt each other. */
+int64_t twg_masked_select_static_max_numel(void);
+int twg_masked_select_f32_static(const TwgIterDesc* desc, const float* src, const uint8_t* mask, float* out,
+                                 int64_t* result_dev, void* stream);
 /* Test hook for the bounded wait.  polls > 0: every look-back wait gives up after `polls` polls.
  * polls < 0: additionally the first tile never publishes its count (a flag nothing sets), so the
  * tiles that depend on it run out of polls after |polls| and result[1] becomes TWG_ERR_TIMEOUT;

@@ -15,6 +15,7 @@
 #include "twg_launch.cuh"
 
 #include <atomic>
+#include <mutex>
 #include <cstdlib>
 #include <string>
 
@@ -477,4 +478,65 @@ extern "C" int twg_masked_select_f32(const TwgIterDesc* desc, const float* src, 
     g_last_path = kPathStrided64;
   }
   return TWG_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// masked_select without any allocation by anybody.
+//
+// twg_masked_select_f32 needs a scratch buffer (ticket counter + one descriptor per chunk) that
+// the caller has to provide, which normally means the caller allocates device memory.  Some
+// callers cannot: a host framework whose own allocator has reserved the whole device and which
+// treats a foreign cudaMalloc as a failure; a plugin that is handed input and output buffers and
+// nothing else, with no way to ask its host for more; a latency-critical loop that must not hit
+// the implicit device synchronisation of cudaMalloc / cudaFree.  For them the scratch lives in
+// the library image itself, as a file-scope __device__ array of fixed size.  Every GPU that loads
+// the library holds these 513 KB until the process exits, used or not.
+//
+// The array's name below is only meaningful in device code.  On the host it is a stand-in symbol,
+// not a device address, so its address is looked up once per device with cudaGetSymbolAddress
+// (with that device current) and the looked-up pointer is what the kernels receive.
+// ------------------------------------------------------------------------------------------
+namespace twg {
+
+constexpr int64_t kMsStaticMaxNumel = int64_t(1) << 28;
+constexpr size_t kMsStaticBytes = kMsHeaderBytes + (size_t)(kMsStaticMaxNumel / kMsRound) * sizeof(u64);
+
+static __device__ __align__(256) unsigned char g_ms_static_scratch[kMsStaticBytes];
+
+static std::mutex g_ms_static_mu;
+static void* g_ms_static_ptr[64] = {};  // per device ordinal; nullptr = not looked up yet
+
+// Device address of the scratch array on the current device (looked up on first use).
+static int ms_static_scratch(void** out) {
+  int dev = 0;
+  TWG_CUDA(cudaGetDevice(&dev));
+  TWG_REQUIRE(dev >= 0 && dev < 64, "twg_masked_select_f32_static: device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_ms_static_mu);
+  if (g_ms_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    TWG_CUDA(cudaGetSymbolAddress(&p, g_ms_static_scratch));
+    TWG_REQUIRE(p != nullptr && is_aligned(p, 256), "twg_masked_select_f32_static: bad scratch address %p", p);
+    g_ms_static_ptr[dev] = p;
+  }
+  *out = g_ms_static_ptr[dev];
+  return TWG_OK;
+}
+
+}  // namespace twg
+
+extern "C" int64_t twg_masked_select_static_max_numel(void) { return twg::kMsStaticMaxNumel; }
+
+extern "C" int twg_masked_select_f32_static(const TwgIterDesc* desc, const float* src, const uint8_t* mask, float* out,
+                                            int64_t* result_dev, void* stream) {
+  if (int rc = check_desc(desc, 2)) return rc;
+  if (desc->numel > kMsStaticMaxNumel)
+    return set_error(TWG_ERR_UNSUPPORTED,
+                     "twg_masked_select_f32_static: %lld elements exceed the %lld this entry point's built-in scratch "
+                     "is sized for; use twg_masked_select_f32 with a caller-provided workspace",
+                     (long long)desc->numel, (long long)kMsStaticMaxNumel);
+  void* scratch = nullptr;
+  if (int rc = ms_static_scratch(&scratch)) return rc;
+  // Same kernels, same clearing of the part of the scratch that must start at zero (done on
+  // `stream` by the call below); only where the scratch comes from differs.
+  return twg_masked_select_f32(desc, src, mask, out, result_dev, scratch, kMsStaticBytes, stream);
 }

@@ -104,6 +104,8 @@ SIGNATURES = {
     "twg_masked_select_f32": (c_int, [POINTER(IterDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_size_t, c_void_p]),
     "twg_masked_select_set_poll_budget": (c_int, [c_int64]),
+    "twg_masked_select_static_max_numel": (c_int64, []),
+    "twg_masked_select_f32_static": (c_int, [POINTER(IterDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "twg_fused_compile": (c_int, [POINTER(FusedInstr), c_int, POINTER(c_void_p)]),
     "twg_fused_kind": (c_int, [c_void_p, POINTER(c_int)]),
     "twg_fused_launch": (c_int, [c_void_p, POINTER(IterDesc), POINTER(c_void_p), c_void_p]),
