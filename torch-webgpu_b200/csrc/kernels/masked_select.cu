@@ -194,13 +194,21 @@ __global__ void __launch_bounds__(kMsThreads, 4)
                                                                (bytes_to_nibble(q.z) << 8) | (bytes_to_nibble(q.w) << 12));
     }
   } else {
+    // one word of bits = 32 consecutive elements; with a row mask and rows that are a multiple
+    // of 32 long, all of them share one row flag
+    const bool row_words = ROWMASK && full_chunk && (row_len.d % 32u) == 0u;
     for (int g = threadIdx.x; g < CH * (kMsRound / 32); g += kMsThreads) {
       u32 word = 0;
+      if (row_words) {
+        word = ld_b8(mask + row_len.div((u32)(chunk_base + (i64)g * 32))) != 0u ? 0xffffffffu : 0u;
+        c += word & 32u;
+      } else {
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const u32 w = mask_quad<ROWMASK>(mask, chunk_base + ((i64)g * 8 + k) * 4, n, row_len);
-        c += __popc(w);
-        word |= bytes_to_nibble(w) << (4 * k);
+        for (int k = 0; k < 8; ++k) {
+          const u32 w = mask_quad<ROWMASK>(mask, chunk_base + ((i64)g * 8 + k) * 4, n, row_len);
+          c += __popc(w);
+          word |= bytes_to_nibble(w) << (4 * k);
+        }
       }
       bits[g] = word;
     }
