@@ -351,6 +351,38 @@ def per_op_table(abi, stream, peak: float) -> dict:
     ms = time_op(abi, stream, run, iters=10)
     k = int(res.download(np.int64, 2, stream)[0])
     put("masked_select_rowmask_16384x1", 4 * n2 + r + 4 * k, ms, f"k={k}; broadcast mask through the strided path")
+
+    # predicate + select: mask kernel then masked_select (two launches) against the one-launch form
+    g = torch.Generator().manual_seed(4)
+    for buf in (dx, dy):
+        buf.upload(torch.randn(n2, generator=g).numpy(), stream)
+    dc = abi.DeviceBuffer(4 * n2)
+    dc.upload(torch.randn(n2, generator=g).numpy(), stream)
+    F = abi
+    positive = [(F.F_INPUT_F32, 0, 0, 0.0), (F.F_CONST_F32, 0, 0, 0.0), (F.F_GT, 0, 1, 0.0), (F.F_OUTPUT, 2, 0, 0.0)]
+    for name, prog, nin in (("chain", abi.CHAIN_MASK_PROGRAM, 3), ("positive", positive, 1)):
+        handle = abi.fused_compile(prog)
+        ins = [dx, dy, dc][:nin]
+        dmask = dense_desc(1 + nin, n2)
+        mask_ptrs = (ctypes.c_void_p * (1 + nin))(dm.ptr, *[i.ptr for i in ins])
+        in_ptrs = (ctypes.c_void_p * nin)(*[i.ptr for i in ins])
+
+        def two_launches():
+            abi.check(L.twg_fused_launch(handle, ctypes.byref(dmask), mask_ptrs, stream))
+            abi.check(L.twg_masked_select_f32(ctypes.byref(dsel), dx.ptr, dm.ptr, dz.ptr, res.ptr, ws.ptr, ws_bytes, stream))
+
+        def one_launch():
+            abi.check(L.twg_fused_select_f32(handle, 0, n2, in_ptrs, dz.ptr, res.ptr, ws.ptr, ws_bytes, stream))
+
+        ms2 = time_op(abi, stream, two_launches, iters=10)
+        k2 = int(res.download(np.int64, 2, stream)[0])
+        ms1 = time_op(abi, stream, one_launch, iters=10)
+        k1, status = (int(v) for v in res.download(np.int64, 2, stream))
+        if k1 != k2 or status != 0:
+            raise RuntimeError(f"fused select kept {k1} elements (status {status}), the two-launch form {k2}")
+        put(f"select_{name}_two_launches", (4 * nin + 1) * n2 + 5 * n2 + 4 * k2, ms2, f"k={k2}; mask written and read back")
+        put(f"select_{name}_one_launch", 4 * nin * n2 + 4 * k1, ms1, f"k={k1}; no mask in memory")
+        abi.check(L.twg_fused_release(handle))
     return table
 
 

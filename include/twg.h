@@ -241,6 +241,16 @@ int twg_fused_kind(const TwgFusedProgram* p, int* kind);
 /* desc operands: outputs (slot order) first, then inputs (slot order).  ptrs likewise. */
 int twg_fused_launch(const TwgFusedProgram* p, const TwgIterDesc* desc, void* const* ptrs, void* stream);
 int twg_fused_release(TwgFusedProgram* p);
+/* Fused predicate + select: out = inputs[src_input][ prog(inputs) ] in ONE pass, for a program
+ * that is a predicate (exactly one bool output over dense f32 inputs of `numel` elements each,
+ * 16-byte aligned).  The mask never reaches memory: the kernel reads every input once and writes
+ * only the selected values, instead of the fused kernel writing the mask and masked_select
+ * (CPU fallback in the reference, csrc/bindings.cpp:42) reading it and src again.
+ * out, result_dev, workspace and the bounded look-back behave as in twg_masked_select_f32.
+ * TWG_ERR_UNSUPPORTED (program is not a predicate, an input is misaligned, no kernel for this
+ * src_input) means: run twg_fused_launch followed by twg_masked_select_f32 instead. */
+int twg_fused_select_f32(const TwgFusedProgram* p, int src_input, int64_t numel, const void* const* inputs,
+                         float* out, int64_t* result_dev, void* workspace, size_t workspace_bytes, void* stream);
 /* Path of the NVRTC shared library to load on first use (default: the loader's search path for
  * libnvrtc.so.12, then /usr/local/cuda/lib64).  Honoured only before the first NVRTC build. */
 int twg_fused_set_nvrtc_path(const char* path);

@@ -338,6 +338,68 @@ def test_fused_program_compiled_at_run_time(abi):
         assert_bit_equal(flag, oracle.compare("gt", oracle.binary("mul", got_g, np.broadcast_to(y, x.shape).copy()), 0.5), "fused flag")
 
 
+@pytest.mark.parametrize("n", [1, 5, 4095, 8192, 8193, 100003, (1 << 22) + 7])
+def test_fused_select_equals_mask_then_masked_select(abi, n):
+    a, bb, c = rnd(n, 85, -3, 3), rnd(n, 86, -3, 3), rnd(n, 87, -3, 3)
+    a[::5] = 0.0
+    (m,), _ = abi.fused(abi.CHAIN_MASK_PROGRAM, [a, bb, c], [np.bool_])
+    sel, kind = abi.fused_select(abi.CHAIN_MASK_PROGRAM, [a, bb, c], 0)
+    assert kind == "aot"
+    assert_bit_equal(sel, abi.masked_select(a, m), "fused select vs mask + masked_select")
+    assert_bit_equal(sel, oracle.masked_select(a, m), "fused select vs oracle on the same mask")
+
+
+def test_fused_select_with_a_predicate_compiled_at_run_time(abi):
+    F = abi
+    # keep y where x * y > 0.25 (selected source is the second input)
+    prog = [(F.F_INPUT_F32, 0, 0, 0.0), (F.F_INPUT_F32, 1, 0, 0.0), (F.F_MUL, 0, 1, 0.0), (F.F_CONST_F32, 0, 0, 0.25),
+            (F.F_GT, 2, 3, 0.0), (F.F_OUTPUT, 4, 0, 0.0)]
+    for n in (3, 70001, 1 << 21):
+        x, y = rnd(n, 88), rnd(n, 89)
+        sel, kind = abi.fused_select(prog, [x, y], 1)
+        assert kind == "nvrtc"
+        m = oracle.compare("gt", oracle.binary("mul", x, y), 0.25)
+        assert_bit_equal(sel, oracle.masked_select(y, m), f"fused select n={n}")
+    # all kept / none kept
+    x = np.full(50000, 2.0, np.float32)
+    sel, _ = abi.fused_select(prog, [x, x], 0)
+    assert_bit_equal(sel, x, "all kept")
+    sel, _ = abi.fused_select(prog, [x, -x], 0)
+    assert sel.size == 0
+
+
+def test_fused_select_bounded_wait_reports_timeout(abi):
+    """Same look-back, same rule: chunk 0 withholds its count, the wait runs out and says so."""
+    n = 64 * 8192
+    a, bb, c = rnd(n, 91, -3, 3), rnd(n, 92, -3, 3), rnd(n, 93, -3, 3)
+    a[::3] = 0.0
+    try:
+        abi.check(abi.lib().twg_masked_select_set_poll_budget(-200))
+        with pytest.raises(abi.TwgError) as err:
+            abi.fused_select(abi.CHAIN_MASK_PROGRAM, [a, bb, c], 0)
+        assert err.value.code == abi.TWG_ERR_TIMEOUT
+    finally:
+        abi.check(abi.lib().twg_masked_select_set_poll_budget(0))
+    (m,), _ = abi.fused(abi.CHAIN_MASK_PROGRAM, [a, bb, c], [np.bool_])
+    sel, _ = abi.fused_select(abi.CHAIN_MASK_PROGRAM, [a, bb, c], 0)
+    assert_bit_equal(sel, oracle.masked_select(a, m), "after timeout")
+
+
+def test_fused_select_rejects_programs_that_are_not_one_predicate(abi):
+    F = abi
+    two_outputs = [(F.F_INPUT_F32, 0, 0, 0.0), (F.F_CONST_F32, 0, 0, 0.0), (F.F_GT, 0, 1, 0.0), (F.F_RELU, 0, 0, 0.0),
+                   (F.F_OUTPUT, 2, 0, 0.0), (F.F_OUTPUT, 3, 1, 0.0)]
+    x = rnd(1000, 90)
+    with pytest.raises(abi.TwgError):
+        abi.fused_select(two_outputs, [x], 0)
+    float_output = [(F.F_INPUT_F32, 0, 0, 0.0), (F.F_RELU, 0, 0, 0.0), (F.F_OUTPUT, 1, 0, 0.0)]
+    with pytest.raises(abi.TwgError):
+        abi.fused_select(float_output, [x], 0)
+    pred = [(F.F_INPUT_F32, 0, 0, 0.0), (F.F_CONST_F32, 0, 0, 0.0), (F.F_GT, 0, 1, 0.0), (F.F_OUTPUT, 2, 0, 0.0)]
+    with pytest.raises(abi.TwgError):
+        abi.fused_select(pred, [x], 3)
+
+
 def test_fused_rejects_malformed_programs(abi):
     F = abi
     with pytest.raises(abi.TwgError):

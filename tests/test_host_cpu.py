@@ -101,6 +101,13 @@ def test_nvrtc_builds_generated_source_without_a_gpu(abi):
             pytest.skip(f"NVRTC is not installed here: {e}")
         raise
     assert abi.fused_kind(h) == "nvrtc"
+    # a predicate (one bool output over f32 inputs) also gets its select kernels, one per input
+    pred = [(abi.F_INPUT_F32, 0, 0, 0.0), (abi.F_INPUT_F32, 1, 0, 0.0), (abi.F_MUL, 0, 1, 0.0),
+            (abi.F_CONST_F32, 0, 0, 0.25), (abi.F_GT, 2, 3, 0.0), (abi.F_OUTPUT, 4, 0, 0.0)]
+    assert abi.fused_kind(abi.fused_compile(pred)) == "nvrtc"
+    src = ctypes.c_char_p()
+    abi.check(abi.lib().twg_fused_source(abi.fused_compile(pred), ctypes.byref(src)))
+    assert b"twg_fused_select_0" in src.value and b"twg_fused_select_1" in src.value
 
 
 @pytest.mark.skipif(torch.cuda.is_available(), reason="checks the behaviour of a machine without a GPU")
@@ -154,6 +161,20 @@ def test_compile_backend_partitions_the_chain_into_one_ahead_of_time_program(abi
     assert len(inputs) == 3 and len(outs) == 1 and prog.out_dtypes() == [11]
     handle = torch.ops.webgpu.compile_fused(*prog.columns())
     assert torch.ops.webgpu.fused_kind(handle) == 0
+
+    # a mask that feeds only masked_select(a, mask) is recognised as a fused select on input 0 ...
+    def select_only(a, b, c):
+        y = torch.relu(torch.nn.functional.silu(a + b) + c)
+        return torch.masked_select(a, torch.bitwise_and(torch.eq(y, 0), torch.ne(a, 0)))
+
+    with FakeTensorMode(shape_env=torch.fx.experimental.symbolic_shapes.ShapeEnv()):
+        gm_sel = make_fx(select_only)(*[torch.empty(4, 8, 8, device="webgpu") for _ in range(3)])
+    (grp,) = wc.partition(gm_sel.graph)
+    prog_s, inputs_s, outs_s = wc.build_program(grp)
+    sel_node, src_index = wc.select_pattern(grp, inputs_s, outs_s)
+    assert sel_node.target is torch.ops.aten.masked_select.default and src_index == 0
+    # ... but not when the mask is also returned
+    assert wc.select_pattern(groups[0], inputs, outs) is None
 
     # a consumer in the middle splits the run; different iteration shapes do not fuse
     def split(a, b):

@@ -267,6 +267,46 @@ def test_config5_compiled_chain():
     assert torch.equal(torch.bitwise_and(torch.eq(y, 0), torch.ne(da, 0)).cpu(), m_cpu)
 
 
+def test_compiled_chain_with_the_select_in_the_graph_is_one_launch():
+    """With masked_select captured in the graph and its mask used nowhere else, predicate and
+    compaction run as one kernel; the result equals the two-launch form bit for bit."""
+    import torch._dynamo
+    import torch_webgpu
+    from torch_webgpu import webgpu_backend
+    from torch_webgpu.compiler import webgpu_compiler as wc
+
+    def chain(a, b, c):
+        y = torch.relu(F.silu(a + b) + c)
+        m = torch.bitwise_and(torch.eq(y, 0), torch.ne(a, 0))
+        return torch.masked_select(a, m)
+
+    g = torch.Generator().manual_seed(5)
+    a, b, c = (torch.randn(2, 4096, 4096, generator=g) for _ in range(3))
+    da, db, dc = a.to("webgpu"), b.to("webgpu"), c.to("webgpu")
+    old = torch._dynamo.config.capture_dynamic_output_shape_ops
+    torch._dynamo.config.capture_dynamic_output_shape_ops = True
+    try:
+        torch._dynamo.reset()
+        torch_webgpu._C.reset_launch_count()
+        one = torch.compile(chain, backend=webgpu_backend)(da, db, dc)
+        assert wc.last_compile_report["fused_selects"] == 1 and wc.last_compile_report["kinds"] == ["aot"]
+        assert torch_webgpu._C.launch_count() == 1
+        torch._dynamo.reset()
+        two = torch.compile(chain, backend=webgpu_backend, options={"fuse_select": False})(da, db, dc)
+        assert wc.last_compile_report["fused_selects"] == 0
+        assert one.dim() == 1 and torch.equal(one.cpu(), two.cpu())
+        # transposed views do not meet the fused kernel's layout rule: same answer by the two-launch route
+        torch._dynamo.reset()
+        ta, tb, tc = (t.transpose(1, 2) for t in (da, db, dc))
+        got = torch.compile(chain, backend=webgpu_backend)(ta, tb, tc)
+        y = torch.relu(F.silu(ta + tb) + tc)
+        eager = torch.masked_select(ta, torch.bitwise_and(torch.eq(y, 0), torch.ne(ta, 0)))
+        assert torch.equal(got.cpu(), eager.cpu())
+    finally:
+        torch._dynamo.config.capture_dynamic_output_shape_ops = old
+        torch._dynamo.reset()
+
+
 @pytest.mark.skipif("torch.cuda.device_count() < 2")
 def test_second_device():
     x = torch.randn(1 << 20)

@@ -65,15 +65,16 @@ def up_to_date(target: Path, stamp: Path, key: str) -> bool:
 
 
 def embed_header(verbose: bool) -> Path:
-    """Turn twg_pointwise.cuh into a raw string literal that fused.cu hands to NVRTC."""
+    """Turn the device headers into raw string literals that fused.cu hands to NVRTC."""
     out_dir = BUILD / "gen"
     out_dir.mkdir(parents=True, exist_ok=True)
-    text = (KERNELS / "twg_pointwise.cuh").read_text()
-    assert ')TWGSRC"' not in text
-    out = out_dir / "twg_pointwise_src.inc"
-    new = 'R"TWGSRC(' + text + ')TWGSRC"\n'
-    if not out.exists() or out.read_text() != new:
-        out.write_text(new)
+    for header in ("twg_pointwise", "twg_compact"):
+        text = (KERNELS / f"{header}.cuh").read_text()
+        assert ')TWGSRC"' not in text
+        out = out_dir / f"{header}_src.inc"
+        new = 'R"TWGSRC(' + text + ')TWGSRC"\n'
+        if not out.exists() or out.read_text() != new:
+            out.write_text(new)
     return out_dir
 
 

@@ -89,6 +89,49 @@ std::vector<at::Tensor> run_fused(int64_t handle, at::TensorList inputs, c10::In
   return outs;
 }
 
+// masked_select(inputs[src_index], program(inputs)) without materialising the mask.  The fused
+// kernel needs dense, equally shaped float32 inputs; any other case (and programs the library has
+// no select form for) runs the program and masked_select one after the other - same result.
+at::Tensor run_fused_select(int64_t handle, at::TensorList inputs, int64_t src_index) {
+  TORCH_CHECK(!inputs.empty() && src_index >= 0 && src_index < static_cast<int64_t>(inputs.size()),
+              "run_fused_select: src_index out of range");
+  auto* program = reinterpret_cast<TwgFusedProgram*>(static_cast<intptr_t>(handle));
+  const at::Tensor& src = inputs[src_index];
+  bool dense = true;
+  for (const auto& t : inputs)
+    dense = dense && t.scalar_type() == at::kFloat && t.is_contiguous() && t.sizes().equals(src.sizes()) &&
+            t.device() == src.device();
+  const int64_t numel = src.numel();
+  if (dense && numel > 0) {
+    const c10::DeviceIndex dev = src.device().index() < 0 ? core::current_device() : src.device().index();
+    core::DeviceScope scope(dev);
+    void* stream = core::current_stream(dev);
+    const size_t ws_bytes = twg_masked_select_workspace_bytes(numel);
+    at::Tensor workspace = at::empty({static_cast<int64_t>(ws_bytes)}, src.options().dtype(at::kByte));
+    at::Tensor result = at::empty({2}, src.options().dtype(at::kLong));
+    at::Tensor out = at::empty({numel}, src.options());
+    std::vector<const void*> ptrs;
+    for (const auto& t : inputs) ptrs.push_back(t.const_data_ptr());
+    const int rc = twg_fused_select_f32(program, static_cast<int>(src_index), numel, ptrs.data(),
+                                        static_cast<float*>(out.data_ptr()), static_cast<int64_t*>(result.data_ptr()),
+                                        workspace.data_ptr(), ws_bytes, stream);
+    if (rc == TWG_OK) {
+      int64_t host[2] = {0, 0};
+      TWG_TORCH_CHECK(twg_memcpy_d2h(host, result.const_data_ptr(), sizeof(host), stream, 1));
+      TORCH_CHECK(host[1] == 0, "torch_webgpu: the fused select's device-side scan failed with status ", host[1]);
+      if (host[0] < numel) {
+        TWG_TORCH_CHECK(twg_trim(out.data_ptr(), static_cast<size_t>(host[0]) * sizeof(float)));
+        out.unsafeGetTensorImpl()->set_sizes_contiguous({host[0]});
+        out.storage().unsafeGetStorageImpl()->set_nbytes(static_cast<size_t>(host[0]) * sizeof(float));
+      }
+      return out;
+    }
+    TORCH_CHECK(rc == TWG_ERR_UNSUPPORTED, "torch_webgpu: ", twg_last_error());
+  }
+  std::vector<at::Tensor> mask = run_fused(handle, inputs, {static_cast<int64_t>(at::kBool)});
+  return at::masked_select(src, mask[0]);
+}
+
 }  // namespace ops
 
 TORCH_LIBRARY(webgpu, m) {
@@ -98,12 +141,14 @@ TORCH_LIBRARY(webgpu, m) {
   m.def("compile_fused(int[] opcodes, int[] a, int[] b, float[] imm) -> int");
   m.def("fused_kind(int handle) -> int");
   m.def("run_fused(int handle, Tensor[] inputs, int[] out_dtypes) -> Tensor[]");
+  m.def("run_fused_select(int handle, Tensor[] inputs, int src_index) -> Tensor");
 }
 TORCH_LIBRARY_IMPL(webgpu, PrivateUse1, m) {
   m.impl("create_buffer", TORCH_FN(ops::create_buffer));
   m.impl("write_buffer", TORCH_FN(ops::write_buffer));
   m.impl("fused_add_relu", TORCH_FN(ops::fused_add_relu));
   m.impl("run_fused", TORCH_FN(ops::run_fused));
+  m.impl("run_fused_select", TORCH_FN(ops::run_fused_select));
 }
 TORCH_LIBRARY_IMPL(webgpu, CatchAll, m) {
   m.impl("create_buffer", TORCH_FN(ops::create_buffer));

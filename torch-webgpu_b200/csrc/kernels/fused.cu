@@ -15,6 +15,7 @@
 #include <string>
 #include <vector>
 
+#include "twg_compact.cuh"
 #include "twg_launch.cuh"
 
 namespace twg {
@@ -22,6 +23,10 @@ namespace twg {
 // The text of twg_pointwise.cuh, embedded at build time for NVRTC.
 static const char kPointwiseHeader[] =
 #include "twg_pointwise_src.inc"
+    ;
+// The text of twg_compact.cuh (fused predicate + select), likewise.
+static const char kCompactHeader[] =
+#include "twg_compact_src.inc"
     ;
 
 // ------------------------------------------------------------------------------------------
@@ -33,6 +38,8 @@ struct Analysis {
   int nin = 0, nout = 0;
   unsigned in_byte_mask = 0, out_byte_mask = 0;
   std::vector<int> type;  // per instruction
+  // a predicate: one bool output over f32 inputs - can drive the fused select
+  bool is_predicate() const { return nout == 1 && out_byte_mask == 1u && in_byte_mask == 0u && nin >= 1; }
 };
 
 static int analyse(const TwgFusedInstr* prog, int n, Analysis* a) {
@@ -124,7 +131,7 @@ static std::string hexf(float f) {
 
 static std::string generate_source(const TwgFusedInstr* prog, int n, const Analysis& a) {
   std::string s;
-  char line[256];
+  char line[512];
   s += "#include \"twg_pointwise.cuh\"\nnamespace twg {\nstruct Prog {\n";
   snprintf(line, sizeof(line),
            "  static constexpr int NIN = %d, NOUT = %d;\n  static constexpr unsigned kInByteMask = %uu, kOutByteMask = %uu;\n",
@@ -184,6 +191,17 @@ static std::string generate_source(const TwgFusedInstr* prog, int n, const Analy
            "extern \"C\" __global__ void __launch_bounds__(kBlock) twg_fused_strided64(PwPtrs<NT> p, StridedDesc<NT, u64> d, i64 n) "
            "{ pw_strided_body<Prog, %d, u64>(p, Prog{}, d, n); }\n", kStridedUnroll);
   s += line;
+  if (a.is_predicate()) {
+    s += "#include \"twg_compact.cuh\"\n";
+    for (int k = 0; k < a.nin; ++k) {
+      snprintf(line, sizeof(line),
+               "extern \"C\" __global__ void __launch_bounds__(kMsThreads) twg_fused_select_%d(PwPtrs<%d> in, float* out, i64 n, "
+               "i64 nchunks, u64* ticket, u64* desc, i64* result, i64 budget) "
+               "{ select_fused_body<Prog, %d>(in, Prog{}, out, n, nchunks, ticket, desc, result, budget); }\n",
+               k, a.nin, k);
+      s += line;
+    }
+  }
   return s;
 }
 
@@ -240,15 +258,42 @@ typedef int (*AotLaunch)(const TwgIterDesc*, void* const*, cudaStream_t);
 template <class F>
 int aot_launch(const TwgIterDesc* d, void* const* ptrs, cudaStream_t s) { return launch_pointwise(F{}, d, ptrs, s); }
 
+// fused predicate + select with src = input 0 (the form the benchmark's chain takes)
+struct SelectArgs {
+  const void* const* inputs;
+  float* out;
+  i64 n, nchunks;
+  unsigned grid;  // persistent CTAs
+  u64 *ticket, *desc;
+  i64* result;
+  i64 budget;
+};
+typedef int (*AotSelect)(const SelectArgs&, cudaStream_t);
+template <class F>
+int aot_select0(const SelectArgs& a, cudaStream_t s) {
+  PwPtrs<F::NIN> in;
+  for (int k = 0; k < F::NIN; ++k) in.p[k] = const_cast<void*>(a.inputs[k]);
+  static bool configured = false;
+  if (!configured) {
+    TWG_CUDA(cudaFuncSetAttribute(select_fused_kernel<F, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSelSmemBytes));
+    configured = true;
+  }
+  select_fused_kernel<F, 0><<<a.grid, kMsThreads, kSelSmemBytes, s>>>(in, F{}, a.out, a.n, a.nchunks, a.ticket, a.desc,
+                                                                       a.result, a.budget);
+  TWG_CHECK_LAUNCH();
+  return TWG_OK;
+}
+
 struct AotEntry {
   const TwgFusedInstr* prog;
   int n;
   AotLaunch launch;
+  AotSelect select0;  // nullptr: no ahead-of-time select for this program
 };
 static const AotEntry kAot[] = {
-    {kProgAddRelu, (int)(sizeof(kProgAddRelu) / sizeof(TwgFusedInstr)), &aot_launch<AotAddRelu>},
-    {kProgChainMask, (int)(sizeof(kProgChainMask) / sizeof(TwgFusedInstr)), &aot_launch<AotChainMask>},
-    {kProgChainMaskY, (int)(sizeof(kProgChainMaskY) / sizeof(TwgFusedInstr)), &aot_launch<AotChainMaskY>},
+    {kProgAddRelu, (int)(sizeof(kProgAddRelu) / sizeof(TwgFusedInstr)), &aot_launch<AotAddRelu>, nullptr},
+    {kProgChainMask, (int)(sizeof(kProgChainMask) / sizeof(TwgFusedInstr)), &aot_launch<AotChainMask>, &aot_select0<AotChainMask>},
+    {kProgChainMaskY, (int)(sizeof(kProgChainMaskY) / sizeof(TwgFusedInstr)), &aot_launch<AotChainMaskY>, nullptr},
 };
 
 static bool same_program(const TwgFusedInstr* a, int na, const TwgFusedInstr* b, int nb) {
@@ -296,6 +341,7 @@ struct Dyn {
   CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream,
                            void**, void**);
   CUresult (*CuGetErrorString)(CUresult, const char**);
+  CUresult (*FuncSetAttribute)(CUfunction, int, int);
 };
 static Dyn g_dyn;
 
@@ -338,7 +384,7 @@ static int load_driver() {
   if (!lib) return set_error(TWG_ERR_CUDA, "cannot load the CUDA driver library libcuda.so.1: %s", dlerror());
   bool ok = sym(lib, "cuModuleLoadData", &d.ModuleLoadData) && sym(lib, "cuModuleUnload", &d.ModuleUnload) &&
             sym(lib, "cuModuleGetFunction", &d.ModuleGetFunction) && sym(lib, "cuLaunchKernel", &d.LaunchKernel) &&
-            sym(lib, "cuGetErrorString", &d.CuGetErrorString);
+            sym(lib, "cuGetErrorString", &d.CuGetErrorString) && sym(lib, "cuFuncSetAttribute", &d.FuncSetAttribute);
   if (!ok) return set_error(TWG_ERR_UNSUPPORTED, "the CUDA driver library lacks a required entry point");
   d.cuda = lib;
   return TWG_OK;
@@ -354,9 +400,9 @@ static int nvrtc_compile(const std::string& source, std::vector<char>* cubin) {
   if (int rc = load_nvrtc()) return rc;
   Dyn& d = g_dyn;
   nvrtcProgram prog = nullptr;
-  const char* headers[] = {kPointwiseHeader};
-  const char* names[] = {"twg_pointwise.cuh"};
-  nvrtcResult r = d.CreateProgram(&prog, source.c_str(), "twg_fused.cu", 1, headers, names);
+  const char* headers[] = {kPointwiseHeader, kCompactHeader};
+  const char* names[] = {"twg_pointwise.cuh", "twg_compact.cuh"};
+  nvrtcResult r = d.CreateProgram(&prog, source.c_str(), "twg_fused.cu", 2, headers, names);
   if (r != 0) return set_error(TWG_ERR_CUDA, "nvrtcCreateProgram failed: %s", d.GetErrorString(r));
   const char* opts[] = {"--gpu-architecture=sm_100a", "--std=c++17", "-lineinfo"};
   r = d.CompileProgram(prog, 3, opts);
@@ -382,6 +428,7 @@ static int nvrtc_compile(const std::string& source, std::vector<char>* cubin) {
 struct DeviceModule {
   CUmodule mod = nullptr;
   CUfunction dense = nullptr, tile = nullptr, strided32 = nullptr, strided64 = nullptr;
+  CUfunction select[TWG_MAX_TENSORS] = {};  // twg_fused_select_<k>, predicates only
 };
 
 }  // namespace twg
@@ -394,6 +441,7 @@ struct TwgFusedProgram {
   std::string source;
   int kind = 0;  // 0 ahead-of-time, 1 NVRTC
   AotLaunch aot = nullptr;
+  AotSelect aot_select0 = nullptr;
   std::vector<char> cubin;
   std::mutex mu;
   std::map<int, DeviceModule> modules;  // per device ordinal
@@ -418,6 +466,16 @@ static int get_module(TwgFusedProgram* p, DeviceModule** out) {
     for (auto& w : want) {
       r = g_dyn.ModuleGetFunction(w.fn, m.mod, w.name);
       if (r != 0) return cu_fail(r, "cuModuleGetFunction");
+    }
+    if (p->an.is_predicate()) {
+      for (int k = 0; k < p->an.nin; ++k) {
+        char name[32];
+        snprintf(name, sizeof(name), "twg_fused_select_%d", k);
+        r = g_dyn.ModuleGetFunction(&m.select[k], m.mod, name);
+        if (r != 0) return cu_fail(r, "cuModuleGetFunction");
+        r = g_dyn.FuncSetAttribute(m.select[k], 8 /* CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES */, (int)kSelSmemBytes);
+        if (r != 0) return cu_fail(r, "cuFuncSetAttribute");
+      }
     }
     it = p->modules.emplace(dev, m).first;
   }
@@ -501,7 +559,7 @@ extern "C" int twg_fused_compile(const TwgFusedInstr* prog, int ninstr, TwgFused
   p->an = an;
   p->source = source;
   for (const AotEntry& e : kAot)
-    if (same_program(prog, ninstr, e.prog, e.n)) { p->aot = e.launch; break; }
+    if (same_program(prog, ninstr, e.prog, e.n)) { p->aot = e.launch; p->aot_select0 = e.select0; break; }
   if (p->aot) {
     p->kind = 0;
   } else {
@@ -551,4 +609,83 @@ extern "C" int twg_fused_launch(const TwgFusedProgram* cp, const TwgIterDesc* de
 extern "C" int twg_fused_release(TwgFusedProgram* p) {
   (void)p;
   return TWG_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// fused predicate + select
+// ------------------------------------------------------------------------------------------
+namespace twg {
+template <int NIN>
+static int jit_select(TwgFusedProgram* p, int src, const SelectArgs& a, cudaStream_t stream) {
+  DeviceModule* m = nullptr;
+  if (int rc = get_module(p, &m)) return rc;
+  PwPtrs<NIN> in;
+  for (int k = 0; k < NIN; ++k) in.p[k] = const_cast<void*>(a.inputs[k]);
+  float* out = a.out;
+  i64 n = a.n, nchunks = a.nchunks, budget = a.budget;
+  u64 *ticket = a.ticket, *desc = a.desc;
+  i64* result = a.result;
+  void* args[] = {&in, &out, &n, &nchunks, &ticket, &desc, &result, &budget};
+  CUresult r = g_dyn.LaunchKernel(m->select[src], a.grid, 1, 1, kMsThreads, 1, 1, kSelSmemBytes,
+                                  reinterpret_cast<CUstream>(stream), args, nullptr);
+  if (r != 0) return cu_fail(r, "cuLaunchKernel");
+  count_launch();
+  return TWG_OK;
+}
+}  // namespace twg
+
+extern "C" int twg_fused_select_f32(const TwgFusedProgram* cp, int src_input, int64_t numel, const void* const* inputs,
+                                    float* out, int64_t* result_dev, void* workspace, size_t workspace_bytes,
+                                    void* stream) {
+  TWG_REQUIRE(cp && inputs && result_dev, "twg_fused_select_f32: null argument");
+  TwgFusedProgram* p = const_cast<TwgFusedProgram*>(cp);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (!p->an.is_predicate())
+    return set_error(TWG_ERR_UNSUPPORTED, "twg_fused_select_f32: the program is not a predicate (one bool output over f32 inputs)");
+  TWG_REQUIRE(src_input >= 0 && src_input < p->an.nin, "twg_fused_select_f32: src_input %d out of range", src_input);
+  TWG_REQUIRE(numel >= 0, "twg_fused_select_f32: negative numel");
+  g_last_path = kPathNone;
+  TWG_CUDA(cudaMemsetAsync(result_dev, 0, 2 * sizeof(int64_t), s));
+  if (numel == 0) return TWG_OK;
+  TWG_REQUIRE(out != nullptr && is_aligned(out, 4), "twg_fused_select_f32: out is null or misaligned");
+  for (int k = 0; k < p->an.nin; ++k) {
+    TWG_REQUIRE(inputs[k] != nullptr, "twg_fused_select_f32: input %d is null", k);
+    if (!is_aligned(inputs[k], 16))
+      return set_error(TWG_ERR_UNSUPPORTED, "twg_fused_select_f32: input %d is not 16-byte aligned", k);
+  }
+  const int64_t nchunks = (numel + kSelChunk - 1) / kSelChunk;
+  TWG_REQUIRE(nchunks <= 0x7fffffff, "twg_fused_select_f32: %lld elements exceed the chunk limit", (long long)numel);
+  const size_t need = kMsHeaderBytes + (size_t)nchunks * sizeof(u64);
+  TWG_REQUIRE(workspace != nullptr && workspace_bytes >= need && is_aligned(workspace, 256),
+              "twg_fused_select_f32: workspace of %zu bytes is smaller than the %zu required or not 256-byte aligned",
+              workspace_bytes, need);
+  TWG_CUDA(cudaMemsetAsync(workspace, 0, need, s));
+  SelectArgs a;
+  a.inputs = inputs;
+  a.out = out;
+  a.n = numel;
+  a.nchunks = nchunks;
+  a.grid = (unsigned)std::min<int64_t>(nchunks, (int64_t)sm_count() * kSelCtasPerSm);
+  a.ticket = ms_use_ticket() ? static_cast<u64*>(workspace) : nullptr;
+  a.desc = reinterpret_cast<u64*>(static_cast<char*>(workspace) + kMsHeaderBytes);
+  a.result = reinterpret_cast<i64*>(result_dev);
+  a.budget = ms_poll_budget();
+  int rc;
+  if (p->aot_select0 && src_input == 0) {
+    rc = p->aot_select0(a, s);
+  } else if (p->kind == 1) {
+    switch (p->an.nin) {
+      case 1: rc = jit_select<1>(p, src_input, a, s); break;
+      case 2: rc = jit_select<2>(p, src_input, a, s); break;
+      case 3: rc = jit_select<3>(p, src_input, a, s); break;
+      case 4: rc = jit_select<4>(p, src_input, a, s); break;
+      case 5: rc = jit_select<5>(p, src_input, a, s); break;
+      case 6: rc = jit_select<6>(p, src_input, a, s); break;
+      default: rc = jit_select<7>(p, src_input, a, s); break;
+    }
+  } else {
+    return set_error(TWG_ERR_UNSUPPORTED, "twg_fused_select_f32: this ahead-of-time program has no select form for input %d", src_input);
+  }
+  if (rc == TWG_OK) g_last_path = kPathDense;
+  return rc;
 }

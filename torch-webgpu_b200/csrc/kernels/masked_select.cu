@@ -13,6 +13,7 @@
 // TWG_ERR_TIMEOUT in result[1], publishes a prefix so that later tiles do not wait on it, and the
 // kernel drains normally.
 #include "twg_launch.cuh"
+#include "twg_compact.cuh"
 
 #include <atomic>
 #include <mutex>
@@ -21,31 +22,11 @@
 
 namespace twg {
 
-constexpr int kMsThreads = 256;
-constexpr int kMsWarps = kMsThreads / 32;
-constexpr int kMsRound = kMsThreads * 16;           // 4096 elements: what one staging pass holds
-constexpr int kMsMaxRounds = 2;                     // double-buffered per-warp totals
-constexpr size_t kMsHeaderBytes = 256;              // ticket counter, padded
+static_assert(kErrTimeout == TWG_ERR_TIMEOUT, "twg_compact.cuh and twg.h disagree");
 
-constexpr u64 kMsAggregate = 1ull << 62;
-constexpr u64 kMsPrefix = 2ull << 62;
-constexpr u64 kMsValueMask = (1ull << 62) - 1ull;
+constexpr int kMsMaxRounds = 2;                     // double-buffered per-warp totals
 
 static std::atomic<long long> g_poll_budget{4000000};
-
-__device__ __forceinline__ u64 ld_relaxed_u64(const u64* p) {
-  u64 v;
-  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_relaxed_u64(u64* p, u64 v) {
-  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-__device__ __forceinline__ u64 warp_sum_u64(u64 v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
-}
 
 struct MsShared {
   float stage[kMsRound];
@@ -54,74 +35,6 @@ struct MsShared {
   i64 tile;
   i64 excl;
 };
-
-// Decoupled look-back in two steps.  lookback_publish (one thread) announces this run's count as
-// soon as it is known; lookback_resolve (warp 0, later) adds up the counts of all earlier runs,
-// publishes the inclusive prefix and returns the exclusive one.  Each poll reads the 32 nearest
-// unresolved predecessors; published aggregates in front of the first unpublished descriptor are
-// consumed at once.
-//
-// A negative poll budget is the test hook "run 0 never publishes": every wait that depends on it
-// must run out after |budget| polls and report TWG_ERR_TIMEOUT instead of hanging.
-__device__ __forceinline__ void lookback_publish(i64 tile, u32 tile_total, u64* desc, i64 poll_budget) {
-  if (tile == 0) {
-    if (poll_budget >= 0) st_relaxed_u64(desc, kMsPrefix | (u64)tile_total);
-  } else {
-    st_relaxed_u64(desc + tile, kMsAggregate | (u64)tile_total);
-  }
-}
-
-__device__ __forceinline__ i64 lookback_resolve(i64 tile, u32 tile_total, u64* desc, i64* result, i64 poll_budget) {
-  const int lane = threadIdx.x & 31;
-  if (tile == 0) return 0;
-  if (poll_budget < 0) poll_budget = -poll_budget;
-  u64 excl = 0;
-  i64 look = tile - 1;  // nearest predecessor not yet accounted for
-  i64 polls = 0;
-  bool timed_out = false;
-  while (true) {
-    const i64 idx = look - lane;
-    const u64 d = idx >= 0 ? ld_relaxed_u64(desc + idx) : kMsPrefix;  // before run 0: prefix of 0
-    const u32 status = (u32)(d >> 62);
-    const u32 invalid = __ballot_sync(0xffffffffu, status == 0u);
-    const u32 prefix = __ballot_sync(0xffffffffu, status == 2u);
-    const int first_invalid = invalid ? __ffs(invalid) - 1 : 32;
-    const int first_prefix = prefix ? __ffs(prefix) - 1 : 32;
-    if (first_prefix < first_invalid) {
-      excl += warp_sum_u64(lane <= first_prefix ? (d & kMsValueMask) : 0ull);
-      break;
-    }
-    if (first_invalid > 0) {
-      excl += warp_sum_u64(lane < first_invalid ? (d & kMsValueMask) : 0ull);
-      look -= first_invalid;
-      if (first_invalid == 32) continue;  // 32 aggregates, no prefix yet: keep walking
-    }
-    if (++polls > poll_budget) { timed_out = true; break; }
-    if (polls > 64) __nanosleep(64);
-  }
-  if (timed_out) {
-    excl = 0;
-    if (lane == 0) result[1] = (i64)TWG_ERR_TIMEOUT;
-  }
-  if (lane == 0) st_relaxed_u64(desc + tile, kMsPrefix | ((excl + (u64)tile_total) & kMsValueMask));
-  return (i64)excl;
-}
-
-// Write `count` staged values to out[base ...].  Runs of a tile are contiguous, so everything
-// between the first and last 16-byte boundary goes out as 128-bit stores.
-__device__ __forceinline__ void flush_stage(const float* stage, float* out, i64 base, u32 count) {
-  float* dst = out + base;
-  const u32 head = min(count, (u32)(((16u - (u32)(reinterpret_cast<unsigned long long>(dst) & 15ull)) & 15u) >> 2));
-  if (threadIdx.x < head) dst[threadIdx.x] = stage[threadIdx.x];
-  const u32 nvec = (count - head) >> 2;
-  float4* dst4 = reinterpret_cast<float4*>(dst + head);
-  for (u32 i = threadIdx.x; i < nvec; i += kMsThreads) {
-    const float* s = stage + head + 4 * i;
-    dst4[i] = make_float4(s[0], s[1], s[2], s[3]);
-  }
-  const u32 tail0 = head + 4 * nvec;
-  if (tail0 + threadIdx.x < count) dst[tail0 + threadIdx.x] = stage[tail0 + threadIdx.x];
-}
 
 // ------------------------------------------------------------------------------------------
 // Dense path: src contiguous and 16-byte aligned; the mask is either a dense bool array (16-byte
@@ -381,10 +294,12 @@ static int dense_chunk_tiles(int64_t n) {
   return ch;
 }
 
+long long ms_poll_budget() { return g_poll_budget.load(); }
+
 // Tile order.  Default: tickets from a global counter (forward progress does not depend on the
 // order in which the hardware starts CTAs).  TWG_MS_ORDER=blockidx uses blockIdx.x instead, for
 // measuring what the ticket costs.
-static bool use_ticket() {
+bool ms_use_ticket() {
   static const bool v = [] {
     const char* env = getenv("TWG_MS_ORDER");
     return !(env && std::string(env) == "blockidx");
@@ -442,7 +357,7 @@ extern "C" int twg_masked_select_f32(const TwgIterDesc* desc, const float* src, 
   TwgIterDesc d = *desc;
   d.ntensors = 2;
   if (int rc = twg_iter_coalesce(&d)) return rc;
-  u64* ticket = use_ticket() ? static_cast<u64*>(workspace) : nullptr;
+  u64* ticket = ms_use_ticket() ? static_cast<u64*>(workspace) : nullptr;
   u64* tdesc = reinterpret_cast<u64*>(static_cast<char*>(workspace) + kMsHeaderBytes);
   i64* result = reinterpret_cast<i64*>(result_dev);
   const long long budget = g_poll_budget.load();

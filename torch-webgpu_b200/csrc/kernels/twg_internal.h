@@ -40,6 +40,9 @@ int check_desc(const TwgIterDesc* d, int ntensors);
 // Largest element offset operand t can reach (strides are non-negative in TensorIterator order
 // except for flipped views, which take the 64-bit path through the absolute value).
 int64_t max_offset(const TwgIterDesc& d, int t);
+// Settings of the look-back shared by masked_select and the fused select (masked_select.cu).
+long long ms_poll_budget();
+bool ms_use_ticket();
 // Host-side multiply-shift divisor for u32 numerators below 2^31.
 void make_fastdiv(uint32_t d, uint32_t* m, uint32_t* s);
 

@@ -110,6 +110,8 @@ SIGNATURES = {
     "twg_fused_kind": (c_int, [c_void_p, POINTER(c_int)]),
     "twg_fused_launch": (c_int, [c_void_p, POINTER(IterDesc), POINTER(c_void_p), c_void_p]),
     "twg_fused_release": (c_int, [c_void_p]),
+    "twg_fused_select_f32": (c_int, [c_void_p, c_int, c_int64, POINTER(c_void_p), c_void_p, c_void_p, c_void_p,
+                                     c_size_t, c_void_p]),
     "twg_fused_set_nvrtc_path": (c_int, [c_char_p]),
     "twg_fused_source": (c_int, [c_void_p, POINTER(c_char_p)]),
     "twg_launch_count": (c_int64, []),
@@ -378,6 +380,23 @@ def fused(instrs, inputs, out_dtypes, *, shape=None, stream=None):
         a = o.numpy(stream)
         outs.append(a.view(np.bool_) if np.dtype(t) == np.bool_ else a)
     return outs, fused_kind(handle)
+
+
+def fused_select(instrs, inputs, src: int, *, stream=None):
+    """out = inputs[src][program(inputs)] in one kernel (dense f32 inputs); returns (values, kind)."""
+    handle = fused_compile(instrs)
+    n = int(inputs[0].size)
+    dins = [DeviceArray(np.ascontiguousarray(i), stream=stream) for i in inputs]
+    out = DeviceBuffer(max(4 * n, 4), stream=stream)
+    result = DeviceBuffer(16, stream=stream)
+    ws_bytes = lib().twg_masked_select_workspace_bytes(n)
+    ws = DeviceBuffer(ws_bytes, stream=stream)
+    ptrs = (c_void_p * len(dins))(*[d.ptr for d in dins])
+    check(lib().twg_fused_select_f32(handle, src, n, ptrs, out.ptr, result.ptr, ws.ptr, ws_bytes, stream))
+    k, status = (int(v) for v in result.download(np.int64, 2, stream))
+    if status != 0:
+        raise TwgError(status, "fused select: the device-side scan reported an error")
+    return out.download(np.float32, k, stream), fused_kind(handle)
 
 
 # the benchmark's chain  m = (relu(silu(a + b) + c) == 0) & (a != 0)  as the compile backend emits it

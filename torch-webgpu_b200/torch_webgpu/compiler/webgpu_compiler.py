@@ -142,6 +142,43 @@ def build_program(group: list[fx.Node]):
     return prog, list(prog.inputs), out_nodes
 
 
+def select_pattern(group: list[fx.Node], inputs: list, out_nodes: list[fx.Node]):
+    """If the group's single output is a bool mask whose only consumer is
+    masked_select(x, mask) with x one of the group's own f32 inputs of the same shape, return
+    (masked_select node, index of x among the inputs): the pair can run as one fused select."""
+    if len(out_nodes) != 1:
+        return None
+    mask = out_nodes[0]
+    users = list(mask.users)
+    if len(users) != 1 or users[0].op != "call_function" or users[0].target is not aten.masked_select.default:
+        return None
+    sel = users[0]
+    if len(sel.args) != 2 or sel.args[1] is not mask or sel.args[0] not in inputs:
+        return None
+    mv = _val(mask)
+    if mv.dtype != torch.bool:
+        return None
+    for node in inputs:
+        v = _val(node)
+        if v.dtype != torch.float32 or tuple(v.shape) != tuple(mv.shape):
+            return None
+    return sel, inputs.index(sel.args[0])
+
+
+class FusedSelectKernel:
+    """Callable placed in the rewritten graph: predicate and masked_select in one launch."""
+
+    def __init__(self, prog: P.Program, src_index: int):
+        self.program = prog
+        self.src_index = src_index
+        self.handle = torch.ops.webgpu.compile_fused(*prog.columns())
+        self.kind = "aot" if torch.ops.webgpu.fused_kind(self.handle) == 0 else "nvrtc"
+        self.__name__ = f"webgpu_fused_select_{len(prog.instrs)}"
+
+    def __call__(self, *inputs):
+        return torch.ops.webgpu.run_fused_select(self.handle, list(inputs), self.src_index)
+
+
 class FusedKernel:
     """Callable placed in the rewritten graph: one launch of a compiled program."""
 
@@ -156,12 +193,26 @@ class FusedKernel:
         return torch.ops.webgpu.run_fused(self.handle, list(inputs), self.out_dtypes)
 
 
-def fuse_graph(gm: fx.GraphModule) -> fx.GraphModule:
+def fuse_graph(gm: fx.GraphModule, options: dict | None = None) -> fx.GraphModule:
+    options = options or {}
     graph = gm.graph
     kernels = []
     for group in partition(graph):
         prog, inputs, out_nodes = build_program(group)
         if not out_nodes:
+            continue
+        pattern = select_pattern(group, inputs, out_nodes) if options.get("fuse_select", True) else None
+        if pattern is not None:
+            sel, src_index = pattern
+            kernel = FusedSelectKernel(prog, src_index)
+            kernels.append(kernel)
+            with graph.inserting_after(sel):
+                call = graph.call_function(kernel, tuple(inputs))
+            call.meta = dict(sel.meta)
+            sel.replace_all_uses_with(call)
+            graph.erase_node(sel)
+            for n in reversed(group):
+                graph.erase_node(n)
             continue
         kernel = FusedKernel(prog)
         kernels.append(kernel)
@@ -182,21 +233,26 @@ def fuse_graph(gm: fx.GraphModule) -> fx.GraphModule:
     last_compile_report.update(
         fused_kernels=len(kernels),
         kinds=[k.kind for k in kernels],
+        fused_selects=sum(isinstance(k, FusedSelectKernel) for k in kernels),
         instructions=[len(k.program.instrs) for k in kernels],
         programs=[str(k.program) for k in kernels],
-        remaining_ops=[str(n.target) for n in graph.nodes if n.op == "call_function" and not isinstance(n.target, FusedKernel)
+        remaining_ops=[str(n.target) for n in graph.nodes if n.op == "call_function" and not isinstance(n.target, (FusedKernel, FusedSelectKernel))
                        and n.target is not operator.getitem],
     )
     return gm
 
 
-def _fw_compiler(gm: fx.GraphModule, example_inputs):
-    return fuse_graph(gm).forward
-
-
-_aot_backend = aot_autograd(fw_compiler=_fw_compiler)
-
-
 @register_backend
 def webgpu_backend(gm: fx.GraphModule, example_inputs: List[torch.Tensor], **kwargs) -> Callable:
-    return _aot_backend(gm, example_inputs, **kwargs)
+    """torch.compile(fn, backend=webgpu_backend[, options={"fuse_select": False}]).
+
+    masked_select has a data-dependent output shape, so dynamo cuts the graph in front of it unless
+    `torch._dynamo.config.capture_dynamic_output_shape_ops = True`; with that flag set, a mask that
+    feeds nothing but masked_select of one of the chain's own inputs is never written to memory.
+    """
+    options = dict(kwargs.pop("options", None) or {})
+
+    def fw_compiler(graph_module: fx.GraphModule, _example_inputs):
+        return fuse_graph(graph_module, options).forward
+
+    return aot_autograd(fw_compiler=fw_compiler)(gm, example_inputs, **kwargs)
