@@ -195,7 +195,7 @@ static std::string generate_source(const TwgFusedInstr* prog, int n, const Analy
     s += "#include \"twg_compact.cuh\"\n";
     for (int k = 0; k < a.nin; ++k) {
       snprintf(line, sizeof(line),
-               "extern \"C\" __global__ void __launch_bounds__(kMsThreads) twg_fused_select_%d(PwPtrs<%d> in, float* out, i64 n, "
+               "extern \"C\" __global__ void __launch_bounds__(kSelThreads, kSelCtasPerSm) twg_fused_select_%d(PwPtrs<%d> in, float* out, i64 n, "
                "i64 nchunks, u64* ticket, u64* desc, i64* result, i64 budget) "
                "{ select_fused_body<Prog, %d>(in, Prog{}, out, n, nchunks, ticket, desc, result, budget); }\n",
                k, a.nin, k);
@@ -273,12 +273,10 @@ template <class F>
 int aot_select0(const SelectArgs& a, cudaStream_t s) {
   PwPtrs<F::NIN> in;
   for (int k = 0; k < F::NIN; ++k) in.p[k] = const_cast<void*>(a.inputs[k]);
-  static bool configured = false;
-  if (!configured) {
-    TWG_CUDA(cudaFuncSetAttribute(select_fused_kernel<F, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSelSmemBytes));
-    configured = true;
-  }
-  select_fused_kernel<F, 0><<<a.grid, kMsThreads, kSelSmemBytes, s>>>(in, F{}, a.out, a.n, a.nchunks, a.ticket, a.desc,
+  // the attribute is per device; setting it again costs microseconds
+  TWG_CUDA(cudaFuncSetAttribute(select_fused_kernel<F, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)kSelSmemBytes));
+  select_fused_kernel<F, 0><<<a.grid, kSelThreads, kSelSmemBytes, s>>>(in, F{}, a.out, a.n, a.nchunks, a.ticket, a.desc,
                                                                        a.result, a.budget);
   TWG_CHECK_LAUNCH();
   return TWG_OK;
@@ -626,7 +624,7 @@ static int jit_select(TwgFusedProgram* p, int src, const SelectArgs& a, cudaStre
   u64 *ticket = a.ticket, *desc = a.desc;
   i64* result = a.result;
   void* args[] = {&in, &out, &n, &nchunks, &ticket, &desc, &result, &budget};
-  CUresult r = g_dyn.LaunchKernel(m->select[src], a.grid, 1, 1, kMsThreads, 1, 1, kSelSmemBytes,
+  CUresult r = g_dyn.LaunchKernel(m->select[src], a.grid, 1, 1, kSelThreads, 1, 1, kSelSmemBytes,
                                   reinterpret_cast<CUstream>(stream), args, nullptr);
   if (r != 0) return cu_fail(r, "cuLaunchKernel");
   count_launch();
@@ -653,7 +651,8 @@ extern "C" int twg_fused_select_f32(const TwgFusedProgram* cp, int src_input, in
     if (!is_aligned(inputs[k], 16))
       return set_error(TWG_ERR_UNSUPPORTED, "twg_fused_select_f32: input %d is not 16-byte aligned", k);
   }
-  const int64_t nchunks = (numel + kSelChunk - 1) / kSelChunk;
+  const int64_t chunk = kSelChunk;
+  const int64_t nchunks = (numel + chunk - 1) / chunk;
   TWG_REQUIRE(nchunks <= 0x7fffffff, "twg_fused_select_f32: %lld elements exceed the chunk limit", (long long)numel);
   const size_t need = kMsHeaderBytes + (size_t)nchunks * sizeof(u64);
   TWG_REQUIRE(workspace != nullptr && workspace_bytes >= need && is_aligned(workspace, 256),
@@ -665,7 +664,7 @@ extern "C" int twg_fused_select_f32(const TwgFusedProgram* cp, int src_input, in
   a.out = out;
   a.n = numel;
   a.nchunks = nchunks;
-  a.grid = (unsigned)std::min<int64_t>(nchunks, (int64_t)sm_count() * kSelCtasPerSm);
+  a.grid = (unsigned)std::min<int64_t>(nchunks, (int64_t)sm_count() * kSelCtasPerSm);  // persistent CTAs
   a.ticket = ms_use_ticket() ? static_cast<u64*>(workspace) : nullptr;
   a.desc = reinterpret_cast<u64*>(static_cast<char*>(workspace) + kMsHeaderBytes);
   a.result = reinterpret_cast<i64*>(result_dev);
