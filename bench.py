@@ -173,6 +173,48 @@ def run_cpu_baseline(target_seconds: float = 12.0) -> dict:
     t0 = time.perf_counter()
     aten()
     out["aten_cpu_gelem_s"] = nslabs * SLAB / (time.perf_counter() - t0) / 1e9
+    out["cpu_model"] = cpu_model()
+    out["ops_aten_cpu_gbs"] = aten_cpu_ops()
+    return out
+
+
+def cpu_model() -> str:
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.startswith("model name"):
+                    return line.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
+
+
+def aten_cpu_ops() -> dict:
+    """The single ops on the host through PyTorch's CPU kernels (what the reference's fallback ops
+    run): algorithmic GB/s on one [4096,4096] slab, best of 3 after a warm-up, all host threads."""
+    g = torch.Generator().manual_seed(0)
+    n = ROWS * COLS
+    x, y = torch.randn(ROWS, COLS, generator=g), torch.randn(ROWS, COLS, generator=g)
+    m1, m2 = x > 0, y > 0
+    cases = {
+        "add": (12 * n, lambda: torch.add(x, y)),
+        "relu": (8 * n, lambda: torch.relu(x)),
+        "silu": (8 * n, lambda: torch.nn.functional.silu(x)),
+        "gelu_erf": (8 * n, lambda: torch.nn.functional.gelu(x)),
+        "eq_tensor": (9 * n, lambda: torch.eq(x, y)),
+        "ne_scalar": (5 * n, lambda: torch.ne(x, 0)),
+        "bitwise_and_bool": (3 * n, lambda: torch.bitwise_and(m1, m2)),
+        "masked_select_p0.5": (5 * n + 4 * int(m1.sum()), lambda: torch.masked_select(x, m1)),
+    }
+    out = {}
+    for name, (nbytes, fn) in cases.items():
+        fn()
+        best = float("inf")
+        for _ in range(3):
+            t0 = time.perf_counter()
+            fn()
+            best = min(best, time.perf_counter() - t0)
+        out[name] = round(nbytes / best / 1e9, 2)
     return out
 
 
@@ -238,7 +280,12 @@ class Events:
         self.abi.check(self.abi.lib().twg_event_sync(self.ev[i]))
 
 
-def time_op(abi, stream, fn, iters: int = 20, warmup: int = 3) -> float:
+class Timing(float):
+    """Median milliseconds; the fastest sample rides along as .min_ms."""
+    min_ms: float = 0.0
+
+
+def time_op(abi, stream, fn, iters: int = 20, warmup: int = 3) -> Timing:
     """Median device time (ms) of fn() on `stream`, CUDA events around each call."""
     ev = Events(abi, 2 * iters)
     for _ in range(warmup):
@@ -248,7 +295,10 @@ def time_op(abi, stream, fn, iters: int = 20, warmup: int = 3) -> float:
         fn()
         ev.record(2 * i + 1, stream)
     abi.check(abi.lib().twg_stream_sync(stream))
-    return statistics.median(ev.elapsed(2 * i, 2 * i + 1) for i in range(iters))
+    samples = [ev.elapsed(2 * i, 2 * i + 1) for i in range(iters)]
+    t = Timing(statistics.median(samples))
+    t.min_ms = min(samples)
+    return t
 
 
 def per_op_table(abi, stream, peak: float) -> dict:
@@ -259,6 +309,8 @@ def per_op_table(abi, stream, peak: float) -> dict:
     def put(name, nbytes, ms, note=None):
         gbs = nbytes / ms / 1e6
         table[name] = {"ms": round(ms, 4), "gbs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 3)}
+        if isinstance(ms, Timing):
+            table[name]["min_ms"] = round(ms.min_ms, 4)
         if note:
             table[name]["note"] = note
 

@@ -144,7 +144,9 @@ typedef enum TwgUnaryOp {
 typedef enum TwgBinaryOp {
   TWG_BINARY_ADD = 0,             /* out = a + alpha*b, one rounding (binary.cpp:97) */
   TWG_BINARY_MUL = 1,             /* binary.cpp:100 */
-  TWG_BINARY_FUSED_ADD_RELU = 2   /* binary.cpp:103 */
+  TWG_BINARY_FUSED_ADD_RELU = 2,  /* binary.cpp:103 */
+  TWG_BINARY_DIV = 3              /* true division, IEEE round-to-nearest; unchecked in the
+                                     reference's op list (README.md:106-114) */
 } TwgBinaryOp;
 typedef enum TwgCompareOp { TWG_CMP_EQ = 0, TWG_CMP_NE = 1, TWG_CMP_LT = 2, TWG_CMP_LE = 3,
                             TWG_CMP_GT = 4, TWG_CMP_GE = 5 } TwgCompareOp;
@@ -154,6 +156,26 @@ int twg_unary_f32(int op, const TwgIterDesc* desc, const float* in, float* out, 
 /* binary_kernel<Op>(iter, alpha) (csrc/ops/binary.h:29-215).  desc: [0]=out, [1]=a, [2]=b. */
 int twg_binary_f32(int op, const TwgIterDesc* desc, const float* a, const float* b, float alpha,
                    float* out, void* stream);
+/* Element types of twg_convert (the ten dtypes the copy path moves). */
+typedef enum TwgDtype {
+  TWG_DTYPE_U8 = 0, TWG_DTYPE_I8 = 1, TWG_DTYPE_I16 = 2, TWG_DTYPE_I32 = 3, TWG_DTYPE_I64 = 4,
+  TWG_DTYPE_F16 = 5, TWG_DTYPE_BF16 = 6, TWG_DTYPE_F32 = 7, TWG_DTYPE_F64 = 8, TWG_DTYPE_BOOL = 9
+} TwgDtype;
+/* out[i] = (dst type)in[i] with C++ static_cast rules (what ATen's copy kernel applies); floats
+ * to float16 / bfloat16 round to nearest even.  The reference has no conversion: its copies
+ * assert float32 (csrc/ops/copy.cpp:22).  desc operands: [0]=out, [1]=in, strides in elements of
+ * each operand's own type. */
+int twg_convert(const TwgIterDesc* desc, int src_dtype, int dst_dtype, const void* in, void* out, void* stream);
+
+/* where.self and masked_fill.Scalar: unchecked entries of the reference's op list
+ * (README.md:128-166), no kernel there.  cond / mask are bool bytes (non-zero = true).
+ * twg_where_f32:       desc operands [0]=out, [1]=cond, [2]=a, [3]=b;  out = cond ? a : b.
+ * twg_masked_fill_f32: desc operands [0]=out, [1]=self, [2]=mask;      out = mask ? value : self
+ *                      (out may be self itself: in-place masked_fill_). */
+int twg_where_f32(const TwgIterDesc* desc, const uint8_t* cond, const float* a, const float* b, float* out,
+                  void* stream);
+int twg_masked_fill_f32(const TwgIterDesc* desc, const float* self, const uint8_t* mask, float value,
+                        float* out, void* stream);
 /* eq.Tensor / ne.Scalar ..., CPU fallbacks in the reference (csrc/bindings.cpp:36-39).
  * b == NULL compares against `scalar`; then desc has operands [0]=out, [1]=a only,
  * otherwise [0]=out, [1]=a, [2]=b.  out is bool bytes. */

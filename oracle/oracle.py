@@ -21,7 +21,7 @@ MAX_DIMS = 8
 
 UNARY = {"copy": 0, "relu": 1, "gelu_tanh": 2, "silu": 3, "gelu_erf": 4, "abs": 5,
          "silu_shader": 6, "gelu_tanh_shader": 7}
-BINARY = {"add": 0, "mul": 1, "fused_add_relu": 2}
+BINARY = {"add": 0, "mul": 1, "fused_add_relu": 2, "div": 3}
 COMPARE = {"eq": 0, "ne": 1, "lt": 2, "le": 3, "gt": 4, "ge": 5}
 
 
@@ -112,6 +112,47 @@ def binary(op: str, a: np.ndarray, b: np.ndarray, alpha: float = 1.0) -> np.ndar
     out = np.empty(shape, dtype=np.float32)
     it = _iter(shape, out, a, b)
     rc = lib().twgo_binary_f32(BINARY[op], ctypes.byref(it), _ptr(a), _ptr(b), ctypes.c_float(alpha), _ptr(out))
+    assert rc == 0
+    return out
+
+
+def sub(a: np.ndarray, b: np.ndarray, alpha: float = 1.0) -> np.ndarray:
+    """a - alpha*b the way ATen computes it: add with the negated alpha (one rounding)."""
+    return binary("add", a, b, -alpha)
+
+
+DTYPES = {"uint8": 0, "int8": 1, "int16": 2, "int32": 3, "int64": 4, "float16": 5, "bf16": 6, "float32": 7,
+          "float64": 8, "bool": 9}
+_NP_OF = {"uint8": np.uint8, "int8": np.int8, "int16": np.int16, "int32": np.int32, "int64": np.int64,
+          "float16": np.float16, "bf16": np.uint16, "float32": np.float32, "float64": np.float64, "bool": np.bool_}
+
+
+def convert(x: np.ndarray, src: str, dst: str) -> np.ndarray:
+    """Element-type conversion; bfloat16 travels as uint16 bit patterns under the name "bf16"."""
+    xs = np.ascontiguousarray(x)
+    assert xs.dtype == _NP_OF[src], (xs.dtype, src)
+    out = np.empty(xs.shape, dtype=_NP_OF[dst])
+    rc = lib().twgo_convert(ctypes.c_int64(xs.size), DTYPES[src], DTYPES[dst], _ptr(xs), _ptr(out))
+    assert rc == 0
+    return out
+
+
+def where(cond: np.ndarray, a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    assert cond.dtype == np.bool_ and a.dtype == np.float32 and b.dtype == np.float32
+    shape = np.broadcast_shapes(cond.shape, a.shape, b.shape)
+    c, x, y = (np.ascontiguousarray(np.broadcast_to(t, shape)) for t in (cond.view(np.uint8), a, b))
+    out = np.empty(shape, dtype=np.float32)
+    rc = lib().twgo_where_f32(ctypes.c_int64(out.size), _ptr(c), _ptr(x), _ptr(y), _ptr(out))
+    assert rc == 0
+    return out
+
+
+def masked_fill(x: np.ndarray, mask: np.ndarray, value: float) -> np.ndarray:
+    assert mask.dtype == np.bool_ and x.dtype == np.float32
+    shape = np.broadcast_shapes(x.shape, mask.shape)
+    xs, m = (np.ascontiguousarray(np.broadcast_to(t, shape)) for t in (x, mask.view(np.uint8)))
+    out = np.empty(shape, dtype=np.float32)
+    rc = lib().twgo_masked_fill_f32(ctypes.c_int64(out.size), _ptr(xs), _ptr(m), ctypes.c_float(value), _ptr(out))
     assert rc == 0
     return out
 

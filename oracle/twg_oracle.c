@@ -54,7 +54,7 @@ enum {
   TWGO_COPY = 0, TWGO_RELU = 1, TWGO_GELU_TANH = 2, TWGO_SILU = 3, TWGO_GELU_ERF = 4, TWGO_ABS = 5,
   TWGO_SILU_SHADER = 6, TWGO_GELU_TANH_SHADER = 7
 };
-enum { TWGO_ADD = 0, TWGO_MUL = 1, TWGO_FUSED_ADD_RELU = 2 };
+enum { TWGO_ADD = 0, TWGO_MUL = 1, TWGO_FUSED_ADD_RELU = 2, TWGO_DIV = 3 };
 enum { TWGO_EQ = 0, TWGO_NE = 1, TWGO_LT = 2, TWGO_LE = 3, TWGO_GT = 4, TWGO_GE = 5 };
 
 int twgo_num_threads(void) {
@@ -126,7 +126,7 @@ int twgo_unary_f32(int op, const TwgoIter* it, const float* in, float* out) {
 }
 
 int twgo_binary_f32(int op, const TwgoIter* it, const float* x, const float* y, float alpha, float* out) {
-  if (op < 0 || op > TWGO_FUSED_ADD_RELU) return -1;
+  if (op < 0 || op > TWGO_DIV) return -1;
   const int64_t n = it->length;
 #pragma omp parallel for schedule(static)
   for (int64_t i = 0; i < n; ++i) {
@@ -135,6 +135,7 @@ int twgo_binary_f32(int op, const TwgoIter* it, const float* x, const float* y, 
     float r;
     if (op == TWGO_ADD) r = fmaf(alpha, y[b], x[a]);            /* binary.cpp:97  */
     else if (op == TWGO_MUL) r = x[a] * y[b];                   /* binary.cpp:100 */
+    else if (op == TWGO_DIV) r = x[a] / y[b];                   /* README.md:107 (div, unchecked) */
     else r = relu1(x[a] + y[b]);                                /* binary.cpp:103 */
     out[o] = r;
   }
@@ -166,6 +167,66 @@ int twgo_compare_f32(int op, const TwgoIter* it, const float* x, const float* y,
 }
 
 /* bool & bool: logical and of 0/1 bytes (any non-zero byte is true). */
+/* Element-type conversion with C cast rules (ATen's copy kernel is a static_cast per element).
+ * dtype codes: 0 u8, 1 i8, 2 i16, 3 i32, 4 i64, 5 f16, 6 bf16 (bit pattern), 7 f32, 8 f64, 9 bool.
+ * Every source is first widened exactly (double for floats, int64 else), then narrowed the way a
+ * cast does: through float for f16 / bf16 (round to nearest even), truncation toward zero for
+ * float -> integer. */
+static inline float bf16_to_f32(uint16_t h) { uint32_t u = (uint32_t)h << 16; float f; memcpy(&f, &u, 4); return f; }
+static inline uint16_t f32_to_bf16(float f) {
+  uint32_t u; memcpy(&u, &f, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return 0x7fc0;                    /* NaN */
+  u += 0x7fffu + ((u >> 16) & 1u);                                        /* round to nearest even */
+  return (uint16_t)(u >> 16);
+}
+int twgo_convert(int64_t n, int src, int dst, const void* in, void* out) {
+  if (src < 0 || src > 9 || dst < 0 || dst > 9) return -1;
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) {
+    double fv = 0.0; int64_t iv = 0; int is_f = 0;
+    switch (src) {
+      case 0: iv = ((const uint8_t*)in)[i]; break;
+      case 1: iv = ((const int8_t*)in)[i]; break;
+      case 2: iv = ((const int16_t*)in)[i]; break;
+      case 3: iv = ((const int32_t*)in)[i]; break;
+      case 4: iv = ((const int64_t*)in)[i]; break;
+      case 5: fv = (double)(float)((const _Float16*)in)[i]; is_f = 1; break;
+      case 6: fv = (double)bf16_to_f32(((const uint16_t*)in)[i]); is_f = 1; break;
+      case 7: fv = (double)((const float*)in)[i]; is_f = 1; break;
+      case 8: fv = ((const double*)in)[i]; is_f = 1; break;
+      default: iv = ((const uint8_t*)in)[i] != 0; break;
+    }
+    const int64_t as_int = is_f ? (int64_t)fv : iv;
+    switch (dst) {
+      case 0: ((uint8_t*)out)[i] = (uint8_t)as_int; break;
+      case 1: ((int8_t*)out)[i] = (int8_t)as_int; break;
+      case 2: ((int16_t*)out)[i] = (int16_t)as_int; break;
+      case 3: ((int32_t*)out)[i] = (int32_t)as_int; break;
+      case 4: ((int64_t*)out)[i] = as_int; break;
+      case 5: ((_Float16*)out)[i] = (_Float16)(is_f ? (float)fv : (float)iv); break;
+      case 6: ((uint16_t*)out)[i] = f32_to_bf16(is_f ? (float)fv : (float)iv); break;
+      case 7: ((float*)out)[i] = is_f ? (float)fv : (float)iv; break;
+      case 8: ((double*)out)[i] = is_f ? fv : (double)iv; break;
+      default: ((uint8_t*)out)[i] = is_f ? (fv != 0.0) : (iv != 0); break;
+    }
+  }
+  return 0;
+}
+
+/* where.self and masked_fill.Scalar (README.md:128-166, unchecked: the reference has no kernel;
+ * semantics are ATen's).  Operands are dense and of one length: the caller has broadcast them. */
+int twgo_where_f32(int64_t n, const uint8_t* cond, const float* x, const float* y, float* out) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) out[i] = cond[i] != 0 ? x[i] : y[i];
+  return 0;
+}
+
+int twgo_masked_fill_f32(int64_t n, const float* self, const uint8_t* mask, float value, float* out) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) out[i] = mask[i] != 0 ? value : self[i];
+  return 0;
+}
+
 int twgo_and_bool(const TwgoIter* it, const uint8_t* x, const uint8_t* y, uint8_t* out) {
   const int64_t n = it->length;
 #pragma omp parallel for schedule(static)

@@ -125,6 +125,44 @@ def main() -> None:
     put("chain_a", ca); put("chain_b", cb); put("chain_c", cc)
     put("chain_y", cy); put("chain_m", cm); put("chain_sel", torch.masked_select(ca, cm))
 
+    # ---- neighbouring ops of the reference's list: sub, div, where, masked_fill -----------------
+    # (appended after everything else so that the generator draws above stay what they were)
+    put("rnd_sub", x - y)
+    put("rnd_sub_alpha", torch.sub(x, y, alpha=1.75))
+    put("rnd_div", x / y)
+    put("edge_div", e / er)
+    put("edge_sub", e - er)
+    put("rnd_where", torch.where(m2, x, y))
+    put("rnd_masked_fill", torch.masked_fill(x, m1, -3.5))
+    wc = torch.rand(37, 1, generator=g) < 0.5
+    put("lay_where_cond", wc)
+    put("lay_where", torch.where(wc, s2, col))             # cond [37,1], a [37,53], b [1,53]
+    put("lay_masked_fill_t", torch.masked_fill(s2.t(), wc.t(), 2.0))
+
+    # ---- element-type conversions (copy_ between dtypes): every pair, in-range values ------------
+    cv = torch.cat([torch.rand(200, generator=g) * 200 - 100, torch.tensor([0.0, -0.0, 0.5, -0.5, 1.5, 2.5, -2.5, 127.0,
+                                                                          -128.0, 1e-3, 65504.0 / 1024])])
+    names = {torch.uint8: "uint8", torch.int8: "int8", torch.int16: "int16", torch.int32: "int32", torch.int64: "int64",
+             torch.float16: "float16", torch.bfloat16: "bf16", torch.float32: "float32", torch.float64: "float64",
+             torch.bool: "bool"}
+    def bits(t: torch.Tensor) -> torch.Tensor:
+        return t.view(torch.int16) if t.dtype == torch.bfloat16 else t
+    for sdt, sname in names.items():
+        if sdt == torch.uint8:
+            base = cv.abs().to(sdt)          # a negative float -> uint8 cast is undefined in C
+        elif sdt == torch.bool:
+            base = cv > 0
+        else:
+            base = cv.to(sdt)
+        put(f"cvt_src_{sname}", bits(base))
+        for ddt, dname in names.items():
+            if ddt == torch.uint8 and sdt not in (torch.uint8, torch.bool):
+                src_t = base.abs() if sdt != torch.uint8 else base
+                put(f"cvt_src_{sname}_for_uint8", bits(src_t))
+                put(f"cvt_{sname}_to_{dname}", bits(src_t.to(ddt)))
+            else:
+                put(f"cvt_{sname}_to_{dname}", bits(base.to(ddt)))
+
     np.savez_compressed(OUT, **d)
     print(f"wrote {OUT} ({OUT.stat().st_size} bytes, {len(d)} arrays, torch {torch.__version__})")
 

@@ -11,7 +11,7 @@ import numpy as np
 import pytest
 
 from oracle import oracle
-from util import assert_bit_equal, assert_close_ulp
+from util import CVT_NAMES, assert_bit_equal, assert_close_ulp, cvt_case
 
 pytestmark = pytest.mark.gpu
 
@@ -97,6 +97,57 @@ def test_random_cases_against_aten(abi, golden):
     assert_bit_equal(abi.masked_select(src, b(golden["ms_mask_row"])), golden["ms_out_row"], "row mask")
     assert_bit_equal(abi.masked_select(src, b(golden["ms_mask_col"])), golden["ms_out_col"], "col mask")
     assert_bit_equal(abi.masked_select(src[:, :1], b(golden["ms_mask_col"])), golden["ms_out_bsrc"], "bcast self")
+
+
+@pytest.mark.parametrize("src", CVT_NAMES)
+def test_conversions(abi, golden, src):
+    for dst in CVT_NAMES:
+        x, want = cvt_case(golden, src, dst)
+        assert_bit_equal(abi.convert(x, src, dst), want, f"{src} -> {dst} vs ATen")
+        assert_bit_equal(abi.convert(x, src, dst, pad=1), want, f"{src} -> {dst} misaligned")
+
+
+def test_conversions_large_and_strided(abi):
+    n = 1 << 20
+    x = rnd(n + 3, 101, -1000, 1000)
+    for dst in ("float16", "bf16", "int32", "float64", "bool", "uint8"):
+        src = np.abs(x) % 250 if dst == "uint8" else x
+        assert_bit_equal(abi.convert(src, "float32", dst), oracle.convert(src, "float32", dst), f"f32 -> {dst}")
+    h = oracle.convert(x, "float32", "float16")
+    assert_bit_equal(abi.convert(h, "float16", "float32"), oracle.convert(h, "float16", "float32"), "f16 -> f32")
+    i = np.random.default_rng(102).integers(-2**40, 2**40, n).astype(np.int64)
+    assert_bit_equal(abi.convert(i, "int64", "float32"), oracle.convert(i, "int64", "float32"), "i64 -> f32")
+    assert_bit_equal(abi.convert(i, "int64", "int16"), oracle.convert(i, "int64", "int16"), "i64 -> i16 wraps")
+    m = x.reshape(-1)[: 512 * 300].reshape(512, 300)
+    assert_bit_equal(abi.convert(m.T, "float32", "bf16"), oracle.convert(np.ascontiguousarray(m.T), "float32", "bf16"), "transposed")
+    assert_bit_equal(abi.convert(m[:, ::3], "float32", "int64"), oracle.convert(np.ascontiguousarray(m[:, ::3]), "float32", "int64"), "slice")
+
+
+def test_sub_div_where_masked_fill(abi, golden):
+    x, y, e, er = golden["rnd_x"], golden["rnd_y"], golden["edge_x"], golden["edge_y"]
+    assert_bit_equal(abi.binary("add", x, y, alpha=-1.0), golden["rnd_sub"], "sub")
+    assert_bit_equal(abi.binary("add", x, y, alpha=-1.75), golden["rnd_sub_alpha"], "sub alpha")
+    assert_bit_equal(abi.binary("div", x, y), golden["rnd_div"], "div")
+    assert_bit_equal(abi.binary("div", e, er), golden["edge_div"], "div edge", any_nan=True)
+    assert_bit_equal(abi.binary("add", e, er, alpha=-1.0), golden["edge_sub"], "sub edge", any_nan=True)
+    m1, m2 = b(golden["rnd_eq"]), b(golden["rnd_ne0"])
+    assert_bit_equal(abi.where(m2, x, y), golden["rnd_where"], "where")
+    assert_bit_equal(abi.masked_fill(x, m1, -3.5), golden["rnd_masked_fill"], "masked_fill")
+    s, col, wc = golden["lay_s"], golden["lay_col"], b(golden["lay_where_cond"])
+    assert_bit_equal(abi.where(wc, s, col), golden["lay_where"], "where broadcast")
+    assert_bit_equal(abi.masked_fill(s.T, wc.T, 2.0), golden["lay_masked_fill_t"], "masked_fill transposed")
+    # every size and alignment on the dense path, and a true transpose, against the oracle
+    for n in (1, 5, 4097, 100003):
+        for pad in (0, 3):
+            u, v = rnd(n, 95), rnd(n, 96)
+            c = np.random.default_rng(97).random(n) < 0.4
+            assert_bit_equal(abi.where(c, u, v, pad=pad), oracle.where(c, u, v), f"where n={n} pad={pad}")
+            assert_bit_equal(abi.masked_fill(u, c, 7.25, pad=pad), oracle.masked_fill(u, c, 7.25), f"masked_fill n={n}")
+            assert_bit_equal(abi.binary("div", u, v, pad=pad), oracle.binary("div", u, v), f"div n={n} pad={pad}")
+    u, v = rnd(96 * 160, 98).reshape(96, 160), rnd(96 * 160, 99).reshape(160, 96)
+    c = np.random.default_rng(100).random((96, 160)) < 0.5
+    assert_bit_equal(abi.where(c, u, v.T), oracle.where(c, u, np.ascontiguousarray(v.T)), "where with a transposed operand")
+    assert_bit_equal(abi.binary("div", u, v.T), oracle.binary("div", u, np.ascontiguousarray(v.T)), "div transposed")
 
 
 # ------------------------------------------------------------------------------------------

@@ -12,7 +12,7 @@ import numpy as np
 import pytest
 
 from oracle import oracle
-from util import assert_bit_equal, assert_close_ulp
+from util import CVT_NAMES, assert_bit_equal, assert_close_ulp, cvt_case
 
 
 def b(a):  # golden bool arrays are stored as uint8
@@ -127,6 +127,30 @@ def test_chain(golden):
     # on this fixture no pre-relu value is close enough to zero for the mask to flip
     assert_bit_equal(m, b(golden["chain_m"]), "chain mask")
     assert_bit_equal(oracle.masked_select(a, m), golden["chain_sel"], "chain select")
+
+
+def test_sub_div_where_masked_fill_against_aten(golden):
+    """Neighbouring ops of the reference's list (README.md:106-166); ATen CPU is the pin."""
+    x, y, e, er = golden["rnd_x"], golden["rnd_y"], golden["edge_x"], golden["edge_y"]
+    assert_bit_equal(oracle.sub(x, y), golden["rnd_sub"], "sub")
+    assert_bit_equal(oracle.sub(x, y, 1.75), golden["rnd_sub_alpha"], "sub alpha")
+    assert_bit_equal(oracle.binary("div", x, y), golden["rnd_div"], "div")
+    assert_bit_equal(oracle.binary("div", e, er), golden["edge_div"], "div edge", any_nan=True)
+    assert_bit_equal(oracle.sub(e, er), golden["edge_sub"], "sub edge", any_nan=True)
+    m1, m2 = golden["rnd_eq"].view(np.bool_), golden["rnd_ne0"].view(np.bool_)
+    assert_bit_equal(oracle.where(m2, x, y), golden["rnd_where"], "where")
+    assert_bit_equal(oracle.masked_fill(x, m1, -3.5), golden["rnd_masked_fill"], "masked_fill")
+    s, col, wc = golden["lay_s"], golden["lay_col"], golden["lay_where_cond"].view(np.bool_)
+    assert_bit_equal(oracle.where(wc, s, col), golden["lay_where"], "where broadcast")
+    assert_bit_equal(oracle.masked_fill(s.T, wc.T, 2.0), golden["lay_masked_fill_t"], "masked_fill transposed")
+
+
+@pytest.mark.parametrize("src", CVT_NAMES)
+def test_conversions_against_aten(golden, src):
+    for dst in CVT_NAMES:
+        x, want = cvt_case(golden, src, dst)
+        got = oracle.convert(x, src, dst)
+        assert_bit_equal(got, want, f"{src} -> {dst}")
 
 
 def test_more_than_eight_dims_rejected():

@@ -145,6 +145,50 @@ def test_scalars_inplace_and_out_variants():
     assert torch.equal(m.cpu(), torch.masked_select(x, x > 0))
 
 
+def test_neighbouring_ops_of_the_reference_list():  # README.md:106-166, unchecked there
+    g = torch.Generator().manual_seed(7)
+    x, y = torch.randn(257, 130, generator=g), torch.randn(257, 130, generator=g)
+    m = torch.rand(257, 130, generator=g) < 0.3
+    dx, dy, dm = x.to("webgpu"), y.to("webgpu"), m.to("webgpu")
+    assert torch.equal((dx - dy).cpu(), x - y) and torch.equal((dx - 1.5).cpu(), x - 1.5)
+    assert torch.equal((dx / dy).cpu(), x / y) and torch.equal((dx / 3.0).cpu(), x / 3.0)
+    assert torch.equal(torch.ne(dx, dy).cpu(), torch.ne(x, y))
+    assert torch.equal(torch.where(dm, dx, dy).cpu(), torch.where(m, x, y))
+    assert torch.equal(torch.where(dm[:, :1], dx, dy.t().contiguous().t()).cpu(), torch.where(m[:, :1], x, y))
+    assert torch.equal(torch.where(dm, dx, 0.25).cpu(), torch.where(m, x, 0.25))
+    assert torch.equal(dx.masked_fill(dm, -2.0).cpu(), x.masked_fill(m, -2.0))
+    z = dx.clone()
+    z.t().masked_fill_(dm.t(), 9.0)                      # in place through a transposed view
+    assert torch.equal(z.cpu(), x.masked_fill(m, 9.0))
+    assert torch.equal(dx.t().clone().cpu(), x.t()) and dx.t().clone().stride() == x.t().clone().stride()
+    assert torch.equal(torch.zeros_like(dx).cpu(), torch.zeros_like(x)) and torch.empty_like(dx).shape == x.shape
+    with pytest.raises(RuntimeError):
+        torch.where(dx > 0, dx.to(torch.float64), dy.to(torch.float64))
+
+
+def test_dtype_conversion_stays_on_the_device():
+    import torch_webgpu
+    g = torch.Generator().manual_seed(8)
+    x = torch.rand(300, 70, generator=g) * 200 - 100
+    d = x.to("webgpu")
+    torch.webgpu.synchronize()
+    torch_webgpu._C.reset_launch_count()
+    for dt in (torch.float16, torch.bfloat16, torch.float64, torch.int32, torch.int64, torch.int16, torch.int8, torch.bool):
+        got = d.to(dt)
+        assert got.dtype == dt and got.device.type == "webgpu"
+        assert torch.equal(got.cpu(), x.to(dt)), dt
+    assert torch_webgpu._C.launch_count() == 8                      # one conversion kernel each, no host pass
+    h = d.to(torch.float16)
+    assert torch.equal(h.to(torch.float32).cpu(), x.to(torch.float16).to(torch.float32))
+    assert torch.equal(d.t().to(torch.int32).cpu(), x.t().to(torch.int32))        # strided source
+    dst = torch.empty(70, 300, dtype=torch.float64, device="webgpu")
+    dst.t().copy_(d)                                                               # strided destination
+    assert torch.equal(dst.cpu(), x.t().to(torch.float64))
+    i = torch.randint(-1000, 1000, (4097,), generator=g)
+    assert torch.equal(i.to("webgpu").to(torch.float32).cpu(), i.to(torch.float32))
+    assert torch.equal((d > 0).to(torch.float32).cpu(), (x > 0).to(torch.float32))
+
+
 def test_allocator_statistics_through_the_device_module():
     torch.webgpu.synchronize()
     torch.webgpu.empty_cache()

@@ -40,6 +40,18 @@ def ulp(ref: np.ndarray) -> np.ndarray:
     return np.maximum(np.spacing(ref), np.float32(1.4e-45)).astype(np.float64)
 
 
+CVT_NAMES = ["uint8", "int8", "int16", "int32", "int64", "float16", "bf16", "float32", "float64", "bool"]
+_CVT_NP = {"uint8": np.uint8, "int8": np.int8, "int16": np.int16, "int32": np.int32, "int64": np.int64,
+           "float16": np.float16, "bf16": np.uint16, "float32": np.float32, "float64": np.float64, "bool": np.bool_}
+
+
+def cvt_case(golden, src: str, dst: str):
+    """(input, expected) of one conversion fixture, in the array types the bindings take
+    (bfloat16 as uint16 bit patterns, bool as numpy bool)."""
+    key = f"cvt_src_{src}_for_uint8" if dst == "uint8" and src not in ("uint8", "bool") else f"cvt_src_{src}"
+    return golden[key].view(_CVT_NP[src]), golden[f"cvt_{src}_to_{dst}"].view(_CVT_NP[dst])
+
+
 def assert_close_ulp(got, ref, *, ulps: float = 2.0, rel: float = 1e-6, abs_floor: float = 0.0, what: str = ""):
     """|got - ref| <= max(ulps * ulp(ref), rel * |ref|, abs_floor); NaN/inf must match exactly.
 

@@ -80,11 +80,47 @@ static void device_to_host(at::Tensor& dst, const at::Tensor& src, bool non_bloc
   }
 }
 
+static int twg_dtype(at::ScalarType t) {
+  switch (t) {
+    case at::kByte: return TWG_DTYPE_U8;
+    case at::kChar: return TWG_DTYPE_I8;
+    case at::kShort: return TWG_DTYPE_I16;
+    case at::kInt: return TWG_DTYPE_I32;
+    case at::kLong: return TWG_DTYPE_I64;
+    case at::kHalf: return TWG_DTYPE_F16;
+    case at::kBFloat16: return TWG_DTYPE_BF16;
+    case at::kFloat: return TWG_DTYPE_F32;
+    case at::kDouble: return TWG_DTYPE_F64;
+    case at::kBool: return TWG_DTYPE_BOOL;
+    default: return -1;
+  }
+}
+
+// dst = src with an element-type conversion, any layouts, both on one device
+static void device_convert(at::Tensor& dst, const at::Tensor& src) {
+  const int st = twg_dtype(src.scalar_type()), dt = twg_dtype(dst.scalar_type());
+  TORCH_CHECK(st >= 0 && dt >= 0, "torch_webgpu: copy_ cannot convert ", src.scalar_type(), " to ", dst.scalar_type());
+  at::TensorIteratorConfig config;
+  config.set_check_mem_overlap(true).check_all_same_dtype(false).promote_inputs_to_common_dtype(false);
+  config.cast_common_dtype_to_outputs(false).resize_outputs(false);
+  config.add_output(dst).add_const_input(src);
+  auto iter = config.build();
+  if (iter.numel() == 0) return;
+  const c10::DeviceIndex dev = dev_of(dst);
+  core::DeviceScope scope(dev);
+  TwgIterDesc desc = desc_from_iter(iter);
+  TWG_TORCH_CHECK(twg_convert(&desc, st, dt, iter.data_ptr(1), iter.data_ptr(0), core::current_stream(dev)));
+}
+
 static void device_to_device(at::Tensor& dst, const at::Tensor& src) {
   if (dst.scalar_type() != src.scalar_type()) {
-    // dtype conversion is outside the accelerated path: convert on the host
-    at::Tensor host = src.cpu().to(dst.scalar_type());
-    host_to_device(dst, host, false);
+    if (dev_of(dst) == dev_of(src)) {
+      device_convert(dst, src);
+    } else {  // move first, convert where the result lives
+      at::Tensor landed = at::empty(src.sizes(), dst.options().dtype(src.scalar_type()));
+      device_to_device(landed, src);
+      device_convert(dst, landed);
+    }
     return;
   }
   if (dev_of(dst) != dev_of(src)) {

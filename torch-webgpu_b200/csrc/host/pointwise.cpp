@@ -111,6 +111,59 @@ at::Tensor& mul_out_webgpu(const at::Tensor& self, const at::Tensor& other, at::
   return binary_out(TWG_BINARY_MUL, self, other, 1, out);
 }
 
+// sub is add with the negated alpha (what ATen does: one fused multiply-add, one rounding)
+at::Tensor& sub_out_webgpu(const at::Tensor& self, const at::Tensor& other, const at::Scalar& alpha, at::Tensor& out) {
+  return binary_out(TWG_BINARY_ADD, self, other, -alpha.to<double>(), out);
+}
+// true division only; floor / trunc rounding modes are not part of this path
+at::Tensor& div_out_webgpu(const at::Tensor& self, const at::Tensor& other, at::Tensor& out) {
+  return binary_out(TWG_BINARY_DIV, self, other, 1, out);
+}
+
+// ---- where / masked_fill -------------------------------------------------------------------
+at::Tensor& where_self_out(const at::Tensor& condition, const at::Tensor& self, const at::Tensor& other, at::Tensor& out) {
+  TORCH_CHECK(condition.scalar_type() == at::kBool, "where expected condition to be a boolean tensor, but got a tensor with dtype ",
+              condition.scalar_type());
+  const at::Tensor a = to_device_if_cpu_scalar(self, condition.device(), at::kFloat);
+  const at::Tensor b = to_device_if_cpu_scalar(other, condition.device(), at::kFloat);
+  TORCH_CHECK(a.scalar_type() == at::kFloat && b.scalar_type() == at::kFloat && out.scalar_type() == at::kFloat,
+              "torch_webgpu: where supports float32 values only, got ", a.scalar_type(), " and ", b.scalar_type());
+  at::TensorIteratorConfig config;
+  config.set_check_mem_overlap(true).check_all_same_dtype(false);
+  config.add_output(out).add_const_input(condition).add_const_input(a).add_const_input(b);
+  auto iter = config.build();
+  if (iter.numel() == 0) return out;
+  const c10::DeviceIndex dev = iter_device(iter);
+  core::DeviceScope scope(dev);
+  TwgIterDesc desc = desc_from_iter(iter);
+  TWG_TORCH_CHECK(twg_where_f32(&desc, static_cast<const uint8_t*>(iter.data_ptr(1)), static_cast<const float*>(iter.data_ptr(2)),
+                                static_cast<const float*>(iter.data_ptr(3)), static_cast<float*>(iter.data_ptr(0)),
+                                core::current_stream(dev)));
+  return out;
+}
+at::Tensor where_self(const at::Tensor& condition, const at::Tensor& self, const at::Tensor& other) {
+  auto shape = at::infer_size(condition.sizes(), at::infer_size(self.sizes(), other.sizes()));
+  at::Tensor out = at::empty(shape, condition.options().dtype(at::kFloat));
+  return where_self_out(condition, self, other, out);
+}
+at::Tensor& masked_fill_scalar_(at::Tensor& self, const at::Tensor& mask, const at::Scalar& value) {
+  TORCH_CHECK(mask.scalar_type() == at::kBool, "masked_fill_ only supports boolean masks, but got mask with dtype ",
+              mask.scalar_type());
+  TORCH_CHECK(self.scalar_type() == at::kFloat, "torch_webgpu: masked_fill_ supports float32 tensors only, got ",
+              self.scalar_type());
+  at::TensorIteratorConfig config;
+  config.set_check_mem_overlap(false).check_all_same_dtype(false).resize_outputs(false);
+  config.add_output(self).add_const_input(self).add_const_input(mask);
+  auto iter = config.build();
+  if (iter.numel() == 0) return self;
+  const c10::DeviceIndex dev = iter_device(iter);
+  core::DeviceScope scope(dev);
+  TwgIterDesc desc = desc_from_iter(iter);
+  TWG_TORCH_CHECK(twg_masked_fill_f32(&desc, static_cast<const float*>(iter.data_ptr(1)), static_cast<const uint8_t*>(iter.data_ptr(2)),
+                                      value.to<float>(), static_cast<float*>(iter.data_ptr(0)), core::current_stream(dev)));
+  return self;
+}
+
 // ---- relu / gelu / silu / abs ----------------------------------------------------------------
 static at::Tensor& unary_out(int op, const at::Tensor& self, at::Tensor& out) {
   at::TensorIteratorConfig config;
@@ -246,6 +299,11 @@ at::Tensor bitwise_and(const at::Tensor& self, const at::Tensor& other) {
 TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("add.out", TORCH_FN(add_out_webgpu));
   m.impl("mul.out", TORCH_FN(mul_out_webgpu));
+  m.impl("sub.out", TORCH_FN(sub_out_webgpu));
+  m.impl("div.out", TORCH_FN(div_out_webgpu));
+  m.impl("where.self", TORCH_FN(where_self));
+  m.impl("where.self_out", TORCH_FN(where_self_out));
+  m.impl("masked_fill_.Scalar", TORCH_FN(masked_fill_scalar_));
   m.impl("relu", TORCH_FN(relu));
   m.impl("relu.out", TORCH_FN(relu_out));
   m.impl("relu_", TORCH_FN(relu_));

@@ -32,6 +32,7 @@ struct BinaryF32 {
     float y;
     if constexpr (OP == TWG_BINARY_ADD) y = f_add(a, b, alpha);
     else if constexpr (OP == TWG_BINARY_MUL) y = f_mul(a, b);
+    else if constexpr (OP == TWG_BINARY_DIV) y = f_div(a, b);
     else y = f_relu(f_add(a, b, 1.0f));
     out[0] = as_u(y);
   }
@@ -62,6 +63,20 @@ struct CompareScalarF32 {
   __device__ __forceinline__ void operator()(const u32* in, u32* out) const {
     out[0] = compare<OP>(as_f(in[0]), scalar);
   }
+};
+
+// out = cond ? a : b with a bool-byte condition (any non-zero byte counts as true, like ATen).
+struct WhereF32 {
+  static constexpr int NIN = 3, NOUT = 1;
+  static constexpr unsigned kInByteMask = 1u, kOutByteMask = 0u;
+  __device__ __forceinline__ void operator()(const u32* in, u32* out) const { out[0] = in[0] != 0u ? in[1] : in[2]; }
+};
+// out = mask ? value : self.
+struct MaskedFillF32 {
+  static constexpr int NIN = 2, NOUT = 1;
+  static constexpr unsigned kInByteMask = 2u, kOutByteMask = 0u;
+  float value;
+  __device__ __forceinline__ void operator()(const u32* in, u32* out) const { out[0] = in[1] != 0u ? as_u(value) : in[0]; }
 };
 
 struct AndBool {
@@ -119,8 +134,21 @@ extern "C" int twg_binary_f32(int op, const TwgIterDesc* desc, const float* a, c
     case TWG_BINARY_ADD: return run_binary<TWG_BINARY_ADD>(desc, a, b, alpha, out, s);
     case TWG_BINARY_MUL: return run_binary<TWG_BINARY_MUL>(desc, a, b, alpha, out, s);
     case TWG_BINARY_FUSED_ADD_RELU: return run_binary<TWG_BINARY_FUSED_ADD_RELU>(desc, a, b, alpha, out, s);
+    case TWG_BINARY_DIV: return run_binary<TWG_BINARY_DIV>(desc, a, b, alpha, out, s);
     default: return set_error(TWG_ERR_INVALID, "twg_binary_f32: unknown op %d", op);
   }
+}
+
+extern "C" int twg_where_f32(const TwgIterDesc* desc, const uint8_t* cond, const float* a, const float* b, float* out,
+                             void* stream) {
+  void* ptrs[4] = {out, const_cast<uint8_t*>(cond), const_cast<float*>(a), const_cast<float*>(b)};
+  return launch_pointwise(WhereF32{}, desc, ptrs, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int twg_masked_fill_f32(const TwgIterDesc* desc, const float* self, const uint8_t* mask, float value,
+                                   float* out, void* stream) {
+  void* ptrs[3] = {out, const_cast<float*>(self), const_cast<uint8_t*>(mask)};
+  return launch_pointwise(MaskedFillF32{value}, desc, ptrs, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int twg_compare_f32(int op, const TwgIterDesc* desc, const float* a, const float* b, float scalar,

@@ -31,6 +31,7 @@ constexpr int kBlock = 256;  // threads per CTA of the dense and strided kernels
 __device__ __forceinline__ float f_add(float a, float b, float alpha) { return __fmaf_rn(alpha, b, a); }
 __device__ __forceinline__ float f_mul(float a, float b) { return __fmul_rn(a, b); }
 // max(0,x) that keeps NaN and -0.0 (clamp_min semantics of the CPU kernel).
+__device__ __forceinline__ float f_div(float a, float b) { return __fdiv_rn(a, b); }
 __device__ __forceinline__ float f_relu(float x) { return (x < 0.0f) ? 0.0f : x; }
 __device__ __forceinline__ float f_abs(float x) { return fabsf(x); }
 __device__ __forceinline__ float f_silu(float x) {

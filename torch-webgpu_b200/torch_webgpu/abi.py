@@ -20,7 +20,7 @@ MAX_DIMS = 8
 MAX_TENSORS = 8
 
 UNARY = {"copy": 0, "relu": 1, "gelu_tanh": 2, "silu": 3, "gelu_erf": 4, "abs": 5}
-BINARY = {"add": 0, "mul": 1, "fused_add_relu": 2}
+BINARY = {"add": 0, "mul": 1, "fused_add_relu": 2, "div": 3}
 COMPARE = {"eq": 0, "ne": 1, "lt": 2, "le": 3, "gt": 4, "ge": 5}
 PATHS = {0: "none", 1: "dense", 2: "tile", 3: "strided32", 4: "strided64"}
 
@@ -99,6 +99,9 @@ SIGNATURES = {
     "twg_unary_f32": (c_int, [c_int, POINTER(IterDesc), c_void_p, c_void_p, c_void_p]),
     "twg_binary_f32": (c_int, [c_int, POINTER(IterDesc), c_void_p, c_void_p, c_float, c_void_p, c_void_p]),
     "twg_compare_f32": (c_int, [c_int, POINTER(IterDesc), c_void_p, c_void_p, c_float, c_void_p, c_void_p]),
+    "twg_convert": (c_int, [POINTER(IterDesc), c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "twg_where_f32": (c_int, [POINTER(IterDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "twg_masked_fill_f32": (c_int, [POINTER(IterDesc), c_void_p, c_void_p, c_float, c_void_p, c_void_p]),
     "twg_bitwise_and": (c_int, [POINTER(IterDesc), c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "twg_masked_select_workspace_bytes": (c_size_t, [c_int64]),
     "twg_masked_select_f32": (c_int, [POINTER(IterDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -281,6 +284,45 @@ def unary(op: str, x: np.ndarray, *, out_like: np.ndarray | None = None, pad: in
                                                                                           stream=stream, pad_front=pad)
     d = make_desc(x.shape, [do, dx])
     check(lib().twg_unary_f32(UNARY[op], byref(d), dx.ptr, do.ptr, stream))
+    return do.numpy(stream)
+
+
+# TwgDtype by numpy dtype; bfloat16 travels as its uint16 bit pattern with dtype name "bf16"
+DTYPES = {"uint8": 0, "int8": 1, "int16": 2, "int32": 3, "int64": 4, "float16": 5, "bf16": 6, "float32": 7,
+          "float64": 8, "bool": 9}
+_NP_OF = {"uint8": np.uint8, "int8": np.int8, "int16": np.int16, "int32": np.int32, "int64": np.int64,
+          "float16": np.float16, "bf16": np.uint16, "float32": np.float32, "float64": np.float64, "bool": np.bool_}
+
+
+def convert(x: np.ndarray, src: str, dst: str, *, pad: int = 0, stream=None) -> np.ndarray:
+    """x holds `src` elements (uint16 bit patterns for "bf16"); returns the `dst` elements."""
+    raw = x.view(np.uint8) if src == "bool" else x
+    dx = DeviceArray(raw, stream=stream, pad_front=pad)
+    out_np = np.uint8 if dst == "bool" else _NP_OF[dst]
+    do = DeviceArray.empty(x.shape, out_np, stream=stream, pad_front=pad)
+    d = make_desc(x.shape, [do, dx])
+    check(lib().twg_convert(byref(d), DTYPES[src], DTYPES[dst], dx.ptr, do.ptr, stream))
+    out = do.numpy(stream)
+    return out.view(np.bool_) if dst == "bool" else out
+
+
+def where(cond: np.ndarray, a: np.ndarray, b: np.ndarray, *, pad: int = 0, stream=None) -> np.ndarray:
+    shape = np.broadcast_shapes(cond.shape, a.shape, b.shape)
+    dc = DeviceArray(cond.view(np.uint8), stream=stream, pad_front=pad)
+    da, db = DeviceArray(a, stream=stream, pad_front=pad), DeviceArray(b, stream=stream, pad_front=pad)
+    do = DeviceArray.empty(shape, np.float32, stream=stream, pad_front=pad)
+    d = make_desc(shape, [do, dc, da, db])
+    check(lib().twg_where_f32(byref(d), dc.ptr, da.ptr, db.ptr, do.ptr, stream))
+    return do.numpy(stream)
+
+
+def masked_fill(x: np.ndarray, mask: np.ndarray, value: float, *, pad: int = 0, stream=None) -> np.ndarray:
+    shape = np.broadcast_shapes(x.shape, mask.shape)
+    dx = DeviceArray(x, stream=stream, pad_front=pad)
+    dm = DeviceArray(mask.view(np.uint8), stream=stream, pad_front=pad)
+    do = DeviceArray.empty(shape, np.float32, stream=stream, pad_front=pad)
+    d = make_desc(shape, [do, dx, dm])
+    check(lib().twg_masked_fill_f32(byref(d), dx.ptr, dm.ptr, value, do.ptr, stream))
     return do.numpy(stream)
 
 
