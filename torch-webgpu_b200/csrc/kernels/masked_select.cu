@@ -43,17 +43,22 @@ struct MsShared {
 //
 // A CTA owns a chunk of CH consecutive tiles of 4096 elements.
 //   Phase A  reads the chunk's mask (1 byte per element), keeps it in shared memory packed to one
-//            bit per element, counts its selected elements and publishes the count.  The chain of
-//            dependent CTAs therefore has one link per chunk, not per tile, and its latency is
-//            amortised over CH tiles of streaming.
-//   Phase B  walks the tiles with a running offset.  The mask comes from shared memory, so src
-//            quads whose four mask bytes are all zero are never fetched, and the next tile's src
-//            loads are issued before the current tile is ranked and flushed.  The look-back is
-//            resolved as late as possible - after the first tile is staged, right before its
-//            flush - so that most predecessors have published by then.
+//            bit per element, and counts the selected elements of every warp span (512 elements)
+//            of every tile.  The chunk count is published at once: the chain of dependent CTAs has
+//            one link per chunk, not per tile, and its latency is amortised over CH tiles.
+//   Phase B  With the table of phase A each warp knows where its run of every tile starts inside
+//            the chunk before it has looked at a single src value, so there is no barrier and no
+//            exchange between warps: a warp loads its span (src quads whose four mask bits are
+//            all zero are never fetched; the next tile's loads are issued before the current one
+//            is ranked), ranks it with popc + a warp scan, stages into its own 2 KB region and
+//            writes its run out, tile after tile.  The look-back is resolved as late as possible
+//            - after tile 0 is staged, right before its flush - so that most predecessors have
+//            published by then; the two barriers around it are the only CTA-wide ones.
 // In a tile a warp covers 512 consecutive elements as 4 sub-rounds of 32 quads; lane l owns quad
 // j*32+l of sub-round j, so src is read as 512-byte runs.  HBM sees every mask byte and every
-// selected sector of src once.
+// selected sector of src once.  (An earlier form ranked across the eight warps of a tile with two
+// barriers per tile; ncu showed it issue-bound at 31 instructions per element with the barrier
+// among the top stalls.  Measured, 2^30 elements at 41 % density: 1.246 ms -> 1.197 ms.)
 // ------------------------------------------------------------------------------------------
 template <bool ROWMASK>
 __device__ __forceinline__ u32 mask_quad(const u8* mask, i64 e, i64 n, const FastDiv32& row_len) {
@@ -76,11 +81,20 @@ __device__ __forceinline__ u32 mask_quad(const u8* mask, i64 e, i64 n, const Fas
 __device__ __forceinline__ u32 bytes_to_nibble(u32 w) { return ((w * 0x01020408u) >> 24) & 0xfu; }
 __device__ __forceinline__ u32 nibble_to_bytes(u32 nib) { return (nib * 0x00204081u) & 0x01010101u; }
 
+template <int CH>
+struct MsDenseShared {
+  float stage[kMsRound];  // warp w stages into [w*512, (w+1)*512)
+  alignas(16) unsigned short cnt[CH][kMsWarps];
+  u32 reduce[kMsWarps];
+  i64 tile;
+  i64 excl;
+};
+
 template <int CH, bool ROWMASK>
 __global__ void __launch_bounds__(kMsThreads, 4)
     ms_dense_kernel(const float* src, const u8* mask, float* out, i64 n, i64 nchunks, u64* ticket, u64* desc,
-                    i64* result, i64 poll_budget, FastDiv32 row_len) {
-  __shared__ MsShared sm;
+                     i64* result, i64 poll_budget, FastDiv32 row_len) {
+  __shared__ MsDenseShared<CH> sm;
   __shared__ u32 bits[CH * (kMsRound / 32)];  // the chunk's mask, one bit per element
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   i64 chunk = blockIdx.x;
@@ -93,7 +107,7 @@ __global__ void __launch_bounds__(kMsThreads, 4)
   const i64 chunk_base = chunk * (i64)(CH * kMsRound);
   const bool full_chunk = chunk_base + (i64)(CH * kMsRound) <= n;
 
-  // ---- phase A: mask -> bits, count ----
+  // ---- phase A: mask -> bits, counts per (tile, warp span), chunk count ----
   u32 c = 0;
   if (!ROWMASK && full_chunk) {
     unsigned short* bits16 = reinterpret_cast<unsigned short*>(bits);
@@ -102,28 +116,34 @@ __global__ void __launch_bounds__(kMsThreads, 4)
       uint4 q = ld_v4(mask + chunk_base + (i64)i * kMsRound + threadIdx.x * 16);
       q.x = __vcmpne4(q.x, 0u) & 0x01010101u; q.y = __vcmpne4(q.y, 0u) & 0x01010101u;
       q.z = __vcmpne4(q.z, 0u) & 0x01010101u; q.w = __vcmpne4(q.w, 0u) & 0x01010101u;
-      c += __popc(q.x) + __popc(q.y) + __popc(q.z) + __popc(q.w);
+      const u32 ci = __popc(q.x) + __popc(q.y) + __popc(q.z) + __popc(q.w);
+      c += ci;
       bits16[i * kMsThreads + threadIdx.x] = (unsigned short)(bytes_to_nibble(q.x) | (bytes_to_nibble(q.y) << 4) |
                                                                (bytes_to_nibble(q.z) << 8) | (bytes_to_nibble(q.w) << 12));
+      const u32 span = __reduce_add_sync(0xffffffffu, ci);  // this warp's 512 bytes are exactly its span of tile i
+      if (lane == 0) sm.cnt[i][warp] = (unsigned short)span;
     }
   } else {
-    // one word of bits = 32 consecutive elements; with a row mask and rows that are a multiple
-    // of 32 long, all of them share one row flag
+    // one word of bits = 32 consecutive elements, 16 words = one warp span: half a warp per span
     const bool row_words = ROWMASK && full_chunk && (row_len.d % 32u) == 0u;
     for (int g = threadIdx.x; g < CH * (kMsRound / 32); g += kMsThreads) {
-      u32 word = 0;
+      u32 word = 0, cw = 0;
       if (row_words) {
         word = ld_b8(mask + row_len.div((u32)(chunk_base + (i64)g * 32))) != 0u ? 0xffffffffu : 0u;
-        c += word & 32u;
+        cw = word & 32u;
       } else {
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const u32 w = mask_quad<ROWMASK>(mask, chunk_base + ((i64)g * 8 + k) * 4, n, row_len);
-          c += __popc(w);
+          cw += __popc(w);
           word |= bytes_to_nibble(w) << (4 * k);
         }
       }
       bits[g] = word;
+      c += cw;
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) cw += __shfl_xor_sync(0xffffffffu, cw, o);
+      if ((lane & 15) == 0) sm.cnt[g >> 7][(g & 127) >> 4] = (unsigned short)cw;
     }
   }
 #pragma unroll
@@ -135,7 +155,7 @@ __global__ void __launch_bounds__(kMsThreads, 4)
   for (int w = 0; w < kMsWarps; ++w) chunk_total += sm.reduce[w];
   if (threadIdx.x == 0) lookback_publish(chunk, chunk_total, desc, poll_budget);
 
-  // ---- phase B: compact tile by tile ----
+  // ---- phase B: every warp compacts its span of every tile on its own ----
   u32 m[4], v[4][4];
   auto load_tile = [&](int t) {
     const i64 tb = chunk_base + (i64)t * kMsRound + (i64)warp * 512;
@@ -145,7 +165,7 @@ __global__ void __launch_bounds__(kMsThreads, 4)
       const i64 e = tb + (i64)(j * 32 + lane) * 4;
       m[j] = nibble_to_bytes((bits[t * (kMsRound / 32) + (q >> 3)] >> ((q & 7) * 4)) & 0xfu);  // 0 beyond n
       if (m[j] != 0u) {
-        if (e + 3 < n) {
+        if (full_chunk || e + 3 < n) {
           const uint4 x = ld_v4(src + e);
           v[j][0] = x.x; v[j][1] = x.y; v[j][2] = x.z; v[j][3] = x.w;
         } else {
@@ -156,7 +176,8 @@ __global__ void __launch_bounds__(kMsThreads, 4)
     }
   };
   const int tiles_here = full_chunk ? CH : (int)((n - chunk_base + kMsRound - 1) / kMsRound);
-  i64 running = 0;
+  float* region = sm.stage + warp * 512;
+  u32 tile_off = 0;  // selected elements of the chunk's earlier tiles
   load_tile(0);
   for (int t = 0; t < tiles_here; ++t) {
     u32 mm[4], vv[4][4];
@@ -166,9 +187,24 @@ __global__ void __launch_bounds__(kMsThreads, 4)
 #pragma unroll
       for (int b = 0; b < 4; ++b) vv[j][b] = v[j][b];
     }
-    if (t + 1 < tiles_here) load_tile(t + 1);  // in flight while this tile is ranked and flushed
+    if (t + 1 < tiles_here) load_tile(t + 1);  // in flight while this tile is ranked and written out
 
-    // ranks: per-sub-round counts packed into one word (each field <= 128 after the warp scan)
+    // where this warp's run starts inside the chunk: the table of phase A
+    const uint4 row = *reinterpret_cast<const uint4*>(sm.cnt[t]);
+    const u32 c01 = row.x, c23 = row.y, c45 = row.z, c67 = row.w;
+    const u32 pair[4] = {(c01 & 0xffffu) + (c01 >> 16), (c23 & 0xffffu) + (c23 >> 16), (c45 & 0xffffu) + (c45 >> 16),
+                         (c67 & 0xffffu) + (c67 >> 16)};
+    u32 warp_off = 0;
+#pragma unroll
+    for (int p = 0; p < 4; ++p)
+      if (2 * p + 1 < warp) warp_off += pair[p];
+    if (warp & 1) {
+      const u32 lo[4] = {c01 & 0xffffu, c23 & 0xffffu, c45 & 0xffffu, c67 & 0xffffu};
+      warp_off += lo[warp >> 1];
+    }
+    const u32 tile_total = pair[0] + pair[1] + pair[2] + pair[3];
+
+    // ranks inside the warp: per-sub-round counts packed into one word (each field <= 128)
     const u32 cnt = __popc(mm[0]) | (__popc(mm[1]) << 8) | (__popc(mm[2]) << 16) | (__popc(mm[3]) << 24);
     u32 incl = cnt;
 #pragma unroll
@@ -180,25 +216,18 @@ __global__ void __launch_bounds__(kMsThreads, 4)
     const u32 t0 = tot & 0xffu, t1 = (tot >> 8) & 0xffu, t2 = (tot >> 16) & 0xffu, t3 = tot >> 24;
     const u32 excl_w = incl - cnt;
     const u32 sub_base[4] = {0u, t0, t0 + t1, t0 + t1 + t2};
-    if (lane == 0) sm.warp_total[t & 1][warp] = t0 + t1 + t2 + t3;
-    __syncthreads();  // totals visible; the previous tile's flush has finished reading the stage
-    u32 warp_off = 0, tile_total = 0;
-#pragma unroll
-    for (int w = 0; w < kMsWarps; ++w) {
-      const u32 x = sm.warp_total[t & 1][w];
-      if (w < warp) warp_off += x;
-      tile_total += x;
-    }
+    const u32 run = t0 + t1 + t2 + t3;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       if (mm[j] != 0u) {
-        u32 pos = warp_off + sub_base[j] + ((excl_w >> (8 * j)) & 0xffu);
+        u32 pos = sub_base[j] + ((excl_w >> (8 * j)) & 0xffu);
 #pragma unroll
         for (int b = 0; b < 4; ++b)
-          if ((mm[j] >> (8 * b)) & 1u) sm.stage[pos++] = __uint_as_float(vv[j][b]);
+          if ((mm[j] >> (8 * b)) & 1u) region[pos++] = __uint_as_float(vv[j][b]);
       }
     }
     if (t == 0) {
+      // the look-back as late as possible: tile 0 is staged, most predecessors have published
       if (warp == 0) {
         const i64 excl = lookback_resolve(chunk, chunk_total, desc, result, poll_budget);
         if (lane == 0) {
@@ -206,10 +235,24 @@ __global__ void __launch_bounds__(kMsThreads, 4)
           if (chunk == nchunks - 1) result[0] = excl + (i64)chunk_total;
         }
       }
+      __syncthreads();
+    } else {
+      __syncwarp();
     }
-    __syncthreads();  // stage complete; in the first iteration also: sm.excl published
-    flush_stage(sm.stage, out, sm.excl + running, tile_total);
-    running += tile_total;
+    // this warp's run: 128-bit stores between the first and last 16-byte boundary
+    float* dst = out + sm.excl + tile_off + warp_off;
+    const u32 head = min(run, (u32)(((16u - (u32)(reinterpret_cast<unsigned long long>(dst) & 15ull)) & 15u) >> 2));
+    if ((u32)lane < head) dst[lane] = region[lane];
+    const u32 nvec = (run - head) >> 2;
+    float4* dst4 = reinterpret_cast<float4*>(dst + head);
+    for (u32 i = lane; i < nvec; i += 32) {
+      const float* r = region + head + 4 * i;
+      dst4[i] = make_float4(r[0], r[1], r[2], r[3]);
+    }
+    const u32 tail0 = head + 4 * nvec;
+    if (tail0 + lane < run) dst[tail0 + lane] = region[tail0 + lane];
+    tile_off += tile_total;
+    __syncwarp();  // the region is rewritten by the next tile
   }
 }
 
