@@ -60,6 +60,11 @@ struct MsShared {
 // barriers per tile; ncu showed it issue-bound at 31 instructions per element with the barrier
 // among the top stalls.  Measured, 2^30 elements at 41 % density: 1.246 ms -> 1.197 ms.)
 // ------------------------------------------------------------------------------------------
+// four arbitrary bytes -> four 0/1 bytes (non-zero counts as true): the carry of (b & 0x7f) + 0x7f
+// reaches bit 7 exactly when the low seven bits are non-zero
+__device__ __forceinline__ u32 nonzero_bytes(u32 w) {
+  return ((((w & 0x7f7f7f7fu) + 0x7f7f7f7fu) | w) >> 7) & 0x01010101u;
+}
 template <bool ROWMASK>
 __device__ __forceinline__ u32 mask_quad(const u8* mask, i64 e, i64 n, const FastDiv32& row_len) {
   u32 w = 0;
@@ -73,13 +78,12 @@ __device__ __forceinline__ u32 mask_quad(const u8* mask, i64 e, i64 n, const Fas
       for (int b = 0; b < 4; ++b)
         if (e + b < n) w |= ld_b8(mask + e + b) << (8 * b);
     }
-    w = __vcmpne4(w, 0u) & 0x01010101u;
+    w = nonzero_bytes(w);
   }
   return w;
 }
-// four 0/1 bytes <-> one nibble (the products have no colliding partial terms, so no carries)
+// four 0/1 bytes -> one nibble (the product has no colliding partial terms, so no carries)
 __device__ __forceinline__ u32 bytes_to_nibble(u32 w) { return ((w * 0x01020408u) >> 24) & 0xfu; }
-__device__ __forceinline__ u32 nibble_to_bytes(u32 nib) { return (nib * 0x00204081u) & 0x01010101u; }
 
 template <int CH>
 struct MsDenseShared {
@@ -114,12 +118,11 @@ __global__ void __launch_bounds__(kMsThreads, 4)
 #pragma unroll
     for (int i = 0; i < CH; ++i) {
       uint4 q = ld_v4(mask + chunk_base + (i64)i * kMsRound + threadIdx.x * 16);
-      q.x = __vcmpne4(q.x, 0u) & 0x01010101u; q.y = __vcmpne4(q.y, 0u) & 0x01010101u;
-      q.z = __vcmpne4(q.z, 0u) & 0x01010101u; q.w = __vcmpne4(q.w, 0u) & 0x01010101u;
-      const u32 ci = __popc(q.x) + __popc(q.y) + __popc(q.z) + __popc(q.w);
+      const u32 sixteen = bytes_to_nibble(nonzero_bytes(q.x)) | (bytes_to_nibble(nonzero_bytes(q.y)) << 4) |
+                          (bytes_to_nibble(nonzero_bytes(q.z)) << 8) | (bytes_to_nibble(nonzero_bytes(q.w)) << 12);
+      const u32 ci = __popc(sixteen);
       c += ci;
-      bits16[i * kMsThreads + threadIdx.x] = (unsigned short)(bytes_to_nibble(q.x) | (bytes_to_nibble(q.y) << 4) |
-                                                               (bytes_to_nibble(q.z) << 8) | (bytes_to_nibble(q.w) << 12));
+      bits16[i * kMsThreads + threadIdx.x] = (unsigned short)sixteen;
       const u32 span = __reduce_add_sync(0xffffffffu, ci);  // this warp's 512 bytes are exactly its span of tile i
       if (lane == 0) sm.cnt[i][warp] = (unsigned short)span;
     }
@@ -156,21 +159,24 @@ __global__ void __launch_bounds__(kMsThreads, 4)
   if (threadIdx.x == 0) lookback_publish(chunk, chunk_total, desc, poll_budget);
 
   // ---- phase B: every warp compacts its span of every tile on its own ----
-  u32 m[4], v[4][4];
-  auto load_tile = [&](int t) {
+  struct TileRegs {
+    u32 m[4];     // the four mask bits of this lane's quad in each sub-round
+    u32 v[4][4];  // its src values (loaded only where a bit is set)
+  };
+  auto load_tile = [&](TileRegs& r, int t) {
     const i64 tb = chunk_base + (i64)t * kMsRound + (i64)warp * 512;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int q = warp * 128 + j * 32 + lane;
       const i64 e = tb + (i64)(j * 32 + lane) * 4;
-      m[j] = nibble_to_bytes((bits[t * (kMsRound / 32) + (q >> 3)] >> ((q & 7) * 4)) & 0xfu);  // 0 beyond n
-      if (m[j] != 0u) {
+      r.m[j] = (bits[t * (kMsRound / 32) + (q >> 3)] >> ((q & 7) * 4)) & 0xfu;  // 0 beyond n
+      if (r.m[j] != 0u) {
         if (full_chunk || e + 3 < n) {
           const uint4 x = ld_v4(src + e);
-          v[j][0] = x.x; v[j][1] = x.y; v[j][2] = x.z; v[j][3] = x.w;
+          r.v[j][0] = x.x; r.v[j][1] = x.y; r.v[j][2] = x.z; r.v[j][3] = x.w;
         } else {
 #pragma unroll
-          for (int b = 0; b < 4; ++b) v[j][b] = (e + b < n) ? ld_b32(src + e + b) : 0u;
+          for (int b = 0; b < 4; ++b) r.v[j][b] = (e + b < n) ? ld_b32(src + e + b) : 0u;
         }
       }
     }
@@ -178,17 +184,7 @@ __global__ void __launch_bounds__(kMsThreads, 4)
   const int tiles_here = full_chunk ? CH : (int)((n - chunk_base + kMsRound - 1) / kMsRound);
   float* region = sm.stage + warp * 512;
   u32 tile_off = 0;  // selected elements of the chunk's earlier tiles
-  load_tile(0);
-  for (int t = 0; t < tiles_here; ++t) {
-    u32 mm[4], vv[4][4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      mm[j] = m[j];
-#pragma unroll
-      for (int b = 0; b < 4; ++b) vv[j][b] = v[j][b];
-    }
-    if (t + 1 < tiles_here) load_tile(t + 1);  // in flight while this tile is ranked and written out
-
+  auto compact_tile = [&](const TileRegs& r, int t) {
     // where this warp's run starts inside the chunk: the table of phase A
     const uint4 row = *reinterpret_cast<const uint4*>(sm.cnt[t]);
     const u32 c01 = row.x, c23 = row.y, c45 = row.z, c67 = row.w;
@@ -205,7 +201,7 @@ __global__ void __launch_bounds__(kMsThreads, 4)
     const u32 tile_total = pair[0] + pair[1] + pair[2] + pair[3];
 
     // ranks inside the warp: per-sub-round counts packed into one word (each field <= 128)
-    const u32 cnt = __popc(mm[0]) | (__popc(mm[1]) << 8) | (__popc(mm[2]) << 16) | (__popc(mm[3]) << 24);
+    const u32 cnt = __popc(r.m[0]) | (__popc(r.m[1]) << 8) | (__popc(r.m[2]) << 16) | (__popc(r.m[3]) << 24);
     u32 incl = cnt;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -219,11 +215,11 @@ __global__ void __launch_bounds__(kMsThreads, 4)
     const u32 run = t0 + t1 + t2 + t3;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      if (mm[j] != 0u) {
+      if (r.m[j] != 0u) {
         u32 pos = sub_base[j] + ((excl_w >> (8 * j)) & 0xffu);
 #pragma unroll
         for (int b = 0; b < 4; ++b)
-          if ((mm[j] >> (8 * b)) & 1u) region[pos++] = __uint_as_float(vv[j][b]);
+          if ((r.m[j] >> b) & 1u) region[pos++] = __uint_as_float(r.v[j][b]);
       }
     }
     if (t == 0) {
@@ -246,13 +242,20 @@ __global__ void __launch_bounds__(kMsThreads, 4)
     const u32 nvec = (run - head) >> 2;
     float4* dst4 = reinterpret_cast<float4*>(dst + head);
     for (u32 i = lane; i < nvec; i += 32) {
-      const float* r = region + head + 4 * i;
-      dst4[i] = make_float4(r[0], r[1], r[2], r[3]);
+      const float* s4 = region + head + 4 * i;
+      dst4[i] = make_float4(s4[0], s4[1], s4[2], s4[3]);
     }
     const u32 tail0 = head + 4 * nvec;
     if (tail0 + lane < run) dst[tail0 + lane] = region[tail0 + lane];
     tile_off += tile_total;
     __syncwarp();  // the region is rewritten by the next tile
+  };
+  TileRegs next;
+  load_tile(next, 0);
+  for (int t = 0; t < tiles_here; ++t) {
+    const TileRegs cur = next;
+    if (t + 1 < tiles_here) load_tile(next, t + 1);  // in flight while this tile is ranked and written out
+    compact_tile(cur, t);
   }
 }
 
