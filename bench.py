@@ -253,7 +253,9 @@ def workload_config(n_gpus: int) -> dict:
     return {"workload": "cfg5: y=relu(silu(a+b)+c); m=(y==0)&(a!=0); masked_select(a,m) over 64 x f32[4096,4096], "
                         "torch.compile(backend=webgpu_backend) fused chain + single-pass compaction",
             "global_batch": BATCH, "elements_per_step": BATCH * SLAB, "parallelism": f"batch-sharded x{n_gpus}",
-            "l2": "inputs (>= 1.5 GiB per rank) are larger than the 126 MB L2; no flush needed"}
+            "l2": "inputs (>= 1.5 GiB per rank) are larger than the 126 MB L2; no flush needed",
+            "pipelining": "every step ends with its count read-back to the host; the host collects the counts of "
+                          "step i while the stream already runs step i+1 (two sets of output buffers)"}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -590,12 +592,15 @@ def run_gpu_arm(args) -> None:
     for buf, h in zip(dev_in, host):
         abi.check(L.twg_memcpy_h2d(buf.ptr, h.data_ptr(), 4 * n, stream))
     d_mask = abi.DeviceBuffer(n, local_rank, stream)
-    d_out = abi.DeviceBuffer(4 * n, local_rank, stream)
-    t_res = torch.zeros(2, dtype=torch.int64, device=cuda_dev)       # [count, status], written by the kernel
-    t_all = torch.zeros(2 * world, dtype=torch.int64, device=cuda_dev)  # every rank's [count, status]
-    h_all = torch.zeros(2 * world, dtype=torch.int64, pin_memory=True)
+    # Two sets of everything a step writes and the host reads: the host picks up the counts of step
+    # i while the GPU already runs step i+1 (the stream never waits for the host).
     ws_bytes = L.twg_masked_select_workspace_bytes(n)
-    d_ws = abi.DeviceBuffer(ws_bytes, local_rank, stream)
+    d_out = [abi.DeviceBuffer(4 * n, local_rank, stream) for _ in range(2)]
+    d_ws = [abi.DeviceBuffer(ws_bytes, local_rank, stream) for _ in range(2)]
+    t_res = [torch.zeros(2, dtype=torch.int64, device=cuda_dev) for _ in range(2)]          # [count, status] of this rank
+    t_all = [torch.zeros(2 * world, dtype=torch.int64, device=cuda_dev) for _ in range(2)]  # every rank's [count, status]
+    h_all = [torch.zeros(2 * world, dtype=torch.int64, pin_memory=True) for _ in range(2)]
+    landed = [torch.cuda.Event() for _ in range(2)]
     h_res = torch.zeros(2, dtype=torch.int64, pin_memory=True)
     program = abi.fused_compile(abi.CHAIN_MASK_PROGRAM)
     assert abi.fused_kind(program) == "aot"
@@ -609,36 +614,48 @@ def run_gpu_arm(args) -> None:
     ev = Events(abi, 2 + 2 * steps)
     counts_seen = []
 
-    def step(i: int | None) -> None:
+    def launch(slot: int, i: int | None) -> None:
+        """Everything one step puts on the stream: fused chain, compaction, the all-gather of the
+        counts, their copy to pinned host memory."""
         if i is not None:
             ev.record(2 + 2 * i, stream)
         abi.check(L.twg_fused_launch(program, ctypes.byref(desc4), ptrs, stream))
         if i is not None:
             ev.record(3 + 2 * i, stream)
-        abi.check(L.twg_masked_select_f32(ctypes.byref(desc2), dev_in[0].ptr, d_mask.ptr, d_out.ptr, t_res.data_ptr(),
-                                          d_ws.ptr, ws_bytes, stream))
+        abi.check(L.twg_masked_select_f32(ctypes.byref(desc2), dev_in[0].ptr, d_mask.ptr, d_out[slot].ptr,
+                                          t_res[slot].data_ptr(), d_ws[slot].ptr, ws_bytes, stream))
         if world > 1:
-            dist.all_gather_into_tensor(t_all, t_res)   # 16 bytes per rank over NVLink
+            dist.all_gather_into_tensor(t_all[slot], t_res[slot])   # 16 bytes per rank over NVLink
         else:
-            t_all.copy_(t_res)
-        h_all.copy_(t_all, non_blocking=True)
-        torch.cuda.current_stream().synchronize()        # the step's one host sync: counts are needed on the host
-        counts = h_all[0::2].tolist()
-        if any(int(v) != 0 for v in h_all[1::2].tolist()):
-            raise RuntimeError(f"masked_select reported device status {h_all[1::2].tolist()}")
+            t_all[slot].copy_(t_res[slot])
+        h_all[slot].copy_(t_all[slot], non_blocking=True)
+        landed[slot].record()
+
+    def collect(slot: int) -> None:
+        """The step's host sync: its counts are needed on the host (output shape, global offset)."""
+        landed[slot].synchronize()
+        counts = h_all[slot][0::2].tolist()
+        if any(int(v) != 0 for v in h_all[slot][1::2].tolist()):
+            raise RuntimeError(f"masked_select reported device status {h_all[slot][1::2].tolist()}")
         h_res[0] = counts[rank]
         counts_seen.append((sum(counts[:rank]), sum(counts)))
 
-    for _ in range(warmup):
-        step(None)
+    def run_steps(count: int, timed: bool) -> None:
+        for i in range(count):
+            launch(i & 1, i if timed else None)
+            if i > 0:
+                collect((i - 1) & 1)
+        if count > 0:
+            collect((count - 1) & 1)
+
+    run_steps(warmup, False)
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     L.twg_reset_launch_count()
     ev.record(0, stream)
-    for i in range(steps):
-        step(i)
+    run_steps(steps, True)
     ev.record(1, stream)
     ev.sync(1)
     launches = int(L.twg_launch_count())
