@@ -212,6 +212,25 @@ def test_true_transpose_uses_the_tile_kernel(abi):
         assert abi.last_path() == "tile"
 
 
+def test_transposes_with_vector_tiles(abi):
+    """Shapes whose strides allow 128-bit accesses in interior tiles (multiples of 4), with scalar
+    edge tiles around them, operands of both orientations, and a misaligned case that must not."""
+    for rows, cols in [(256, 192), (260, 200), (64, 64), (68, 1028)]:
+        x = rnd(rows * cols, rows + 1).reshape(rows, cols)
+        y = rnd(rows * cols, cols + 2).reshape(cols, rows)
+        for pad in (0, 1):
+            assert_bit_equal(abi.unary("relu", x.T, pad=pad), oracle.unary("relu", x.T), f"relu T {rows}x{cols} pad={pad}")
+            assert abi.last_path() == "tile"
+            assert_bit_equal(abi.binary("add", x.T, y, alpha=0.5, pad=pad), oracle.binary("add", x.T, y, 0.5), "add T + dense")
+            assert_bit_equal(abi.binary("mul", y, x.T, pad=pad), oracle.binary("mul", y, x.T), "dense * T")
+        assert_close_ulp(abi.unary("gelu_erf", x.T), oracle.unary("gelu_erf", x.T), abs_floor=2e-6, what="gelu T")
+        out_like = np.empty((cols, rows), np.float32).T   # logical [rows, cols], dense along dimension 0
+        assert_bit_equal(abi.unary("relu", x, out_like=out_like), oracle.unary("relu", x), "relu into transposed out")
+        assert abi.last_path() == "tile"
+        c = np.random.default_rng(rows).random((cols, rows)) < 0.5
+        assert_bit_equal(abi.where(c, x.T, y), oracle.where(c, np.ascontiguousarray(x.T), y), "where with a transposed operand")
+
+
 def test_transposed_output_layout(abi):
     x = rnd(96 * 80, 7).reshape(96, 80)
     out_like = np.empty((80, 96), np.float32).T  # logical [96,80], dense along dimension 0

@@ -502,7 +502,7 @@ static int jit_launch(TwgFusedProgram* p, const TwgIterDesc* desc, void* const* 
     }
     case kPathTile: {
       TileDesc<NT> td;
-      fill_tile_desc<NT>(plan, &td);
+      fill_tile_desc<NT>(plan, &td, ptrs_in, p->an.in_byte_mask == 0u && p->an.out_byte_mask == 0u);
       void* args[] = {&ptrs, &td};
       r = g_dyn.LaunchKernel(m->tile, plan.grid, 1, 1, kTileX, kTileRows, 1, 0, cs, args, nullptr);
       break;

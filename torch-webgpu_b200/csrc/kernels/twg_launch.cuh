@@ -55,8 +55,10 @@ int plan_pointwise(const PwSig& sig, const TwgIterDesc* desc, void* const* ptrs,
 bool plan_tile(const TwgIterDesc& d, int nt, int tile_edge, PwPlan* plan);
 bool fits_32bit(const TwgIterDesc& d, int nt);
 
+// `ptrs` and `four_byte` (every operand is 4 bytes wide) decide whether interior tiles may use
+// 128-bit accesses; callers that leave them out get the scalar tile code.
 template <int NT>
-void fill_tile_desc(const PwPlan& p, TileDesc<NT>* td) {
+void fill_tile_desc(const PwPlan& p, TileDesc<NT>* td, void* const* ptrs = nullptr, bool four_byte = false) {
   td->shape0 = p.d.shape[0];
   td->shape1 = p.d.shape[1];
   td->tiles0 = p.tiles0;
@@ -65,6 +67,13 @@ void fill_tile_desc(const PwPlan& p, TileDesc<NT>* td) {
   td->ntiles = p.ntiles;
   for (int t = 0; t < NT; ++t) { td->s0[t] = p.d.strides[t][0]; td->s1[t] = p.d.strides[t][1]; }
   td->dim1_mask = p.dim1_mask;
+  bool vec = four_byte && ptrs != nullptr;
+  for (int t = 0; vec && t < NT; ++t) {
+    const bool along1 = (p.dim1_mask >> t) & 1u;
+    const i64 dense = along1 ? td->s1[t] : td->s0[t], other = along1 ? td->s0[t] : td->s1[t];
+    vec = dense == 1 && other % 4 == 0 && (reinterpret_cast<uintptr_t>(ptrs[t]) & 15u) == 0;
+  }
+  td->vec = vec ? 1u : 0u;
 }
 template <int NT>
 void fill_strided_desc(const TwgIterDesc& d, StridedDesc<NT, u32>* sd) {
@@ -99,7 +108,7 @@ int launch_pointwise(const F& f, const TwgIterDesc* desc, void* const* ptrs_in, 
       break;
     case kPathTile: {
       TileDesc<NT> td;
-      fill_tile_desc<NT>(plan, &td);
+      fill_tile_desc<NT>(plan, &td, ptrs_in, F::kInByteMask == 0u && F::kOutByteMask == 0u);
       pw_tile_kernel<F><<<plan.grid, dim3(kTileX, kTileRows), 0, stream>>>(ptrs, f, td);
       break;
     }

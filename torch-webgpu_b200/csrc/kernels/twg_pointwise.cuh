@@ -366,6 +366,8 @@ struct TileDesc {
   i64 ntiles;          // CTAs' worth of work: tiles, or padded super-block slots
   i64 s0[NT], s1[NT];
   u32 dim1_mask;
+  u32 vec;  // every operand is 4 bytes wide, 16-byte aligned, unit stride along its dense dimension
+            // and a multiple of 4 along the other: interior tiles may use 128-bit accesses
 };
 
 typedef u32 (*PwTileSmem)[kPwTile + 1];
@@ -468,10 +470,82 @@ __device__ __forceinline__ void pw_tile_one(const PwPtrs<PwTraits<F>::NT>& ptrs,
   tile_store_outputs<F, INTERIOR>(ptrs, d, t0, t1, smem, vout);
 }
 
+// Interior tile with 128-bit global accesses (TileDesc::vec).  The 256 threads are seen as 16x16:
+// thread (vx, vy) holds elements (i0 = 4 vx + c, i1 = vy + 16 r), c, r = 0..3 - four float4 along
+// dimension 0.  Operands dense along dimension 0 are loaded and stored in exactly that shape (a
+// warp access is two 256-byte runs).  Operands dense along dimension 1 are accessed as float4
+// along dimension 1 - thread (vx, vy) takes (i1 = 4 vx .. 4 vx + 3, i0 = vy + 16 r) - and turned
+// through a 64x64 shared tile whose 16-byte chunks are XOR-swizzled with (i0 >> 2), which makes
+// both the float4 row accesses and the scalar column accesses conflict-free without padding.
+template <class F>
+__device__ __forceinline__ void pw_tile_one_vec(const PwPtrs<PwTraits<F>::NT>& ptrs, const F& f,
+                                                const TileDesc<PwTraits<F>::NT>& d, i64 t0, i64 t1, u32* smem) {
+  constexpr int NS = F::NIN > 0 ? F::NIN : 1;
+  const int lin = threadIdx.y * kTileX + threadIdx.x;
+  const int vx = lin & 15, vy = lin >> 4;
+  u32 vin[kTileElems][NS], vout[kTileElems][F::NOUT];  // element r * 4 + c
+#pragma unroll
+  for (int k = 0; k < F::NIN; ++k) {
+    const int t = F::NOUT + k;
+    const u32* p = static_cast<const u32*>(ptrs.p[t]);
+    if ((d.dim1_mask >> t) & 1u) {
+      __syncthreads();  // the tile is free (previous operand gathered, previous tile stored)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int i0 = vy + 16 * r;
+        const uint4 q = ld_v4(p + (t0 + i0) * d.s0[t] + (t1 + 4 * vx));
+        *reinterpret_cast<uint4*>(smem + i0 * kPwTile + ((vx ^ ((i0 >> 2) & 15)) << 2)) = q;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int i1 = vy + 16 * r;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)  // row i0 = 4 vx + c, whose swizzle key is vx
+          vin[r * 4 + c][k] = smem[(4 * vx + c) * kPwTile + ((((i1 >> 2) ^ vx) & 15) << 2) + (i1 & 3)];
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const uint4 q = ld_v4(p + (t0 + 4 * vx) + (t1 + vy + 16 * r) * d.s1[t]);
+        vin[r * 4 + 0][k] = q.x; vin[r * 4 + 1][k] = q.y; vin[r * 4 + 2][k] = q.z; vin[r * 4 + 3][k] = q.w;
+      }
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < kTileElems; ++e) f(vin[e], vout[e]);
+#pragma unroll
+  for (int k = 0; k < F::NOUT; ++k) {
+    u32* p = static_cast<u32*>(ptrs.p[k]);
+    if ((d.dim1_mask >> k) & 1u) {
+      __syncthreads();  // previous use of the tile is finished
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int i1 = vy + 16 * r;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          smem[(4 * vx + c) * kPwTile + ((((i1 >> 2) ^ vx) & 15) << 2) + (i1 & 3)] = vout[r * 4 + c][k];
+      }
+      __syncthreads();
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int i0 = vy + 16 * r;
+        const uint4 q = *reinterpret_cast<const uint4*>(smem + i0 * kPwTile + ((vx ^ ((i0 >> 2) & 15)) << 2));
+        st_v4(p + (t0 + i0) * d.s0[k] + (t1 + 4 * vx), q);
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < 4; ++r)
+        st_v4(p + (t0 + 4 * vx) + (t1 + vy + 16 * r) * d.s1[k],
+              make_uint4(vout[r * 4 + 0][k], vout[r * 4 + 1][k], vout[r * 4 + 2][k], vout[r * 4 + 3][k]));
+    }
+  }
+}
+
 template <class F>
 __device__ __forceinline__ void pw_tile_body(const PwPtrs<PwTraits<F>::NT>& ptrs, const F& f,
                                              const TileDesc<PwTraits<F>::NT>& d) {
-  __shared__ u32 smem[kPwTile][kPwTile + 1];
+  __shared__ __align__(16) u32 smem[kPwTile][kPwTile + 1];
   for (i64 slot = blockIdx.x; slot < d.ntiles; slot += gridDim.x) {
     // Tiles are walked in super-blocks of 8x8, so that the CTAs running side by side touch
     // neighbouring pieces of the rows they share along dimension 0 and dimension 1 alike.
@@ -481,8 +555,17 @@ __device__ __forceinline__ void pw_tile_body(const PwPtrs<PwTraits<F>::NT>& ptrs
     const i64 b1 = (sb / d.sb0) * kTileSuper + within / kTileSuper;
     if (b0 >= d.tiles0 || b1 >= d.tiles1) continue;
     const i64 t0 = b0 * kPwTile, t1 = b1 * kPwTile;
-    if (t0 + kPwTile <= d.shape0 && t1 + kPwTile <= d.shape1) pw_tile_one<F, true>(ptrs, f, d, t0, t1, smem);
-    else pw_tile_one<F, false>(ptrs, f, d, t0, t1, smem);
+    if (t0 + kPwTile <= d.shape0 && t1 + kPwTile <= d.shape1) {
+      if constexpr (F::kInByteMask == 0u && F::kOutByteMask == 0u) {
+        if (d.vec) {
+          pw_tile_one_vec<F>(ptrs, f, d, t0, t1, &smem[0][0]);
+          continue;
+        }
+      }
+      pw_tile_one<F, true>(ptrs, f, d, t0, t1, smem);
+    } else {
+      pw_tile_one<F, false>(ptrs, f, d, t0, t1, smem);
+    }
   }
 }
 
