@@ -494,7 +494,7 @@ def run_case(args) -> None:
         fn = lambda: abi.check(L.twg_unary_f32(1, ctypes.byref(d), x.ptr, y.ptr, stream))
         nbytes = 8 * n
         bufs = [x, y]
-    elif args.case in ("masked_select", "masked_select_rowmask"):
+    elif args.case in ("masked_select", "masked_select_rowmask", "masked_select_transposed"):
         x, out = abi.DeviceBuffer(4 * n), abi.DeviceBuffer(4 * n)
         x.upload(host(n))
         res = abi.DeviceBuffer(16)
@@ -504,6 +504,12 @@ def run_case(args) -> None:
             mk = abi.DeviceBuffer(n)
             mk.upload((rng.random(n) < args.case_density).astype(np.uint8))
             d = dense(2, n)
+        elif args.case == "masked_select_transposed":
+            r = int(round(n ** 0.5))
+            n = r * r
+            mk = abi.DeviceBuffer(n)
+            mk.upload((rng.random(n) < args.case_density).astype(np.uint8))
+            d = abi.make_desc((r, r), [((r, r), (1, r)), ((r, r), (1, r))])   # src.t() and mask.t()
         else:
             r = int(round(n ** 0.5))
             n = r * r
@@ -513,7 +519,7 @@ def run_case(args) -> None:
         fn = lambda: abi.check(L.twg_masked_select_f32(ctypes.byref(d), x.ptr, mk.ptr, out.ptr, res.ptr, ws.ptr, wsb, stream))
         fn()
         k = int(res.download(np.int64, 2)[0])
-        nbytes = (5 if args.case == "masked_select" else 4) * n + 4 * k
+        nbytes = (4 if args.case == "masked_select_rowmask" else 5) * n + 4 * k
         bufs = [x, out, res, ws, mk]
     elif args.case == "fused_select":
         ins = [abi.DeviceBuffer(4 * n) for _ in range(3)]

@@ -408,7 +408,7 @@ def test_fused_program_compiled_at_run_time(abi):
         assert_bit_equal(flag, oracle.compare("gt", oracle.binary("mul", got_g, np.broadcast_to(y, x.shape).copy()), 0.5), "fused flag")
 
 
-@pytest.mark.parametrize("n", [1, 5, 4095, 8192, 8193, 100003, (1 << 22) + 7])
+@pytest.mark.parametrize("n", [1, 5, 4095, 7680, 7681, 8193, 100003, (1 << 22) + 7])
 def test_fused_select_equals_mask_then_masked_select(abi, n):
     a, bb, c = rnd(n, 85, -3, 3), rnd(n, 86, -3, 3), rnd(n, 87, -3, 3)
     a[::5] = 0.0

@@ -278,6 +278,27 @@ def test_config4_masked_select():
     assert torch.equal(got.cpu(), torch.masked_select(src, mask_b))
 
 
+def test_masked_select_of_permuted_operands():
+    """Large permuted operands are copied into logical order and take the dense path; small ones
+    and broadcasts keep the strided walk.  Either way the order is torch.masked_select's."""
+    g = torch.Generator().manual_seed(6)
+    x = torch.randn(1024, 2048, generator=g)
+    m = torch.rand(1024, 2048, generator=g) < 0.4
+    dx, dm = x.to("webgpu"), m.to("webgpu")
+    assert torch.equal(torch.masked_select(dx.t(), dm.t()).cpu(), torch.masked_select(x.t(), m.t()))
+    assert torch.equal(torch.masked_select(dx.t(), dm.t().contiguous()).cpu(), torch.masked_select(x.t(), m.t()))
+    assert torch.equal(torch.masked_select(dx, dm.t().contiguous().t()).cpu(), torch.masked_select(x, m))
+    assert torch.equal(torch.masked_select(dx[:, ::2], dm[:, ::2]).cpu(), torch.masked_select(x[:, ::2], m[:, ::2]))
+    row = m[:, :1].contiguous()
+    assert torch.equal(torch.masked_select(dx.t(), row.to("webgpu").t()).cpu(), torch.masked_select(x.t(), row.t()))
+    y = x.reshape(8, 128, 2048).permute(2, 0, 1)
+    my = m.reshape(8, 128, 2048).permute(2, 0, 1)
+    assert torch.equal(torch.masked_select(y.to("webgpu"), my.to("webgpu")).cpu(), torch.masked_select(y, my))
+    dy = dx.reshape(8, 128, 2048).permute(2, 0, 1)
+    dmy = dm.reshape(8, 128, 2048).permute(2, 0, 1)
+    assert torch.equal(torch.masked_select(dy, dmy).cpu(), torch.masked_select(y, my))
+
+
 def test_config5_compiled_chain():
     from torch_webgpu import webgpu_backend
     from torch_webgpu.compiler import webgpu_compiler as wc

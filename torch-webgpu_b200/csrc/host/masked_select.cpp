@@ -30,9 +30,23 @@ static TwgIterDesc rowmajor_desc(c10::IntArrayRef shape, const at::Tensor& self,
   return d;
 }
 
+// A permuted operand (no broadcast dimension, not contiguous) would be walked in logical order
+// with one useful element per 32-byte sector.  Copying it into logical order first runs at copy
+// bandwidth (the 2-D tile kernels) and lets the compaction take its dense path, which is several
+// times cheaper than the sector over-fetch for anything that does not fit in L2.  Broadcast
+// operands are left alone: their strided walk re-reads cached rows and materialising them would
+// multiply the traffic.
+static at::Tensor logical_order(const at::Tensor& t) {
+  if (t.is_contiguous() || t.numel() < (1 << 16)) return t;
+  for (int64_t d = 0; d < t.dim(); ++d)
+    if (t.size(d) > 1 && t.stride(d) == 0) return t;
+  return t.contiguous();
+}
+
 // Runs the compaction into `out_storage` (room for numel elements) and returns the count.
-static int64_t run_masked_select(const at::Tensor& self, const at::Tensor& mask, at::Tensor& out_storage,
+static int64_t run_masked_select(const at::Tensor& self_in, const at::Tensor& mask_in, at::Tensor& out_storage,
                                  c10::IntArrayRef shape) {
+  const at::Tensor self = logical_order(self_in), mask = logical_order(mask_in);
   const c10::DeviceIndex dev = self.device().index() < 0 ? core::current_device() : self.device().index();
   core::DeviceScope scope(dev);
   void* stream = core::current_stream(dev);

@@ -157,6 +157,54 @@ __global__ void __launch_bounds__(kMsThreads, 4)
 #pragma unroll
   for (int w = 0; w < kMsWarps; ++w) chunk_total += sm.reduce[w];
   if (threadIdx.x == 0) lookback_publish(chunk, chunk_total, desc, poll_budget);
+  const int tiles_here = full_chunk ? CH : (int)((n - chunk_base + kMsRound - 1) / kMsRound);
+
+  // ---- phase B for sparse chunks (fewer than one element in sixteen selected) ----
+  // Ranking, staging and quad loads cost the same whether anything is selected or not; here a
+  // lane walks the set bits of its 16 elements instead: one scalar load and one store per selected
+  // element, and spans that select nothing are skipped with one look at the table of phase A.
+  if (chunk_total * 16u < (u32)(CH * kMsRound)) {
+    if (warp == 0) {
+      const i64 excl = lookback_resolve(chunk, chunk_total, desc, result, poll_budget);
+      if (lane == 0) {
+        sm.excl = excl;
+        if (chunk == nchunks - 1) result[0] = excl + (i64)chunk_total;
+      }
+    }
+    __syncthreads();
+    float* chunk_out = out + sm.excl;
+    u32 tile_off = 0;
+    for (int t = 0; t < tiles_here; ++t) {
+      const u32 mine = sm.cnt[t][warp];
+      u32 before = 0, tile_total = 0;  // selected by the spans in front of this one / by the whole tile
+#pragma unroll
+      for (int w = 0; w < kMsWarps; ++w) {
+        const u32 x = sm.cnt[t][w];
+        if (w < warp) before += x;
+        tile_total += x;
+      }
+      if (mine != 0u) {
+        const u32 word = bits[t * (kMsRound / 32) + warp * 16 + (lane >> 1)];
+        u32 half = (word >> ((lane & 1) * 16)) & 0xffffu;  // this lane's 16 consecutive elements
+        const u32 cnt = __popc(half);
+        u32 incl = cnt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const u32 x = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl += x;
+        }
+        const float* from = src + chunk_base + (i64)t * kMsRound + (i64)warp * 512 + lane * 16;
+        float* to = chunk_out + tile_off + before + (incl - cnt);
+        while (half != 0u) {
+          const int bit = __ffs(half) - 1;
+          half &= half - 1u;
+          *to++ = __uint_as_float(ld_b32(from + bit));
+        }
+      }
+      tile_off += tile_total;
+    }
+    return;
+  }
 
   // ---- phase B: every warp compacts its span of every tile on its own ----
   struct TileRegs {
@@ -181,7 +229,6 @@ __global__ void __launch_bounds__(kMsThreads, 4)
       }
     }
   };
-  const int tiles_here = full_chunk ? CH : (int)((n - chunk_base + kMsRound - 1) / kMsRound);
   float* region = sm.stage + warp * 512;
   u32 tile_off = 0;  // selected elements of the chunk's earlier tiles
   auto compact_tile = [&](const TileRegs& r, int t) {
