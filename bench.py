@@ -494,7 +494,8 @@ def run_case(args) -> None:
         fn = lambda: abi.check(L.twg_unary_f32(1, ctypes.byref(d), x.ptr, y.ptr, stream))
         nbytes = 8 * n
         bufs = [x, y]
-    elif args.case in ("masked_select", "masked_select_rowmask", "masked_select_transposed"):
+    elif args.case in ("masked_select", "masked_select_rowmask", "masked_select_transposed", "masked_select_colmask",
+                       "masked_select_slice"):
         x, out = abi.DeviceBuffer(4 * n), abi.DeviceBuffer(4 * n)
         x.upload(host(n))
         res = abi.DeviceBuffer(16)
@@ -504,6 +505,18 @@ def run_case(args) -> None:
             mk = abi.DeviceBuffer(n)
             mk.upload((rng.random(n) < args.case_density).astype(np.uint8))
             d = dense(2, n)
+        elif args.case == "masked_select_colmask":
+            r = int(round(n ** 0.5))
+            n = r * r
+            mk = abi.DeviceBuffer(r)
+            mk.upload((rng.random(r) < args.case_density).astype(np.uint8))
+            d = abi.make_desc((r, r), [((r, r), (r, 1)), ((1, r), (1, 1))])   # one mask byte per column
+        elif args.case == "masked_select_slice":
+            r = int(round(n ** 0.5))
+            n = r * (r // 2)
+            mk = abi.DeviceBuffer(r * r)
+            mk.upload((rng.random(r * r) < args.case_density).astype(np.uint8))
+            d = abi.make_desc((r, r // 2), [((r, r // 2), (r, 2)), ((r, r // 2), (r, 2))])   # x[:, ::2], m[:, ::2]
         elif args.case == "masked_select_transposed":
             r = int(round(n ** 0.5))
             n = r * r
@@ -519,7 +532,7 @@ def run_case(args) -> None:
         fn = lambda: abi.check(L.twg_masked_select_f32(ctypes.byref(d), x.ptr, mk.ptr, out.ptr, res.ptr, ws.ptr, wsb, stream))
         fn()
         k = int(res.download(np.int64, 2)[0])
-        nbytes = (4 if args.case == "masked_select_rowmask" else 5) * n + 4 * k
+        nbytes = (4 if args.case in ("masked_select_rowmask", "masked_select_colmask") else 5) * n + 4 * k
         bufs = [x, out, res, ws, mk]
     elif args.case == "fused_select":
         ins = [abi.DeviceBuffer(4 * n) for _ in range(3)]

@@ -301,6 +301,25 @@ def test_masked_select_dense(abi, n, p):
         assert abi.last_path() == "dense"
 
 
+def test_masked_select_mixed_density(abi):
+    """Chunks on either side of the sparse / dense decision inside one call, and a sparse row mask."""
+    n = (1 << 22) + 4099
+    x = rnd(n, 71)
+    rng = np.random.default_rng(72)
+    mask = np.zeros(n, np.bool_)
+    third = n // 3
+    mask[:third] = rng.random(third) < 0.9
+    mask[third:2 * third] = rng.random(third) < 0.002
+    mask[2 * third:] = rng.random(n - 2 * third) < 0.06
+    mask[n - 1] = True
+    assert_bit_equal(abi.masked_select(x, mask), oracle.masked_select(x, mask), "mixed density")
+    rows, cols = 2048, 1024
+    y = rnd(rows * cols, 73).reshape(rows, cols)
+    rowmask = (rng.random((rows, 1)) < 0.01)
+    assert_bit_equal(abi.masked_select(y, rowmask), oracle.masked_select(y, rowmask), "sparse row mask")
+    assert abi.last_path() == "dense"
+
+
 @pytest.mark.parametrize("pad", [1, 2, 3])
 def test_masked_select_misaligned(abi, pad):
     n = 5 * 4096 + 123

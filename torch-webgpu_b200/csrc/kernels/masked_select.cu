@@ -18,6 +18,7 @@
 #include <atomic>
 #include <mutex>
 #include <cstdlib>
+#include <cstring>
 #include <string>
 
 namespace twg {
@@ -39,7 +40,10 @@ struct MsShared {
 // ------------------------------------------------------------------------------------------
 // Dense path: src contiguous and 16-byte aligned; the mask is either a dense bool array (16-byte
 // aligned) or, with ROWMASK, one bool per row of `row_len` elements (a [R,1] mask broadcast over
-// [R,C] with C % 4 == 0).
+// [R,C] with C % 4 == 0).  A third mode walks both operands through the iteration descriptor
+// (element index -> offsets with 32-bit multiply-shift division): slices, broadcast masks and
+// other non-dense layouts get the same chunking, at one index computation per mask byte and per
+// selected element.
 //
 // A CTA owns a chunk of CH consecutive tiles of 4096 elements.
 //   Phase A  reads the chunk's mask (1 byte per element), keeps it in shared memory packed to one
@@ -65,10 +69,53 @@ struct MsShared {
 __device__ __forceinline__ u32 nonzero_bytes(u32 w) {
   return ((((w & 0x7f7f7f7fu) + 0x7f7f7f7fu) | w) >> 7) & 0x01010101u;
 }
-template <bool ROWMASK>
-__device__ __forceinline__ u32 mask_quad(const u8* mask, i64 e, i64 n, const FastDiv32& row_len) {
+// How the chunked kernel addresses its operands.
+constexpr int kMsDense = 0;    // src and mask dense
+constexpr int kMsRowMask = 1;  // src dense, one mask byte per row
+constexpr int kMsStrided = 2;  // both through the iteration descriptor (32-bit index math)
+
+// Offsets of logical element `lin` in src and mask; returns its coordinate along dimension 0, so
+// that a caller walking consecutive elements can step by the dimension-0 strides until the
+// coordinate wraps.
+__device__ __forceinline__ u32 ms_offsets(const StridedDesc<2, u32>& d, u32 lin, u32& osrc, u32& omask) {
+  u32 q = d.shape[0].div(lin);
+  const u32 c0 = lin - q * d.shape[0].d;
+  osrc = c0 * d.strides[0][0];
+  omask = c0 * d.strides[1][0];
+#pragma unroll
+  for (int k = 1; k < kMaxDims; ++k) {
+    if (k >= d.ndim) break;
+    const u32 q2 = d.shape[k].div(q);
+    const u32 c = q - q2 * d.shape[k].d;
+    q = q2;
+    osrc += c * d.strides[0][k];
+    omask += c * d.strides[1][k];
+  }
+  return c0;
+}
+
+template <int MODE>
+__device__ __forceinline__ u32 mask_quad(const u8* mask, i64 e, i64 n, const FastDiv32& row_len,
+                                         const StridedDesc<2, u32>& sd) {
   u32 w = 0;
-  if constexpr (ROWMASK) {
+  if constexpr (MODE == kMsStrided) {
+    if (e < n) {
+      u32 os, om;
+      u32 c0 = ms_offsets(sd, (u32)e, os, om);
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        if (e + b < n) w |= (ld_b8(mask + om) != 0u ? 1u : 0u) << (8 * b);
+        if (b < 3) {
+          if (++c0 == sd.shape[0].d) {
+            if (e + b + 1 < n) c0 = ms_offsets(sd, (u32)(e + b + 1), os, om);
+          } else {
+            om += sd.strides[1][0];
+          }
+        }
+      }
+    }
+    return w;
+  } else if constexpr (MODE == kMsRowMask) {
     if (e < n) w = ld_b8(mask + row_len.div((u32)e)) != 0u ? 0x01010101u : 0u;  // n < 2^31 on this path
     if (e + 3 >= n && w) w &= (e + 2 < n) ? 0x00ffffffu : (e + 1 < n) ? 0x0000ffffu : 0x000000ffu;
   } else {
@@ -94,10 +141,11 @@ struct MsDenseShared {
   i64 excl;
 };
 
-template <int CH, bool ROWMASK>
+template <int CH, int MODE>
 __global__ void __launch_bounds__(kMsThreads, 4)
     ms_dense_kernel(const float* src, const u8* mask, float* out, i64 n, i64 nchunks, u64* ticket, u64* desc,
-                     i64* result, i64 poll_budget, FastDiv32 row_len) {
+                     i64* result, i64 poll_budget, FastDiv32 row_len, StridedDesc<2, u32> sd) {
+  constexpr bool ROWMASK = MODE == kMsRowMask;
   __shared__ MsDenseShared<CH> sm;
   __shared__ u32 bits[CH * (kMsRound / 32)];  // the chunk's mask, one bit per element
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -113,7 +161,7 @@ __global__ void __launch_bounds__(kMsThreads, 4)
 
   // ---- phase A: mask -> bits, counts per (tile, warp span), chunk count ----
   u32 c = 0;
-  if (!ROWMASK && full_chunk) {
+  if (MODE == kMsDense && full_chunk) {
     unsigned short* bits16 = reinterpret_cast<unsigned short*>(bits);
 #pragma unroll
     for (int i = 0; i < CH; ++i) {
@@ -126,6 +174,30 @@ __global__ void __launch_bounds__(kMsThreads, 4)
       const u32 span = __reduce_add_sync(0xffffffffu, ci);  // this warp's 512 bytes are exactly its span of tile i
       if (lane == 0) sm.cnt[i][warp] = (unsigned short)span;
     }
+  } else if constexpr (MODE == kMsStrided) {
+    // a warp takes whole spans; lane l looks at element 32 g + l of word g, so that neighbouring
+    // lanes read neighbouring mask bytes, and a ballot is the word
+    for (int sidx = warp; sidx < CH * kMsWarps; sidx += kMsWarps) {
+      u32 span_count = 0;
+#pragma unroll 4
+      for (int k = 0; k < 16; ++k) {
+        const int g = sidx * 16 + k;
+        const i64 e = chunk_base + (i64)g * 32 + lane;
+        bool nz = false;
+        if (e < n) {
+          u32 os, om;
+          ms_offsets(sd, (u32)e, os, om);
+          nz = ld_b8(mask + om) != 0u;
+        }
+        const u32 word = __ballot_sync(0xffffffffu, nz);
+        if (lane == 0) bits[g] = word;
+        span_count += __popc(word);
+      }
+      if (lane == 0) {
+        sm.cnt[sidx >> 3][sidx & 7] = (unsigned short)span_count;
+        c += span_count;
+      }
+    }
   } else {
     // one word of bits = 32 consecutive elements, 16 words = one warp span: half a warp per span
     const bool row_words = ROWMASK && full_chunk && (row_len.d % 32u) == 0u;
@@ -137,7 +209,7 @@ __global__ void __launch_bounds__(kMsThreads, 4)
       } else {
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const u32 w = mask_quad<ROWMASK>(mask, chunk_base + ((i64)g * 8 + k) * 4, n, row_len);
+          const u32 w = mask_quad<MODE>(mask, chunk_base + ((i64)g * 8 + k) * 4, n, row_len, sd);
           cw += __popc(w);
           word |= bytes_to_nibble(w) << (4 * k);
         }
@@ -193,12 +265,23 @@ __global__ void __launch_bounds__(kMsThreads, 4)
           const u32 x = __shfl_up_sync(0xffffffffu, incl, o);
           if (lane >= o) incl += x;
         }
-        const float* from = src + chunk_base + (i64)t * kMsRound + (i64)warp * 512 + lane * 16;
+        const i64 first = chunk_base + (i64)t * kMsRound + (i64)warp * 512 + lane * 16;
         float* to = chunk_out + tile_off + before + (incl - cnt);
+        u32 first_os = 0, first_c0 = 0;
+        if constexpr (MODE == kMsStrided) {
+          u32 om;
+          if (half != 0u) first_c0 = ms_offsets(sd, (u32)first, first_os, om);
+        }
         while (half != 0u) {
           const int bit = __ffs(half) - 1;
           half &= half - 1u;
-          *to++ = __uint_as_float(ld_b32(from + bit));
+          if constexpr (MODE == kMsStrided) {
+            u32 o = first_os + bit * sd.strides[0][0], om;
+            if (first_c0 + bit >= sd.shape[0].d) ms_offsets(sd, (u32)(first + bit), o, om);
+            *to++ = __uint_as_float(ld_b32(src + o));
+          } else {
+            *to++ = __uint_as_float(ld_b32(src + first + bit));
+          }
         }
       }
       tile_off += tile_total;
@@ -218,7 +301,25 @@ __global__ void __launch_bounds__(kMsThreads, 4)
       const int q = warp * 128 + j * 32 + lane;
       const i64 e = tb + (i64)(j * 32 + lane) * 4;
       r.m[j] = (bits[t * (kMsRound / 32) + (q >> 3)] >> ((q & 7) * 4)) & 0xfu;  // 0 beyond n
-      if (r.m[j] != 0u) {
+      if constexpr (MODE == kMsStrided) {
+        if (r.m[j] != 0u) {  // set bits only exist below n
+          u32 os0, om;
+          const u32 c0 = ms_offsets(sd, (u32)e, os0, om);
+          if (sd.strides[0][0] == 1u && c0 + 3 < sd.shape[0].d && ((reinterpret_cast<unsigned long long>(src + os0) & 15ull) == 0)) {
+            const uint4 x = ld_v4(src + os0);  // the quad is one aligned 16-byte piece of src
+            r.v[j][0] = x.x; r.v[j][1] = x.y; r.v[j][2] = x.z; r.v[j][3] = x.w;
+          } else {
+            // neighbouring elements share sectors: let L1 serve the repeats
+#pragma unroll
+            for (int b = 0; b < 4; ++b)
+              if ((r.m[j] >> b) & 1u) {
+                u32 o = os0 + b * sd.strides[0][0];
+                if (c0 + b >= sd.shape[0].d) ms_offsets(sd, (u32)(e + b), o, om);  // the quad runs into the next row
+                r.v[j][b] = __float_as_uint(__ldg(src + o));
+              }
+          }
+        }
+      } else if (r.m[j] != 0u) {
         if (full_chunk || e + 3 < n) {
           const uint4 x = ld_v4(src + e);
           r.v[j][0] = x.x; r.v[j][1] = x.y; r.v[j][2] = x.z; r.v[j][3] = x.w;
@@ -307,7 +408,7 @@ __global__ void __launch_bounds__(kMsThreads, 4)
 }
 
 // ------------------------------------------------------------------------------------------
-// Strided / broadcast path.  Logical element e (row-major over the broadcast shape) is mapped to
+// Strided / broadcast path for iterations whose offsets need 64 bits (and flipped views).  Logical element e (row-major over the broadcast shape) is mapped to
 // a src offset and a mask offset with the descriptor's strides (0 = broadcast).  Lane l of a warp
 // owns elements warp_base + i*32 + l, i = 0..15, so that a ballot over the warp is the selection
 // bitmap of 32 consecutive elements and popc of its low bits is the rank.
@@ -400,11 +501,12 @@ bool ms_use_ticket() {
   return v;
 }
 
-template <bool ROWMASK>
+template <int MODE>
 static void launch_dense(int chunk_tiles, unsigned nchunks, cudaStream_t s, const float* src, const u8* mask, float* out,
-                         i64 n, u64* ticket, u64* tdesc, i64* result, i64 budget, FastDiv32 row_len) {
+                         i64 n, u64* ticket, u64* tdesc, i64* result, i64 budget, FastDiv32 row_len,
+                         const StridedDesc<2, u32>& sd) {
 #define TWG_MS_LAUNCH(CH) \
-  ms_dense_kernel<CH, ROWMASK><<<nchunks, kMsThreads, 0, s>>>(src, mask, out, n, nchunks, ticket, tdesc, result, budget, row_len)
+  ms_dense_kernel<CH, MODE><<<nchunks, kMsThreads, 0, s>>>(src, mask, out, n, nchunks, ticket, tdesc, result, budget, row_len, sd)
   switch (chunk_tiles) {
     case 1: TWG_MS_LAUNCH(1); break;
     case 2: TWG_MS_LAUNCH(2); break;
@@ -461,7 +563,10 @@ extern "C" int twg_masked_select_f32(const TwgIterDesc* desc, const float* src, 
   // dimension 1 walks rows in both
   const bool rowmask = d.ndim == 2 && d.strides[0][0] == 1 && d.strides[1][0] == 0 && d.strides[0][1] == d.shape[0] &&
                        d.strides[1][1] == 1 && d.shape[0] % 4 == 0 && n < (int64_t(1) << 31) && is_aligned(src, 16);
-  if (dense || rowmask) {
+  // anything else whose element count and offsets fit 32 bits goes through the same chunked
+  // kernel with index math per element; only the rest keeps the one-tile-per-CTA kernel
+  const bool strided32 = !dense && !rowmask && n < (int64_t(1) << 31) && fits_32bit(d, 2);
+  if (dense || rowmask || strided32) {
     const int chunk_tiles = dense_chunk_tiles(n);
     const int64_t tile_elems = (int64_t)chunk_tiles * kMsRound;
     const int64_t ntiles = (n + tile_elems - 1) / tile_elems;
@@ -470,10 +575,14 @@ extern "C" int twg_masked_select_f32(const TwgIterDesc* desc, const float* src, 
     FastDiv32 row_len;
     row_len.d = rowmask ? (uint32_t)d.shape[0] : 1u;
     make_fastdiv(row_len.d, &row_len.m, &row_len.s);
-    if (rowmask) launch_dense<true>(chunk_tiles, (unsigned)ntiles, s, src, mask, out, n, ticket, tdesc, result, budget, row_len);
-    else launch_dense<false>(chunk_tiles, (unsigned)ntiles, s, src, mask, out, n, ticket, tdesc, result, budget, row_len);
+    StridedDesc<2, u32> sd;
+    std::memset(&sd, 0, sizeof(sd));
+    if (strided32) fill_strided_desc<2>(d, &sd);
+    if (dense) launch_dense<kMsDense>(chunk_tiles, (unsigned)ntiles, s, src, mask, out, n, ticket, tdesc, result, budget, row_len, sd);
+    else if (rowmask) launch_dense<kMsRowMask>(chunk_tiles, (unsigned)ntiles, s, src, mask, out, n, ticket, tdesc, result, budget, row_len, sd);
+    else launch_dense<kMsStrided>(chunk_tiles, (unsigned)ntiles, s, src, mask, out, n, ticket, tdesc, result, budget, row_len, sd);
     TWG_CHECK_LAUNCH();
-    g_last_path = kPathDense;
+    g_last_path = strided32 ? kPathStrided32 : kPathDense;
     return TWG_OK;
   }
 
