@@ -176,6 +176,11 @@ int twg_where_f32(const TwgIterDesc* desc, const uint8_t* cond, const float* a, 
                   void* stream);
 int twg_masked_fill_f32(const TwgIterDesc* desc, const float* self, const uint8_t* mask, float value,
                         float* out, void* stream);
+/* The binary ops with a scalar right operand (add.Scalar, mul.Scalar, ... reach the reference's
+ * add / mul stubs as 0-dim tensors, csrc/ops/arithmetic.cpp:413-417).  desc: [0]=out, [1]=a;
+ * out = a + alpha*scalar, a * scalar, relu(a + scalar), a / scalar. */
+int twg_binary_scalar_f32(int op, const TwgIterDesc* desc, const float* a, float scalar, float alpha,
+                          float* out, void* stream);
 /* eq.Tensor / ne.Scalar ..., CPU fallbacks in the reference (csrc/bindings.cpp:36-39).
  * b == NULL compares against `scalar`; then desc has operands [0]=out, [1]=a only,
  * otherwise [0]=out, [1]=a, [2]=b.  out is bool bytes. */

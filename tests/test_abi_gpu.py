@@ -123,6 +123,23 @@ def test_conversions_large_and_strided(abi):
     assert_bit_equal(abi.convert(m[:, ::3], "float32", "int64"), oracle.convert(np.ascontiguousarray(m[:, ::3]), "float32", "int64"), "slice")
 
 
+def test_scalar_right_operands(abi):
+    for n in (1, 7, 4097, 100003):
+        x = rnd(n, 110 + n)
+        s_arr = np.full(n, 2.5, np.float32)
+        for pad in (0, 1):
+            assert_bit_equal(abi.binary_scalar("add", x, 2.5, pad=pad), oracle.binary("add", x, s_arr), f"x + 2.5 n={n}")
+            assert_bit_equal(abi.binary_scalar("add", x, 2.5, alpha=-0.75, pad=pad), oracle.binary("add", x, s_arr, -0.75), "x - 0.75*2.5")
+            assert_bit_equal(abi.binary_scalar("mul", x, 2.5, pad=pad), oracle.binary("mul", x, s_arr), "x * 2.5")
+            assert_bit_equal(abi.binary_scalar("div", x, 2.5, pad=pad), oracle.binary("div", x, s_arr), "x / 2.5")
+        if n >= 4096:
+            assert abi.last_path() == "strided32"   # pad = 1 is misaligned
+            abi.binary_scalar("mul", x, 2.5)
+            assert abi.last_path() == "dense"
+    m = rnd(96 * 160, 111).reshape(96, 160)
+    assert_bit_equal(abi.binary_scalar("mul", m.T, -3.0), oracle.binary("mul", np.ascontiguousarray(m.T), np.full((160, 96), -3.0, np.float32)), "transposed * scalar")
+
+
 def test_sub_div_where_masked_fill(abi, golden):
     x, y, e, er = golden["rnd_x"], golden["rnd_y"], golden["edge_x"], golden["edge_y"]
     assert_bit_equal(abi.binary("add", x, y, alpha=-1.0), golden["rnd_sub"], "sub")

@@ -89,8 +89,27 @@ void binary_kernel(int op, at::TensorIteratorBase& iter, const at::Scalar& alpha
 }
 
 // ---- add / mul ---------------------------------------------------------------------------
+// Python numbers on the right (x + 2, x * 0.5) arrive as 0-dim CPU tensors: they ride in the kernel's
+// arguments instead of being uploaded and read back as a broadcast operand.
+static bool binary_scalar_out(int op, const at::Tensor& self, const at::Tensor& other, const at::Scalar& alpha,
+                              at::Tensor& out) {
+  if (!(other.device().is_cpu() && other.dim() == 0 && self.device().is_privateuseone())) return false;
+  if (self.scalar_type() != at::kFloat || out.scalar_type() != at::kFloat) return false;
+  at::TensorIteratorConfig config;
+  config.set_check_mem_overlap(true).add_output(out).add_const_input(self).check_all_same_dtype(true);
+  auto iter = config.build();
+  if (iter.numel() == 0) return true;
+  const c10::DeviceIndex dev = iter_device(iter);
+  core::DeviceScope scope(dev);
+  TwgIterDesc desc = desc_from_iter(iter);
+  TWG_TORCH_CHECK(twg_binary_scalar_f32(op, &desc, static_cast<const float*>(iter.data_ptr(1)), other.item<float>(),
+                                        alpha.to<float>(), static_cast<float*>(iter.data_ptr(0)), core::current_stream(dev)));
+  return true;
+}
+
 static at::Tensor& binary_out(int op, const at::Tensor& self, const at::Tensor& other, const at::Scalar& alpha,
                               at::Tensor& out) {
+  if (binary_scalar_out(op, self, other, alpha, out)) return out;
   const at::Tensor a = to_device_if_cpu_scalar(self, out.device(), out.scalar_type());
   const at::Tensor b = to_device_if_cpu_scalar(other, out.device(), out.scalar_type());
   at::TensorIteratorConfig config;

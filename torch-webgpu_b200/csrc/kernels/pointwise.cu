@@ -38,6 +38,23 @@ struct BinaryF32 {
   }
 };
 
+// The same ops with a scalar right operand (x + 2, x * 0.5, x / 3): one stream in, one out.
+template <int OP>
+struct BinaryScalarF32 {
+  static constexpr int NIN = 1, NOUT = 1;
+  static constexpr unsigned kInByteMask = 0u, kOutByteMask = 0u;
+  float scalar, alpha;
+  __device__ __forceinline__ void operator()(const u32* in, u32* out) const {
+    const float a = as_f(in[0]);
+    float y;
+    if constexpr (OP == TWG_BINARY_ADD) y = f_add(a, scalar, alpha);
+    else if constexpr (OP == TWG_BINARY_MUL) y = f_mul(a, scalar);
+    else if constexpr (OP == TWG_BINARY_DIV) y = f_div(a, scalar);
+    else y = f_relu(f_add(a, scalar, 1.0f));
+    out[0] = as_u(y);
+  }
+};
+
 template <int OP>
 __device__ __forceinline__ u32 compare(float a, float b) {
   if constexpr (OP == TWG_CMP_EQ) return f_eq(a, b);
@@ -96,6 +113,11 @@ int run_binary(const TwgIterDesc* d, const float* a, const float* b, float alpha
   return launch_pointwise(BinaryF32<OP>{alpha}, d, ptrs, s);
 }
 template <int OP>
+int run_binary_scalar(const TwgIterDesc* d, const float* a, float scalar, float alpha, float* out, cudaStream_t s) {
+  void* ptrs[2] = {out, const_cast<float*>(a)};
+  return launch_pointwise(BinaryScalarF32<OP>{scalar, alpha}, d, ptrs, s);
+}
+template <int OP>
 int run_compare(const TwgIterDesc* d, const float* a, const float* b, float scalar, uint8_t* out, cudaStream_t s) {
   if (b) {
     void* ptrs[3] = {out, const_cast<float*>(a), const_cast<float*>(b)};
@@ -136,6 +158,18 @@ extern "C" int twg_binary_f32(int op, const TwgIterDesc* desc, const float* a, c
     case TWG_BINARY_FUSED_ADD_RELU: return run_binary<TWG_BINARY_FUSED_ADD_RELU>(desc, a, b, alpha, out, s);
     case TWG_BINARY_DIV: return run_binary<TWG_BINARY_DIV>(desc, a, b, alpha, out, s);
     default: return set_error(TWG_ERR_INVALID, "twg_binary_f32: unknown op %d", op);
+  }
+}
+
+extern "C" int twg_binary_scalar_f32(int op, const TwgIterDesc* desc, const float* a, float scalar, float alpha,
+                                     float* out, void* stream) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (op) {
+    case TWG_BINARY_ADD: return run_binary_scalar<TWG_BINARY_ADD>(desc, a, scalar, alpha, out, s);
+    case TWG_BINARY_MUL: return run_binary_scalar<TWG_BINARY_MUL>(desc, a, scalar, alpha, out, s);
+    case TWG_BINARY_FUSED_ADD_RELU: return run_binary_scalar<TWG_BINARY_FUSED_ADD_RELU>(desc, a, scalar, alpha, out, s);
+    case TWG_BINARY_DIV: return run_binary_scalar<TWG_BINARY_DIV>(desc, a, scalar, alpha, out, s);
+    default: return set_error(TWG_ERR_INVALID, "twg_binary_scalar_f32: unknown op %d", op);
   }
 }
 

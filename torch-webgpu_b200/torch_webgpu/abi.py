@@ -99,6 +99,7 @@ SIGNATURES = {
     "twg_unary_f32": (c_int, [c_int, POINTER(IterDesc), c_void_p, c_void_p, c_void_p]),
     "twg_binary_f32": (c_int, [c_int, POINTER(IterDesc), c_void_p, c_void_p, c_float, c_void_p, c_void_p]),
     "twg_compare_f32": (c_int, [c_int, POINTER(IterDesc), c_void_p, c_void_p, c_float, c_void_p, c_void_p]),
+    "twg_binary_scalar_f32": (c_int, [c_int, POINTER(IterDesc), c_void_p, c_float, c_float, c_void_p, c_void_p]),
     "twg_convert": (c_int, [POINTER(IterDesc), c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "twg_where_f32": (c_int, [POINTER(IterDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "twg_masked_fill_f32": (c_int, [POINTER(IterDesc), c_void_p, c_void_p, c_float, c_void_p, c_void_p]),
@@ -304,6 +305,14 @@ def convert(x: np.ndarray, src: str, dst: str, *, pad: int = 0, stream=None) -> 
     check(lib().twg_convert(byref(d), DTYPES[src], DTYPES[dst], dx.ptr, do.ptr, stream))
     out = do.numpy(stream)
     return out.view(np.bool_) if dst == "bool" else out
+
+
+def binary_scalar(op: str, a: np.ndarray, scalar: float, alpha: float = 1.0, *, pad: int = 0, stream=None) -> np.ndarray:
+    da = DeviceArray(a, stream=stream, pad_front=pad)
+    do = DeviceArray.empty(a.shape, np.float32, stream=stream, pad_front=pad)
+    d = make_desc(a.shape, [do, da])
+    check(lib().twg_binary_scalar_f32(BINARY[op], byref(d), da.ptr, scalar, alpha, do.ptr, stream))
+    return do.numpy(stream)
 
 
 def where(cond: np.ndarray, a: np.ndarray, b: np.ndarray, *, pad: int = 0, stream=None) -> np.ndarray:
