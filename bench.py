@@ -38,7 +38,8 @@ sys.path.insert(0, str(REPO))
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
-BATCH, ROWS, COLS = 64, 4096, 4096
+# 64 slabs is the benchmark; TWG_BENCH_BATCH shrinks it to diagnose host overhead on few GPUs
+BATCH, ROWS, COLS = int(os.environ.get("TWG_BENCH_BATCH", "64")), 4096, 4096
 SLAB = ROWS * COLS
 SEED = 4
 FALLBACK_HBM_GBS = 6650.0
@@ -611,15 +612,16 @@ def run_gpu_arm(args) -> None:
     for buf, h in zip(dev_in, host):
         abi.check(L.twg_memcpy_h2d(buf.ptr, h.data_ptr(), 4 * n, stream))
     d_mask = abi.DeviceBuffer(n, local_rank, stream)
-    # Two sets of everything a step writes and the host reads: the host picks up the counts of step
-    # i while the GPU already runs step i+1 (the stream never waits for the host).
+    # Several sets of everything a step writes and the host reads: the host picks up the counts of
+    # step i while the GPU already runs the steps after it (the stream never waits for the host).
+    DEPTH = 2 if world == 1 else 4
     ws_bytes = L.twg_masked_select_workspace_bytes(n)
-    d_out = [abi.DeviceBuffer(4 * n, local_rank, stream) for _ in range(2)]
-    d_ws = [abi.DeviceBuffer(ws_bytes, local_rank, stream) for _ in range(2)]
-    t_res = [torch.zeros(2, dtype=torch.int64, device=cuda_dev) for _ in range(2)]          # [count, status] of this rank
-    t_all = [torch.zeros(2 * world, dtype=torch.int64, device=cuda_dev) for _ in range(2)]  # every rank's [count, status]
-    h_all = [torch.zeros(2 * world, dtype=torch.int64, pin_memory=True) for _ in range(2)]
-    landed = [torch.cuda.Event() for _ in range(2)]
+    d_out = [abi.DeviceBuffer(4 * n, local_rank, stream) for _ in range(DEPTH)]
+    d_ws = [abi.DeviceBuffer(ws_bytes, local_rank, stream) for _ in range(DEPTH)]
+    t_res = [torch.zeros(2, dtype=torch.int64, device=cuda_dev) for _ in range(DEPTH)]          # [count, status] of this rank
+    t_all = [torch.zeros(2 * world, dtype=torch.int64, device=cuda_dev) for _ in range(DEPTH)]  # every rank's [count, status]
+    h_all = [torch.zeros(2 * world, dtype=torch.int64, pin_memory=True) for _ in range(DEPTH)]
+    landed = [torch.cuda.Event() for _ in range(DEPTH)]
     h_res = torch.zeros(2, dtype=torch.int64, pin_memory=True)
     program = abi.fused_compile(abi.CHAIN_MASK_PROGRAM)
     assert abi.fused_kind(program) == "aot"
@@ -633,53 +635,107 @@ def run_gpu_arm(args) -> None:
     ev = Events(abi, 2 + 2 * steps)
     counts_seen = []
 
-    def launch(slot: int, i: int | None) -> None:
+    def enqueue(slot: int, on, i: int | None) -> None:
         """Everything one step puts on the stream: fused chain, compaction, the all-gather of the
         counts, their copy to pinned host memory."""
         if i is not None:
-            ev.record(2 + 2 * i, stream)
-        abi.check(L.twg_fused_launch(program, ctypes.byref(desc4), ptrs, stream))
+            ev.record(2 + 2 * i, on)
+        abi.check(L.twg_fused_launch(program, ctypes.byref(desc4), ptrs, on))
         if i is not None:
-            ev.record(3 + 2 * i, stream)
+            ev.record(3 + 2 * i, on)
         abi.check(L.twg_masked_select_f32(ctypes.byref(desc2), dev_in[0].ptr, d_mask.ptr, d_out[slot].ptr,
-                                          t_res[slot].data_ptr(), d_ws[slot].ptr, ws_bytes, stream))
+                                          t_res[slot].data_ptr(), d_ws[slot].ptr, ws_bytes, on))
         if world > 1:
             dist.all_gather_into_tensor(t_all[slot], t_res[slot])   # 16 bytes per rank over NVLink
         else:
             t_all[slot].copy_(t_res[slot])
-        h_all[slot].copy_(t_all[slot], non_blocking=True)
+        # (through the C ABI: with the webgpu accelerator registered, torch no longer recognises its
+        # own pinned tensors during graph capture)
+        abi.check(L.twg_memcpy_d2h(h_all[slot].data_ptr(), t_all[slot].data_ptr(), 16 * world, on, 0))
+
+    # Optionally the step is captured once per slot as a CUDA graph and replayed with one call.  If
+    # capture is not possible the plain calls remain.
+    graphs, graph_note, launches_per_step = None, None, 0
+    # Replaying a graph that contains the NCCL all-gather stopped making progress on two GPUs (the
+    # run was ended by its time limit), so graphs are only offered for the single-GPU run.
+    want_graphs = args.graphs == "on" and world == 1
+
+    def capture_graphs():
+        captured = []
+        for slot in range(DEPTH):
+            g_ = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_):
+                enqueue(slot, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), None)
+            captured.append(g_)
+        return captured
+
+    host_s = [0.0, 0.0]   # seconds the host spent issuing steps / collecting counts (after the wait)
+
+    def launch(slot: int, i: int | None) -> None:
+        t_issue = time.perf_counter()
+        try:
+            _launch(slot, i)
+        finally:
+            host_s[0] += time.perf_counter() - t_issue
+
+    def _launch(slot: int, i: int | None) -> None:
+        if graphs is not None:
+            graphs[slot].replay()
+        else:
+            enqueue(slot, stream, i)
         landed[slot].record()
 
     def collect(slot: int) -> None:
         """The step's host sync: its counts are needed on the host (output shape, global offset)."""
         landed[slot].synchronize()
-        counts = h_all[slot][0::2].tolist()
-        if any(int(v) != 0 for v in h_all[slot][1::2].tolist()):
-            raise RuntimeError(f"masked_select reported device status {h_all[slot][1::2].tolist()}")
-        h_res[0] = counts[rank]
+        t_collect = time.perf_counter()
+        flat = h_all[slot].tolist()
+        counts, status = flat[0::2], flat[1::2]
+        if any(status):
+            raise RuntimeError(f"masked_select reported device status {status}")
         counts_seen.append((sum(counts[:rank]), sum(counts)))
+        host_s[1] += time.perf_counter() - t_collect
 
     def run_steps(count: int, timed: bool) -> None:
         for i in range(count):
-            launch(i & 1, i if timed else None)
-            if i > 0:
-                collect((i - 1) & 1)
-        if count > 0:
-            collect((count - 1) & 1)
+            launch(i % DEPTH, i if timed else None)
+            if i >= DEPTH - 1:
+                collect((i - (DEPTH - 1)) % DEPTH)
+        for i in range(max(count - (DEPTH - 1), 0), count):
+            collect(i % DEPTH)
 
-    run_steps(warmup, False)
+    run_steps(max(warmup, 1), False)
+    if want_graphs:
+        try:
+            barrier()
+            before = int(L.twg_launch_count())
+            graphs = capture_graphs()
+            launches_per_step = (int(L.twg_launch_count()) - before) // DEPTH
+            run_steps(DEPTH, False)   # one replay of every graph before the clock starts
+        except Exception as exc:  # noqa: BLE001 - any capture problem means: keep the plain calls
+            graphs, graph_note = None, f"graph capture failed, plain calls used: {type(exc).__name__}: {exc}"[:300]
+            torch.cuda.synchronize()
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     L.twg_reset_launch_count()
+    host_s[0] = host_s[1] = 0.0
     ev.record(0, stream)
     run_steps(steps, True)
     ev.record(1, stream)
     ev.sync(1)
-    launches = int(L.twg_launch_count())
+    launches = int(L.twg_launch_count()) + (steps * launches_per_step if graphs is not None else 0)
     barrier()
     clocks = sampler.stop() if rank == 0 else {}
+    if graphs is not None:
+        # the events around the fused kernel cannot sit inside a graph: time it right after the
+        # timed region, same buffers, same clocks
+        for i in range(steps):
+            ev.record(2 + 2 * i, stream)
+            abi.check(L.twg_fused_launch(program, ctypes.byref(desc4), ptrs, stream))
+            ev.record(3 + 2 * i, stream)
+        ev.sync(3 + 2 * (steps - 1))
     ms_total = ev.elapsed(0, 1)
     fused_ms = statistics.mean(ev.elapsed(2 + 2 * i, 3 + 2 * i) for i in range(steps))
     t = torch.tensor([ms_total, fused_ms], dtype=torch.float64, device=cuda_dev)
@@ -688,7 +744,7 @@ def run_gpu_arm(args) -> None:
     ms_total, fused_ms_max = float(t[0]), float(t[1])
     ms_per_step = ms_total / steps
     value = BATCH * SLAB / (ms_per_step * 1e-3) / 1e9
-    local_k, total_k = int(h_res[0]), counts_seen[-1][1]
+    total_k = counts_seen[-1][1]
 
     # ---- per-op table (single GPU only) -----------------------------------------------------
     del d_out, d_mask, d_ws
@@ -772,7 +828,12 @@ def run_gpu_arm(args) -> None:
                          "frac": achieved / peak, "traffic": traffic, "ms_per_launch": fused_ms_max,
                          "algorithmic_bytes_per_launch": CHAIN_BYTES_PER_ELEM * n},
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+            "host_us_per_step": {"issue": round(host_s[0] / steps * 1e6, 1), "collect": round(host_s[1] / steps * 1e6, 1)},
+            "step_issue": ("one CUDA graph replay per step; the fused kernel's ms_per_launch is timed right after the "
+                           "timed region") if graphs is not None else "plain calls",
         }
+        if graph_note:
+            line["step_issue_note"] = graph_note
         if ops is not None:
             line["ops"] = ops
         if world == 1 and not args.no_cpu:
@@ -790,6 +851,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-ops", action="store_true", help="skip the per-op GB/s table")
+    ap.add_argument("--graphs", default="off", choices=["on", "off"],
+                    help="replay each step as a CUDA graph (single-GPU runs only)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--case", default=None, help="run one kernel on a small case (for ncu captures) and exit")
     ap.add_argument("--case-elems", type=int, default=1 << 27)
