@@ -621,7 +621,17 @@ def run_gpu_arm(args) -> None:
     t_res = [torch.zeros(2, dtype=torch.int64, device=cuda_dev) for _ in range(DEPTH)]          # [count, status] of this rank
     t_all = [torch.zeros(2 * world, dtype=torch.int64, device=cuda_dev) for _ in range(DEPTH)]  # every rank's [count, status]
     h_all = [torch.zeros(2 * world, dtype=torch.int64, pin_memory=True) for _ in range(DEPTH)]
-    landed = [torch.cuda.Event() for _ in range(DEPTH)]
+    # With many ranks on one host the waiting threads yield their core instead of spinning on it
+    # (eight spinning ranks next to eight NCCL threads and the launcher oversubscribe a 16-core box);
+    # the wake-up latency disappears behind the steps already queued.
+    yield_wanted = os.environ.get("TWG_BENCH_YIELD", "auto")   # "1" / "0" force it for experiments
+    landed = [torch.cuda.Event(blocking=yield_wanted == "1" or (yield_wanted == "auto" and world > 2))
+              for _ in range(DEPTH)]
+    counted = [torch.cuda.Event() for _ in range(DEPTH)]
+    side_wanted = os.environ.get("TWG_BENCH_SIDE_STREAM", "auto")   # "1" / "0" force it for experiments
+    use_side = world > 1 and (side_wanted == "1" or (side_wanted == "auto" and world > 2))
+    side = torch.cuda.Stream(device=cuda_dev) if use_side else None
+    side_handle = ctypes.c_void_p(side.cuda_stream) if side is not None else None
     h_res = torch.zeros(2, dtype=torch.int64, pin_memory=True)
     program = abi.fused_compile(abi.CHAIN_MASK_PROGRAM)
     assert abi.fused_kind(program) == "aot"
@@ -645,13 +655,25 @@ def run_gpu_arm(args) -> None:
             ev.record(3 + 2 * i, on)
         abi.check(L.twg_masked_select_f32(ctypes.byref(desc2), dev_in[0].ptr, d_mask.ptr, d_out[slot].ptr,
                                           t_res[slot].data_ptr(), d_ws[slot].ptr, ws_bytes, on))
-        if world > 1:
-            dist.all_gather_into_tensor(t_all[slot], t_res[slot])   # 16 bytes per rank over NVLink
+        if side is not None:
+            # The all-gather is where the ranks meet.  Only the host needs its result, so with many
+            # ranks it runs on a second stream behind the compaction: this rank's kernels of the
+            # next step do not wait for the slowest rank of this one.  (On two ranks it measured
+            # within run-to-run noise of the single-stream form, 626 and 657 against 649-652 Gelem/s.)
+            counted[slot].record()
+            with torch.cuda.stream(side):
+                side.wait_event(counted[slot])
+                dist.all_gather_into_tensor(t_all[slot], t_res[slot])   # 16 bytes per rank over NVLink
+                abi.check(L.twg_memcpy_d2h(h_all[slot].data_ptr(), t_all[slot].data_ptr(), 16 * world, side_handle, 0))
+                landed[slot].record()
         else:
-            t_all[slot].copy_(t_res[slot])
-        # (through the C ABI: with the webgpu accelerator registered, torch no longer recognises its
-        # own pinned tensors during graph capture)
-        abi.check(L.twg_memcpy_d2h(h_all[slot].data_ptr(), t_all[slot].data_ptr(), 16 * world, on, 0))
+            if world > 1:
+                dist.all_gather_into_tensor(t_all[slot], t_res[slot])   # 16 bytes per rank over NVLink
+            else:
+                t_all[slot].copy_(t_res[slot])
+            # (through the C ABI: with the webgpu accelerator registered, torch no longer recognises
+            # its own pinned tensors during graph capture)
+            abi.check(L.twg_memcpy_d2h(h_all[slot].data_ptr(), t_all[slot].data_ptr(), 16 * world, on, 0))
 
     # Optionally the step is captured once per slot as a CUDA graph and replayed with one call.  If
     # capture is not possible the plain calls remain.
@@ -683,7 +705,8 @@ def run_gpu_arm(args) -> None:
             graphs[slot].replay()
         else:
             enqueue(slot, stream, i)
-        landed[slot].record()
+        if side is None:
+            landed[slot].record()
 
     def collect(slot: int) -> None:
         """The step's host sync: its counts are needed on the host (output shape, global offset)."""
@@ -829,6 +852,7 @@ def run_gpu_arm(args) -> None:
                          "algorithmic_bytes_per_launch": CHAIN_BYTES_PER_ELEM * n},
             "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
             "host_us_per_step": {"issue": round(host_s[0] / steps * 1e6, 1), "collect": round(host_s[1] / steps * 1e6, 1)},
+            "count_allgather": "second stream" if side is not None else ("compute stream" if world > 1 else "none"),
             "step_issue": ("one CUDA graph replay per step; the fused kernel's ms_per_launch is timed right after the "
                            "timed region") if graphs is not None else "plain calls",
         }
