@@ -38,15 +38,16 @@ sys.path.insert(0, str(REPO))
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
-# 64 slabs is the benchmark; TWG_BENCH_BATCH shrinks it to diagnose host overhead on few GPUs
-BATCH, ROWS, COLS = int(os.environ.get("TWG_BENCH_BATCH", "64")), 4096, 4096
+BATCH, ROWS, COLS = 64, 4096, 4096   # --batch changes the first (a diagnostic, not the benchmark)
 SLAB = ROWS * COLS
 SEED = 4
 FALLBACK_HBM_GBS = 6650.0
+NOMINAL_HBM_GBS = 8000.0   # the round figure for B200 HBM3e; every fraction is also reported against it
 CHAIN_BYTES_PER_ELEM = 13  # read a, b, c (3 x 4 B), write the bool mask (1 B)
-# dram__bytes_read.sum + dram__bytes_write.sum of the fused-chain kernel per element, from the ncu
-# capture summarised in profiles/chain_kernel_ncu.md (2^27 elements; DRAM traffic of this streaming
-# kernel is proportional to the element count, so it is scaled to the elements of a launch)
+# DRAM bytes the fused-chain kernel moves per element (dram__bytes_read.sum + dram__bytes_write.sum
+# of one ncu capture on 2^27 elements).  A constant taken from that capture, not a measurement of
+# this run: the traffic of a streaming kernel is proportional to its element count, so it is scaled
+# to the elements of a launch.
 CHAIN_DRAM_BYTES_PER_ELEM = 12.89
 
 
@@ -237,12 +238,15 @@ def run_reference_arm(args) -> None:
         cpu_chain_step(oracle, a, b, c)
     dt = time.perf_counter() - t0
     value = args.steps * nslabs * SLAB / dt / 1e9
-    sample = f"each step = {nslabs} of {BATCH} [4096,4096] slabs of the chain on the host cores"
+    sample = (f"each step = {nslabs} of {BATCH} [4096,4096] slabs of the chain on the host cores, C restatement with "
+              f"OpenMP on {oracle.num_threads()} threads (faster than the PyTorch CPU kernels the reference's fallback ops run)")
     line = {
         "impl": "reference", "metric": "Gelem/s of the compiled chain + masked_select", "value": value, "unit": "Gelem/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args.gpus),
+        "config": dict(workload_config(args.gpus, 0), elements_per_step_timed=nslabs * SLAB,
+                       note=f"each timed step processes {nslabs} of the {BATCH} slabs (a bounded sample of the workload); "
+                            "the rate is per element and comparable, the step time is not"),
         "cpu_baseline": {"value": value, "unit": "Gelem/s", "cores": oracle.num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "Gelem/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -250,13 +254,16 @@ def run_reference_arm(args) -> None:
     print(json.dumps(line), flush=True)
 
 
-def workload_config(n_gpus: int) -> dict:
-    return {"workload": "cfg5: y=relu(silu(a+b)+c); m=(y==0)&(a!=0); masked_select(a,m) over 64 x f32[4096,4096], "
-                        "torch.compile(backend=webgpu_backend) fused chain + single-pass compaction",
-            "global_batch": BATCH, "elements_per_step": BATCH * SLAB, "parallelism": f"batch-sharded x{n_gpus}",
-            "l2": "inputs (>= 1.5 GiB per rank) are larger than the 126 MB L2; no flush needed",
-            "pipelining": "every step ends with its count read-back to the host; the host collects the counts of "
-                          "step i while the stream already runs step i+1 (two sets of output buffers)"}
+def workload_config(n_gpus: int, depth: int) -> dict:
+    cfg = {"workload": "cfg5: y=relu(silu(a+b)+c); m=(y==0)&(a!=0); masked_select(a,m) over 64 x f32[4096,4096]; "
+                       "`value` = C ABI calls twg_fused_launch + twg_masked_select_f32 + count exchange per step, "
+                       "`public_api` / `e2e` = the same through torch.compile(backend=webgpu_backend)",
+           "global_batch": BATCH, "elements_per_step": BATCH * SLAB, "parallelism": f"batch-sharded x{n_gpus}",
+           "l2": "inputs (>= 1.5 GiB per rank) are larger than the 126 MB L2; no flush needed"}
+    if depth:
+        cfg["pipelining"] = (f"every step ends with its counts on the host; the host collects the counts of step i while the "
+                             f"stream already runs up to {depth - 1} later steps ({depth} sets of output buffers)")
+    return cfg
 
 
 # ---------------------------------------------------------------------------------------------
@@ -311,7 +318,8 @@ def per_op_table(abi, stream, peak: float) -> dict:
 
     def put(name, nbytes, ms, note=None):
         gbs = nbytes / ms / 1e6
-        table[name] = {"ms": round(ms, 4), "gbs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 3)}
+        table[name] = {"ms": round(ms, 4), "gbs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 3),
+                       "frac_of_nominal_8000": round(gbs / NOMINAL_HBM_GBS, 3)}
         if isinstance(ms, Timing):
             table[name]["min_ms"] = round(ms.min_ms, 4)
         if note:
@@ -442,8 +450,8 @@ def per_op_table(abi, stream, peak: float) -> dict:
 
 
 def run_case(args) -> None:
-    """One kernel on a small case (a few GB at most, still larger than L2): the command the ncu
-    captures under profiles/ are taken with.  Prints its own JSON line; not the benchmark."""
+    """One kernel on a small case (a few GB at most, still larger than L2), sized for a profiler
+    capture.  Prints its own JSON line; not the benchmark."""
     from torch_webgpu import abi
     L = abi.lib()
     n = args.case_elems
@@ -557,82 +565,126 @@ def run_case(args) -> None:
     del bufs
 
 
+def pin_to_core_block(local_rank: int, local_world: int) -> list[int]:
+    """With several ranks on one host, give each its own block of the allowed cores so that the
+    ranks' issuing threads and their helper threads do not migrate over each other."""
+    try:
+        allowed = sorted(os.sched_getaffinity(0))
+        per = len(allowed) // max(local_world, 1)
+        if local_world > 1 and per >= 2:
+            mine = allowed[local_rank * per:(local_rank + 1) * per]
+            os.sched_setaffinity(0, mine)
+            return mine
+        return allowed
+    except (AttributeError, OSError):
+        return []
+
+
+def verify_slab(oracle, a, b, c, gpu_mask, gpu_selected, what: str) -> None:
+    """One [4096,4096] slab of the timed run against the CPU oracle.  The mask may differ from the
+    oracle's only where the value under relu is within rounding of zero (silu is allowed 2 ulp);
+    given the mask, the selected values and their order must be bit-identical."""
+    y_ref, m_ref = oracle.chain_mask(a, b, c, want_y=True)
+    gpu_mask = gpu_mask.reshape(m_ref.shape).astype(bool)
+    flipped = gpu_mask != m_ref
+    if flipped.sum() > max(4, m_ref.size // 1_000_000) or not np.all(np.abs(y_ref[flipped]) < 1e-6):
+        raise RuntimeError(f"bench verification failed ({what}): {int(flipped.sum())} mask elements differ from the oracle")
+    ref_sel = oracle.masked_select(a.reshape(-1), gpu_mask.reshape(-1))
+    if ref_sel.size != gpu_selected.size or not np.array_equal(ref_sel.view(np.uint32), gpu_selected.view(np.uint32)):
+        raise RuntimeError(f"bench verification failed ({what}): the selected values differ from the oracle "
+                           f"({gpu_selected.size} on the GPU, {ref_sel.size} expected)")
+
+
 def run_gpu_arm(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_world = int(os.environ.get("LOCAL_WORLD_SIZE", str(world)))
     if args.gpus != world and world > 1:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; this benchmark has no CPU fallback (use --impl reference for the CPU arm)")
 
-    import torch.distributed as dist
-
-    torch.cuda.set_device(local_rank)
-    cuda_dev = torch.device("cuda", local_rank)
-    if world > 1:
-        # NCCL is set up before the webgpu backend is imported: once PrivateUse1 is registered,
-        # torch.accelerator reports "webgpu" and init_process_group rejects a cuda device_id.
-        dist.init_process_group("nccl")
-        warm = torch.zeros(1, device=cuda_dev)
-        dist.all_reduce(warm)
-        torch.cuda.synchronize()
-
     import torch_webgpu
     from torch_webgpu import abi, webgpu_backend
-    from torch_webgpu.sharding import global_segment, shard_range
+    from torch_webgpu.sharding import NcclExchange, PeerStoreExchange, Rendezvous, shard_range
 
+    cores = pin_to_core_block(local_rank, local_world)
+    rdv = Rendezvous.from_env()
     torch.webgpu.set_device(local_rank)
     L = abi.lib()
-    # Leg 1 drives the C ABI on torch's current CUDA stream, so the NCCL all-gather of the counts
-    # is ordered after the compaction kernel without a host round trip in between.
-    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    abi.check(L.twg_set_device(local_rank))
+    stream = ctypes.c_void_p(torch.webgpu.current_stream_handle(local_rank))   # the backend's compute stream
+    side = ctypes.c_void_p()
+    abi.check(L.twg_get_stream(local_rank, 2, ctypes.byref(side)))             # collects the counts behind it
     peak, peak_kind = measured_peak()
 
     lo, hi = shard_range(BATCH, rank, world)
     nb = hi - lo
     n = nb * SLAB
+    DEPTH = 2 if world == 1 else 4      # steps the host may run ahead of the counts it has seen
+    RING = 2 * DEPTH                    # mailbox slots (see twg_exchange_publish's reuse rule)
+
+    # ---- the ranks' communicator and count exchange, all through the C ABI ---------------------
+    nccl = None
+    exchange_note = None
+    if world > 1:
+        uid = rdv.broadcast(NcclExchange.make_unique_id(abi) if rank == 0 else None)
+        nccl = NcclExchange(abi, rank, world, uid, local_rank, ring=RING)
+    d_token = abi.DeviceBuffer(8 * (world + 1), local_rank, stream)
+
+    def barrier() -> None:
+        """Every rank's stream has drained and every rank has arrived (device-side meeting point:
+        the ranks leave within microseconds of each other)."""
+        abi.check(L.twg_stream_sync(side))
+        abi.check(L.twg_stream_sync(stream))
+        if nccl is not None:
+            nccl.allgather(d_token.ptr, d_token.ptr + 8, 1, stream)
+            abi.check(L.twg_stream_sync(stream))
+
+    xchg = None
+    if args.exchange in ("auto", "peer"):
+        px, handle, ok = None, b"", 1
+        try:
+            px = PeerStoreExchange(abi, rank, world, ring=RING)
+            handle = px.export_handle() if world > 1 else b""
+        except abi.TwgError as exc:
+            ok, exchange_note = 0, str(exc)
+        handles = rdv.share(handle)
+        if ok and world > 1:
+            try:
+                px.connect(handles)
+            except abi.TwgError as exc:
+                ok, exchange_note = 0, str(exc)
+        oks = rdv.share(bytes([ok]) + (exchange_note or "").encode()[:200])
+        if all(o[:1] == b"\x01" for o in oks):
+            xchg = px
+        else:
+            exchange_note = next(o[1:].decode(errors="replace") for o in oks if o[:1] != b"\x01")
+            if args.exchange == "peer":
+                raise SystemExit(f"bench.py: --exchange peer is not possible here: {exchange_note}")
+    if xchg is None:
+        if nccl is None:
+            raise SystemExit("bench.py: --exchange nccl needs more than one rank")
+        xchg = nccl
 
     # ---- synthetic inputs in pinned host memory --------------------------------------------
     host = [torch.empty(nb, ROWS, COLS, pin_memory=True) for _ in range(3)]
     for t, buf in enumerate(host):
         fill_shard(buf, t, lo, hi)
 
-    token = torch.zeros(1, device=cuda_dev)
-
-    def barrier():
-        abi.check(L.twg_stream_sync(stream))
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.all_reduce(token)  # a barrier that names its device explicitly
-            torch.cuda.synchronize()
-
     # ---- leg 1: inputs resident in HBM, C ABI calls ----------------------------------------
     dev_in = [abi.DeviceBuffer(4 * n, local_rank, stream) for _ in range(3)]
     for buf, h in zip(dev_in, host):
         abi.check(L.twg_memcpy_h2d(buf.ptr, h.data_ptr(), 4 * n, stream))
     d_mask = abi.DeviceBuffer(n, local_rank, stream)
-    # Several sets of everything a step writes and the host reads: the host picks up the counts of
-    # step i while the GPU already runs the steps after it (the stream never waits for the host).
-    DEPTH = 2 if world == 1 else 4
+    # DEPTH sets of everything a step writes: the host picks up the counts of step i while the GPU
+    # already runs the steps after it, so the stream never waits for the host or for another rank.
     ws_bytes = L.twg_masked_select_workspace_bytes(n)
     d_out = [abi.DeviceBuffer(4 * n, local_rank, stream) for _ in range(DEPTH)]
     d_ws = [abi.DeviceBuffer(ws_bytes, local_rank, stream) for _ in range(DEPTH)]
-    t_res = [torch.zeros(2, dtype=torch.int64, device=cuda_dev) for _ in range(DEPTH)]          # [count, status] of this rank
-    t_all = [torch.zeros(2 * world, dtype=torch.int64, device=cuda_dev) for _ in range(DEPTH)]  # every rank's [count, status]
-    h_all = [torch.zeros(2 * world, dtype=torch.int64, pin_memory=True) for _ in range(DEPTH)]
-    # With many ranks on one host the waiting threads yield their core instead of spinning on it
-    # (eight spinning ranks next to eight NCCL threads and the launcher oversubscribe a 16-core box);
-    # the wake-up latency disappears behind the steps already queued.
-    yield_wanted = os.environ.get("TWG_BENCH_YIELD", "auto")   # "1" / "0" force it for experiments
-    landed = [torch.cuda.Event(blocking=yield_wanted == "1" or (yield_wanted == "auto" and world > 2))
-              for _ in range(DEPTH)]
-    counted = [torch.cuda.Event() for _ in range(DEPTH)]
-    side_wanted = os.environ.get("TWG_BENCH_SIDE_STREAM", "auto")   # "1" / "0" force it for experiments
-    use_side = world > 1 and (side_wanted == "1" or (side_wanted == "auto" and world > 2))
-    side = torch.cuda.Stream(device=cuda_dev) if use_side else None
-    side_handle = ctypes.c_void_p(side.cuda_stream) if side is not None else None
-    h_res = torch.zeros(2, dtype=torch.int64, pin_memory=True)
+    d_res = [abi.DeviceBuffer(16, local_rank, stream) for _ in range(DEPTH)]   # [count, status] of this rank
+    compacted = Events(abi, DEPTH)
     program = abi.fused_compile(abi.CHAIN_MASK_PROGRAM)
     assert abi.fused_kind(program) == "aot"
     desc4 = abi.IterDesc()
@@ -643,141 +695,121 @@ def run_gpu_arm(args) -> None:
 
     steps, warmup = args.steps, args.warmup
     ev = Events(abi, 2 + 2 * steps)
-    counts_seen = []
+    counts_seen: list[tuple[int, int, int]] = []   # (this rank's count, its global offset, total) per collected step
+    host_s = [0.0, 0.0, 0.0]   # seconds spent issuing steps / waiting for counts / handling them
+    seq_next = [1]
 
-    def enqueue(slot: int, on, i: int | None) -> None:
-        """Everything one step puts on the stream: fused chain, compaction, the all-gather of the
-        counts, their copy to pinned host memory."""
-        if i is not None:
-            ev.record(2 + 2 * i, on)
-        abi.check(L.twg_fused_launch(program, ctypes.byref(desc4), ptrs, on))
-        if i is not None:
-            ev.record(3 + 2 * i, on)
-        abi.check(L.twg_masked_select_f32(ctypes.byref(desc2), dev_in[0].ptr, d_mask.ptr, d_out[slot].ptr,
-                                          t_res[slot].data_ptr(), d_ws[slot].ptr, ws_bytes, on))
-        if side is not None:
-            # The all-gather is where the ranks meet.  Only the host needs its result, so with many
-            # ranks it runs on a second stream behind the compaction: this rank's kernels of the
-            # next step do not wait for the slowest rank of this one.  (On two ranks it measured
-            # within run-to-run noise of the single-stream form, 626 and 657 against 649-652 Gelem/s.)
-            counted[slot].record()
-            with torch.cuda.stream(side):
-                side.wait_event(counted[slot])
-                dist.all_gather_into_tensor(t_all[slot], t_res[slot])   # 16 bytes per rank over NVLink
-                abi.check(L.twg_memcpy_d2h(h_all[slot].data_ptr(), t_all[slot].data_ptr(), 16 * world, side_handle, 0))
-                landed[slot].record()
-        else:
-            if world > 1:
-                dist.all_gather_into_tensor(t_all[slot], t_res[slot])   # 16 bytes per rank over NVLink
-            else:
-                t_all[slot].copy_(t_res[slot])
-            # (through the C ABI: with the webgpu accelerator registered, torch no longer recognises
-            # its own pinned tensors during graph capture)
-            abi.check(L.twg_memcpy_d2h(h_all[slot].data_ptr(), t_all[slot].data_ptr(), 16 * world, on, 0))
-
-    # Optionally the step is captured once per slot as a CUDA graph and replayed with one call.  If
-    # capture is not possible the plain calls remain.
-    graphs, graph_note, launches_per_step = None, None, 0
-    # Replaying a graph that contains the NCCL all-gather stopped making progress on two GPUs (the
-    # run was ended by its time limit), so graphs are only offered for the single-GPU run.
-    want_graphs = args.graphs == "on" and world == 1
-
-    def capture_graphs():
-        captured = []
-        for slot in range(DEPTH):
-            g_ = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g_):
-                enqueue(slot, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), None)
-            captured.append(g_)
-        return captured
-
-    host_s = [0.0, 0.0]   # seconds the host spent issuing steps / collecting counts (after the wait)
-
-    def launch(slot: int, i: int | None) -> None:
+    def launch(i: int | None) -> int:
+        """Everything one step puts on the GPU: fused chain and compaction on the compute stream,
+        the publication of this rank's count to every rank, and (second stream) the kernel that
+        gathers all ranks' counts for the host."""
         t_issue = time.perf_counter()
-        try:
-            _launch(slot, i)
-        finally:
-            host_s[0] += time.perf_counter() - t_issue
+        seq = seq_next[0]
+        seq_next[0] += 1
+        slot = seq % DEPTH
+        if i is not None:
+            ev.record(2 + 2 * i, stream)
+        abi.check(L.twg_fused_launch(program, ctypes.byref(desc4), ptrs, stream))
+        if i is not None:
+            ev.record(3 + 2 * i, stream)
+        abi.check(L.twg_masked_select_f32(ctypes.byref(desc2), dev_in[0].ptr, d_mask.ptr, d_out[slot].ptr,
+                                          d_res[slot].ptr, d_ws[slot].ptr, ws_bytes, stream))
+        xchg.publish(seq, d_res[slot].ptr, stream)
+        compacted.record(slot, stream)
+        abi.check(L.twg_event_wait(compacted.ev[slot], side))
+        xchg.collect(seq, side)
+        host_s[0] += time.perf_counter() - t_issue
+        return seq
 
-    def _launch(slot: int, i: int | None) -> None:
-        if graphs is not None:
-            graphs[slot].replay()
-        else:
-            enqueue(slot, stream, i)
-        if side is None:
-            landed[slot].record()
-
-    def collect(slot: int) -> None:
+    def collect(seq: int) -> None:
         """The step's host sync: its counts are needed on the host (output shape, global offset)."""
-        landed[slot].synchronize()
-        t_collect = time.perf_counter()
-        flat = h_all[slot].tolist()
-        counts, status = flat[0::2], flat[1::2]
-        if any(status):
-            raise RuntimeError(f"masked_select reported device status {status}")
-        counts_seen.append((sum(counts[:rank]), sum(counts)))
-        host_s[1] += time.perf_counter() - t_collect
+        t_wait = time.perf_counter()
+        counts, offset, total = xchg.wait(seq)
+        t_got = time.perf_counter()
+        counts_seen.append((counts[rank], offset, total))
+        host_s[1] += t_got - t_wait
+        host_s[2] += time.perf_counter() - t_got
 
     def run_steps(count: int, timed: bool) -> None:
+        pending: list[int] = []
         for i in range(count):
-            launch(i % DEPTH, i if timed else None)
-            if i >= DEPTH - 1:
-                collect((i - (DEPTH - 1)) % DEPTH)
-        for i in range(max(count - (DEPTH - 1), 0), count):
-            collect(i % DEPTH)
+            pending.append(launch(i if timed else None))
+            if len(pending) >= DEPTH:
+                collect(pending.pop(0))
+        while pending:
+            collect(pending.pop(0))
 
-    run_steps(max(warmup, 1), False)
-    if want_graphs:
-        try:
-            barrier()
-            before = int(L.twg_launch_count())
-            graphs = capture_graphs()
-            launches_per_step = (int(L.twg_launch_count()) - before) // DEPTH
-            run_steps(DEPTH, False)   # one replay of every graph before the clock starts
-        except Exception as exc:  # noqa: BLE001 - any capture problem means: keep the plain calls
-            graphs, graph_note = None, f"graph capture failed, plain calls used: {type(exc).__name__}: {exc}"[:300]
-            torch.cuda.synchronize()
-    barrier()
+    # the clock sampler attaches to NVML before the ranks meet, so that nothing but the record of
+    # the first event lies between the barrier and the timed region
     sampler = ClockSampler(local_rank)
+    run_steps(max(warmup, 1), False)
     if rank == 0:
         sampler.start()
     L.twg_reset_launch_count()
-    host_s[0] = host_s[1] = 0.0
+    counts_seen.clear()
+    barrier()
+    host_s[0] = host_s[1] = host_s[2] = 0.0
     ev.record(0, stream)
     run_steps(steps, True)
     ev.record(1, stream)
     ev.sync(1)
-    launches = int(L.twg_launch_count()) + (steps * launches_per_step if graphs is not None else 0)
+    launches = int(L.twg_launch_count())
     barrier()
     clocks = sampler.stop() if rank == 0 else {}
-    if graphs is not None:
-        # the events around the fused kernel cannot sit inside a graph: time it right after the
-        # timed region, same buffers, same clocks
-        for i in range(steps):
-            ev.record(2 + 2 * i, stream)
-            abi.check(L.twg_fused_launch(program, ctypes.byref(desc4), ptrs, stream))
-            ev.record(3 + 2 * i, stream)
-        ev.sync(3 + 2 * (steps - 1))
     ms_total = ev.elapsed(0, 1)
-    fused_ms = statistics.mean(ev.elapsed(2 + 2 * i, 3 + 2 * i) for i in range(steps))
-    t = torch.tensor([ms_total, fused_ms], dtype=torch.float64, device=cuda_dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total, fused_ms_max = float(t[0]), float(t[1])
+    fused_samples = [ev.elapsed(2 + 2 * i, 3 + 2 * i) for i in range(steps)]
+    intervals = [ev.elapsed(2 + 2 * i, 4 + 2 * i) for i in range(steps - 1)]
+    mine = {"ms_total": ms_total, "fused_ms": statistics.mean(fused_samples),
+            "first_kernel_ms": ev.elapsed(0, 2), "tail_ms": ev.elapsed(2 + 2 * (steps - 1), 1),
+            "step_ms_median": statistics.median(intervals) if intervals else ms_total,
+            "step_ms_p90": sorted(intervals)[int(0.9 * (len(intervals) - 1))] if intervals else ms_total,
+            "step_ms_max": max(intervals) if intervals else ms_total,
+            "host_us": [round(x / steps * 1e6, 1) for x in host_s],
+            "count": counts_seen[-1][0], "offset": counts_seen[-1][1], "total": counts_seen[-1][2],
+            "same_every_step": len(set(counts_seen)) == 1}
+    per_rank = [json.loads(x) for x in rdv.share(json.dumps(mine).encode())]
+    ms_total = max(r["ms_total"] for r in per_rank)
+    fused_ms_max = max(r["fused_ms"] for r in per_rank)
     ms_per_step = ms_total / steps
     value = BATCH * SLAB / (ms_per_step * 1e-3) / 1e9
-    total_k = counts_seen[-1][1]
+    total_k = per_rank[0]["total"]
+    # every rank saw the same total, the offsets are the exclusive prefix sums of the counts, and
+    # no step produced a different count from the others (the inputs never change)
+    acc = 0
+    for r in per_rank:
+        if r["total"] != total_k or r["offset"] != acc or not r["same_every_step"]:
+            raise RuntimeError(f"bench: inconsistent counts across ranks or steps: {per_rank}")
+        acc += r["count"]
+    if acc != total_k:
+        raise RuntimeError(f"bench: the ranks' counts add up to {acc}, the exchanged total is {total_k}")
+
+    # ---- verification, not timed: this rank's first and last slab against the CPU oracle --------
+    verified = None
+    if not args.no_verify:
+        from oracle import oracle
+        oracle.build()
+        oracle.set_num_threads(max(1, len(cores) or (os.cpu_count() or 1)))
+        last_slot = (seq_next[0] - 1) % DEPTH
+        k_mine = counts_seen[-1][0]
+        for which in sorted({0, nb - 1}):
+            gmask = d_mask.download(np.uint8, SLAB, stream, offset_bytes=which * SLAB)
+            kept = int(np.count_nonzero(gmask))
+            seg_lo = 0 if which == 0 else k_mine - kept      # first slab: head of the output; last slab: its tail
+            if nb == 1 and kept != k_mine:
+                raise RuntimeError(f"bench verification failed: the mask keeps {kept} elements, the kernel counted {k_mine}")
+            gsel = d_out[last_slot].download(np.float32, kept, stream, offset_bytes=4 * seg_lo)
+            verify_slab(oracle, host[0][which].numpy(), host[1][which].numpy(), host[2][which].numpy(), gmask, gsel,
+                        f"rank {rank}, slab {lo + which}")
+        verified = all(x == b"ok" for x in rdv.share(b"ok"))
 
     # ---- per-op table (single GPU only) -----------------------------------------------------
     del d_out, d_mask, d_ws
     for b_ in dev_in:
         b_.free()
     ops = per_op_table(abi, stream, peak) if world == 1 and not args.no_ops else None
-    stream = ctypes.c_void_p(torch.webgpu.current_stream_handle(local_rank))  # leg 2 runs on the backend's own stream
     abi.check(L.twg_empty_cache(local_rank))
 
-    # ---- leg 2: end to end through the public API with host buffers ---------------------------
+    # ---- the public API: torch.compile(chain, backend=webgpu_backend) -------------------------
     def chain(a, b, c):
         y = torch.relu(torch.nn.functional.silu(a + b) + c)
         m = torch.bitwise_and(torch.eq(y, 0), torch.ne(a, 0))
@@ -785,10 +817,47 @@ def run_gpu_arm(args) -> None:
 
     compiled = torch.compile(chain, backend=webgpu_backend)
     dev_name = f"webgpu:{local_rank}"
+    d_cnt = abi.DeviceBuffer(16, local_rank, stream)
+    h_cnt = (ctypes.c_int64 * 2)()
+
+    def exchange_count(k: int) -> tuple[int, int]:
+        """The count a rank's masked_select returned, told to every rank: (global offset, total)."""
+        seq = seq_next[0]
+        seq_next[0] += 1
+        h_cnt[0], h_cnt[1] = k, 0
+        abi.check(L.twg_memcpy_h2d(d_cnt.ptr, ctypes.addressof(h_cnt), 16, stream))
+        xchg.publish(seq, d_cnt.ptr, stream)
+        xchg.collect(seq, stream)
+        _counts, offset, total = xchg.wait(seq)
+        return offset, total
+
+    # (a) inputs resident on the device: what a drop-in user of the backend gets per step
+    resident = [h.to(dev_name) for h in host]
+    api_steps = max(1, min(steps, 10))
+    for _ in range(2):
+        compiled(*resident)
+    barrier()
+    ev3 = Events(abi, 2)
+    ev3.record(0, stream)
+    for _ in range(api_steps):
+        sel = compiled(*resident)     # ends with the count read-back that sizes the result
+        api_total = exchange_count(sel.numel())[1]
+    ev3.record(1, stream)
+    ev3.sync(1)
+    if api_total != total_k:
+        raise RuntimeError(f"bench: the public API selected {api_total} elements, the C ABI leg {total_k}")
+    api_ms = max(float(x) for x in rdv.share(repr(ev3.elapsed(0, 1) / api_steps).encode()))
+    public_api = {"value": BATCH * SLAB / (api_ms * 1e-3) / 1e9, "unit": "Gelem/s", "ms_per_step": api_ms, "steps": api_steps,
+                  "api": "torch.compile(chain, backend=webgpu_backend)(a, b, c) on device-resident webgpu tensors; "
+                         "every call ends with the blocking count read-back of masked_select"}
+    del resident, sel
+    abi.check(L.twg_empty_cache(local_rank))
+
+    # (b) end to end with host buffers: upload of a, b, c and read-back of the result every step
     h_sel = [torch.empty(n, pin_memory=True) for _ in range(2)]   # the read-back of step i runs under step i+1's uploads
     e2e_steps = max(1, min(steps, 8))
     d2h_bytes = [0]
-    side = torch.Stream(device=dev_name)
+    side2 = torch.Stream(device=dev_name)
     in_flight: list = []    # (event after the read-back, the tensor it reads) of the previous step
 
     def retire() -> None:
@@ -802,17 +871,17 @@ def run_gpu_arm(args) -> None:
         k = sel.numel()
         ready = torch.Event(device=dev_name)
         ready.record()
-        with side:                                  # PCIe is full duplex: read back on a second stream
-            side.wait_event(ready)
+        with side2:                                 # PCIe is full duplex: read back on a second stream
+            side2.wait_event(ready)
             h_sel[i & 1][:k].copy_(sel, non_blocking=True)
             copied = torch.Event(device=dev_name)
             copied.record()
         retire()                                    # the previous step's result is now complete on the host
         in_flight.append((copied, sel))
         d2h_bytes[0] = 4 * k + 16
-        global_segment(k, cuda_dev)
+        exchange_count(k)
 
-    e2e_step(0)  # compile + warm the allocator
+    e2e_step(0)  # warm the allocator
     retire()
     barrier()
     ev2 = Events(abi, 2)
@@ -827,16 +896,32 @@ def run_gpu_arm(args) -> None:
     barrier()
     # the last read-back runs on the second stream, which the events on the main stream do not see:
     # the host clock around the loop (it ends after retire()) bounds it, so take the larger
-    t = torch.tensor([max(ev2.elapsed(0, 1), host_ms)], dtype=torch.float64, device=cuda_dev)
-    tb = torch.tensor([3 * 4 * n, d2h_bytes[0]], dtype=torch.int64, device=cuda_dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dist.all_reduce(tb, op=dist.ReduceOp.SUM)
-    e2e_ms = float(t[0]) / e2e_steps
+    e2e_mine = max(ev2.elapsed(0, 1), host_ms) / e2e_steps
+    # the same uploads and nothing else: what the host side of PCIe delivers to this many GPUs at once
+    staging = [abi.DeviceBuffer(4 * n, local_rank, stream) for _ in range(3)]
+    for _ in range(2):
+        for buf, h in zip(staging, host):
+            abi.check(L.twg_memcpy_h2d(buf.ptr, h.data_ptr(), 4 * n, stream))
+    barrier()
+    ev4 = Events(abi, 2)
+    ev4.record(0, stream)
+    for _ in range(4):
+        for buf, h in zip(staging, host):
+            abi.check(L.twg_memcpy_h2d(buf.ptr, h.data_ptr(), 4 * n, stream))
+    ev4.record(1, stream)
+    ev4.sync(1)
+    h2d_only_ms = ev4.elapsed(0, 1) / 4
+    del staging
+    shared = [json.loads(x) for x in rdv.share(json.dumps([e2e_mine, h2d_only_ms, 3 * 4 * n, d2h_bytes[0]]).encode())]
+    e2e_ms = max(s[0] for s in shared)
+    h2d_total, d2h_total = sum(s[2] for s in shared), sum(s[3] for s in shared)
     e2e = {"value": BATCH * SLAB / (e2e_ms * 1e-3) / 1e9, "unit": "Gelem/s", "ms_per_step": e2e_ms, "steps": e2e_steps,
-           "h2d_bytes_per_step": int(tb[0]), "d2h_bytes_per_step": int(tb[1]),
+           "h2d_bytes_per_step": int(h2d_total), "d2h_bytes_per_step": int(d2h_total),
+           "h2d_gbs_achieved": round(h2d_total / e2e_ms / 1e6, 1),
+           "h2d_only_gbs": round(h2d_total / max(s[1] for s in shared) / 1e6, 1),
            "api": "x.to('webgpu') from pinned tensors, torch.compile(backend=webgpu_backend) chain, pinned read-back "
-                  "on a second torch.Stream so that it overlaps the next step's uploads"}
+                  "on a second torch.Stream so that it overlaps the next step's uploads; h2d_only_gbs is the same "
+                  "uploads with nothing else running, all ranks at once"}
 
     if rank == 0:
         achieved = CHAIN_BYTES_PER_ELEM * n / (fused_ms_max * 1e-3) / 1e9
@@ -844,28 +929,36 @@ def run_gpu_arm(args) -> None:
         line = {
             "metric": "Gelem/s of the compiled chain + masked_select", "value": value, "unit": "Gelem/s", "n_gpus": world,
             "steps": steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(world),
-            "selected_elements": total_k,
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(world, DEPTH),
+            "selected_elements": total_k, "verified": verified,
             "roofline": {"bound": "hbm", "kernel": "pw_contig_kernel<AotChainMask> (fused chain, 13 B/elem)",
                          "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": traffic, "ms_per_launch": fused_ms_max,
-                         "algorithmic_bytes_per_launch": CHAIN_BYTES_PER_ELEM * n},
-            "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
-            "host_us_per_step": {"issue": round(host_s[0] / steps * 1e6, 1), "collect": round(host_s[1] / steps * 1e6, 1)},
-            "count_allgather": "second stream" if side is not None else ("compute stream" if world > 1 else "none"),
-            "step_issue": ("one CUDA graph replay per step; the fused kernel's ms_per_launch is timed right after the "
-                           "timed region") if graphs is not None else "plain calls",
+                         "frac": achieved / peak, "frac_of_nominal_8000": achieved / NOMINAL_HBM_GBS, "traffic": traffic,
+                         "ms_per_launch": fused_ms_max, "algorithmic_bytes_per_launch": CHAIN_BYTES_PER_ELEM * n},
+            "e2e": e2e, "public_api": public_api, "gpu_launches": launches, "clocks": clocks,
+            "step_ms_median": max(r["step_ms_median"] for r in per_rank),
+            "step_timing": {"per_rank_ms_total": [round(r["ms_total"], 4) for r in per_rank],
+                            "step_ms_median": [round(r["step_ms_median"], 4) for r in per_rank],
+                            "step_ms_p90": [round(r["step_ms_p90"], 4) for r in per_rank],
+                            "step_ms_max": [round(r["step_ms_max"], 4) for r in per_rank],
+                            "first_kernel_ms": [round(r["first_kernel_ms"], 4) for r in per_rank],
+                            "last_step_and_drain_ms": [round(r["tail_ms"], 4) for r in per_rank],
+                            "host_us_per_step_issue_wait_handle": [r["host_us"] for r in per_rank]},
+            "count_exchange": xchg.kind, "cores_per_rank": len(cores),
         }
-        if graph_note:
-            line["step_issue_note"] = graph_note
+        if exchange_note:
+            line["count_exchange_note"] = exchange_note[:300]
         if ops is not None:
             line["ops"] = ops
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = run_cpu_baseline()
         print(json.dumps(line), flush=True)
-    if world > 1:
-        barrier()
-        dist.destroy_process_group()
+    barrier()
+    if xchg is not nccl:
+        xchg.close()
+    if nccl is not None:
+        nccl.close()
+    rdv.barrier()
 
 
 def main() -> None:
@@ -875,13 +968,19 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-ops", action="store_true", help="skip the per-op GB/s table")
-    ap.add_argument("--graphs", default="off", choices=["on", "off"],
-                    help="replay each step as a CUDA graph (single-GPU runs only)")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "nccl"],
+                    help="how the ranks exchange their counts: the library's peer-store kernels, ncclAllGather through "
+                         "the C ABI, or (auto) peer stores when every rank can map every other rank's mailbox")
+    ap.add_argument("--no-verify", action="store_true", help="skip the oracle check of each rank's first and last slab")
+    ap.add_argument("--batch", type=int, default=64,
+                    help="slabs in the batch (64 is the benchmark; smaller values are for diagnosing overheads)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--case", default=None, help="run one kernel on a small case (for ncu captures) and exit")
     ap.add_argument("--case-elems", type=int, default=1 << 27)
     ap.add_argument("--case-density", type=float, default=0.5)
     args = ap.parse_args()
+    global BATCH
+    BATCH = args.batch
     if args.case:
         run_case(args)
     elif args.impl == "reference":

@@ -285,6 +285,59 @@ int twg_fused_set_nvrtc_path(const char* path);
  * be given); the pointer stays valid until twg_fused_release. */
 int twg_fused_source(const TwgFusedProgram* p, const char** source);
 
+/* ---- the count exchange of the batch-sharded path ---------------------------------------------
+ * No counterpart in the reference: it drives one device (`webgpu_device_count = 1`,
+ * csrc/core/webgpu_device_guard.h:9).  When a batch is cut over several GPUs, masked_select of
+ * the whole batch is the concatenation of the per-rank results in rank order, and the only thing
+ * the ranks have to tell each other is how many elements each produced (one int64 + one status
+ * per rank and step).  Two transports:
+ *
+ * (1) NCCL.  libnccl.so.2 is loaded on first use (dlopen); without it these calls return
+ *     TWG_ERR_UNSUPPORTED and everything else keeps working.  The 128-byte unique id made on one
+ *     rank must reach the others through the host's own channel (a file, a socket, a key-value
+ *     store).  Plain ncclAllGather on the caller's stream; `n` int64 per rank. */
+#define TWG_COMM_ID_BYTES 128
+int twg_comm_set_nccl_path(const char* path);   /* honoured only before the first NCCL call */
+int twg_comm_unique_id(void* out128);
+int twg_comm_init_rank(const void* unique_id, int rank, int nranks, void** comm);  /* blocks: all ranks must call */
+int twg_comm_destroy(void* comm);
+int twg_allgather_i64(void* comm, const int64_t* send_dev, int64_t* recv_dev, int n, void* stream);
+/* (2) Peer stores over NVLink, no library call on the step.  Every rank creates an exchange object
+ *     on its device (current device of the calling thread), hands its 64-byte handle to every other
+ *     rank and connects theirs (twg_exchange_connect_ipc for ranks in other processes,
+ *     twg_exchange_connect_local for ranks of the same process).  Per step, with a sequence number
+ *     seq = 1, 2, 3 ... that all ranks use for the same step:
+ *       twg_exchange_publish(x, seq, result_dev, stream)   after masked_select on `stream`:
+ *           a one-warp kernel stores {result_dev[0], seq, result_dev[1]} into this rank's slot of
+ *           every rank's mailbox (plain stores to peer memory, the flag word a release store);
+ *       twg_exchange_collect(x, seq, stream2)   on any stream ordered after the publish:
+ *           a one-warp kernel waits until every rank's slot of the local mailbox carries `seq`
+ *           (bounded: after the time limit a missing rank is reported as TWG_ERR_TIMEOUT in its
+ *           status and the kernel returns), then writes counts, statuses, this rank's exclusive
+ *           offset and the total to device memory (twg_exchange_gathered) and to pinned host memory;
+ *       twg_exchange_wait(x, seq, counts, statuses, &offset, &total, timeout_ms)   blocks:
+ *           the host polls that pinned record; returns the worst status (TWG_OK when every rank
+ *           reported 0).  counts / statuses hold nranks entries; any output may be NULL.
+ *     Rule for reusing mailbox slots (slot = seq % ring): publish seq only after twg_exchange_wait
+ *     has returned for seq - ring/2 on this rank.  Nothing reads a peer's memory, there is no
+ *     multicast and no TMA; a rank that never publishes costs the others one time limit, not a hang. */
+#define TWG_EXCHANGE_HANDLE_BYTES 64
+#define TWG_EXCHANGE_MAX_RANKS 16
+int twg_exchange_create(int rank, int nranks, int ring, void** xchg);   /* blocks (allocates, clears) */
+int twg_exchange_handle(void* xchg, void* out64);
+int twg_exchange_connect_ipc(void* xchg, int peer_rank, const void* handle64);
+int twg_exchange_connect_local(void* xchg, int peer_rank, void* peer_xchg);
+int twg_exchange_publish(void* xchg, int64_t seq, const int64_t* result_dev, void* stream);
+int twg_exchange_collect(void* xchg, int64_t seq, void* stream);
+int twg_exchange_wait(void* xchg, int64_t seq, int64_t* counts, int64_t* statuses, int64_t* offset, int64_t* total,
+                      int timeout_ms);
+/* Device copy of the record of `seq`: int64[2*nranks + 2] = counts, statuses, offset, total; valid
+ * for work ordered after that step's twg_exchange_collect. */
+int twg_exchange_gathered(void* xchg, int64_t seq, const int64_t** dev_record);
+/* Time limit of the collect kernel's wait (default 2 s; <= 0 restores the default). */
+int twg_exchange_set_timeout_ns(void* xchg, int64_t timeout_ns);
+int twg_exchange_destroy(void* xchg);   /* blocks */
+
 /* ---- launch accounting: number of kernels this library launched on the calling thread's
  *      behalf since the last reset (all threads), used by the benchmark's gpu_launches ----- */
 int64_t twg_launch_count(void);

@@ -243,3 +243,70 @@ def test_two_rank_sharding_reproduces_the_single_rank_result(tmp_path):
     for p in parts:
         out[int(p["offset"]): int(p["offset"]) + p["sel"].size] = p["sel"]
     assert np.array_equal(out.view(np.uint32), ref.view(np.uint32))
+
+
+def _share_main(rank: int, world: int, port: int, out_dir: str) -> None:
+    from torch_webgpu.sharding import Rendezvous
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    os.environ.pop("TORCHELASTIC_USE_AGENT_STORE", None)
+    rdv = Rendezvous.from_env()
+    got = rdv.share(f"handle-of-{rank}".encode() * (rank + 1))
+    uid = rdv.broadcast(b"\x07" * 128 if rank == 0 else None)
+    rdv.barrier()
+    with open(os.path.join(out_dir, f"share{rank}.txt"), "w") as f:
+        f.write(repr((rdv.rank, rdv.world, got, uid)))
+
+
+def test_rendezvous_channel_passes_startup_data_between_two_ranks(tmp_path):
+    """The host-side channel that carries the NCCL unique id and the mailbox handles at start-up."""
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_share_main, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    expect = [b"handle-of-0", b"handle-of-1" * 2]
+    for r in range(2):
+        rank, world, got, uid = eval((tmp_path / f"share{r}.txt").read_text())
+        assert (rank, world, got, uid) == (r, 2, expect, b"\x07" * 128)
+    from torch_webgpu.sharding import Rendezvous
+    solo = Rendezvous(None, 0, 1)
+    assert solo.share(b"x") == [b"x"] and solo.broadcast(b"y") == b"y"
+
+
+def test_communicator_entry_points_fail_cleanly_on_the_host(abi):
+    """Bad arguments and a missing NCCL library come back as status codes with a message - no
+    crash, no exception from the C side, nothing touches a GPU."""
+    import subprocess
+    import sys
+    L = abi.lib()
+    comm = ctypes.c_void_p(123)
+    assert L.twg_comm_init_rank(ctypes.c_char_p(b"\0" * 128), 0, 2, ctypes.byref(comm)) == abi.TWG_ERR_INVALID
+    assert comm.value is None and b"all zeros" in L.twg_last_error()
+    assert L.twg_comm_init_rank(ctypes.c_char_p(b"\1" * 128), 2, 2, ctypes.byref(comm)) == abi.TWG_ERR_INVALID
+    assert L.twg_comm_init_rank(None, 0, 1, ctypes.byref(comm)) == abi.TWG_ERR_INVALID
+    assert L.twg_allgather_i64(None, None, None, 1, None) == abi.TWG_ERR_INVALID
+    assert L.twg_comm_destroy(None) == abi.TWG_OK
+    x = ctypes.c_void_p()
+    assert L.twg_exchange_create(0, 17, 8, ctypes.byref(x)) == abi.TWG_ERR_INVALID       # too many ranks
+    assert L.twg_exchange_create(3, 2, 8, ctypes.byref(x)) == abi.TWG_ERR_INVALID        # rank outside the world
+    assert L.twg_exchange_create(0, 2, 3, ctypes.byref(x)) == abi.TWG_ERR_INVALID        # odd ring
+    assert L.twg_exchange_publish(None, 1, None, None) == abi.TWG_ERR_INVALID
+    assert L.twg_exchange_wait(None, 1, None, None, None, None, 0) == abi.TWG_ERR_INVALID
+    assert L.twg_exchange_destroy(None) == abi.TWG_OK
+    # a library path that does not exist: TWG_ERR_UNSUPPORTED from every NCCL entry point (own
+    # process, because the path is only honoured before the first NCCL call)
+    code = (
+        "import ctypes, sys\n"
+        f"sys.path.insert(0, {str(REPO / 'torch-webgpu_b200')!r})\n"
+        "from torch_webgpu import abi\n"
+        "L = abi.lib()\n"
+        "assert L.twg_comm_set_nccl_path(b'/nonexistent/libnccl.so.2') == 0\n"
+        "buf = ctypes.create_string_buffer(128)\n"
+        "rc = L.twg_comm_unique_id(buf)\n"
+        "assert rc == abi.TWG_ERR_UNSUPPORTED, rc\n"
+        "assert b'/nonexistent/libnccl.so.2' in L.twg_last_error()\n"
+        "comm = ctypes.c_void_p()\n"
+        "assert L.twg_comm_init_rank(ctypes.c_char_p(b'\\x01' * 128), 0, 1, ctypes.byref(comm)) == abi.TWG_ERR_UNSUPPORTED\n"
+        "print('ok')\n")
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0 and out.stdout.strip() == "ok", out.stderr

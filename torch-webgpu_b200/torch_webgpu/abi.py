@@ -118,6 +118,22 @@ SIGNATURES = {
                                      c_size_t, c_void_p]),
     "twg_fused_set_nvrtc_path": (c_int, [c_char_p]),
     "twg_fused_source": (c_int, [c_void_p, POINTER(c_char_p)]),
+    "twg_comm_set_nccl_path": (c_int, [c_char_p]),
+    "twg_comm_unique_id": (c_int, [c_void_p]),
+    "twg_comm_init_rank": (c_int, [c_void_p, c_int, c_int, POINTER(c_void_p)]),
+    "twg_comm_destroy": (c_int, [c_void_p]),
+    "twg_allgather_i64": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "twg_exchange_create": (c_int, [c_int, c_int, c_int, POINTER(c_void_p)]),
+    "twg_exchange_handle": (c_int, [c_void_p, c_void_p]),
+    "twg_exchange_connect_ipc": (c_int, [c_void_p, c_int, c_void_p]),
+    "twg_exchange_connect_local": (c_int, [c_void_p, c_int, c_void_p]),
+    "twg_exchange_publish": (c_int, [c_void_p, c_int64, c_void_p, c_void_p]),
+    "twg_exchange_collect": (c_int, [c_void_p, c_int64, c_void_p]),
+    "twg_exchange_wait": (c_int, [c_void_p, c_int64, POINTER(c_int64), POINTER(c_int64), POINTER(c_int64),
+                                  POINTER(c_int64), c_int]),
+    "twg_exchange_gathered": (c_int, [c_void_p, c_int64, POINTER(c_void_p)]),
+    "twg_exchange_set_timeout_ns": (c_int, [c_void_p, c_int64]),
+    "twg_exchange_destroy": (c_int, [c_void_p]),
     "twg_launch_count": (c_int64, []),
     "twg_reset_launch_count": (None, []),
     "twg_last_launch_path": (c_int, []),
