@@ -494,13 +494,14 @@ def run_case(args) -> None:
         fn = lambda: abi.check(L.twg_binary_f32(0, ctypes.byref(d), x.ptr, y.ptr, 1.0, z.ptr, stream))
         nbytes = 12 * n
         bufs = [x, y, z]
-    elif args.case == "relu_transposed":
+    elif args.case in ("relu_transposed", "silu_transposed", "gelu_erf_transposed"):
         r = int(round(n ** 0.5))
         n = r * r
         x, y = abi.DeviceBuffer(4 * n), abi.DeviceBuffer(4 * n)
         x.upload(host(n))
         d = abi.make_desc((r, r), [((r, r), (r, 1)), ((r, r), (1, r))])
-        fn = lambda: abi.check(L.twg_unary_f32(1, ctypes.byref(d), x.ptr, y.ptr, stream))
+        op = abi.UNARY[args.case[:-len("_transposed")]]
+        fn = lambda: abi.check(L.twg_unary_f32(op, ctypes.byref(d), x.ptr, y.ptr, stream))
         nbytes = 8 * n
         bufs = [x, y]
     elif args.case in ("masked_select", "masked_select_rowmask", "masked_select_transposed", "masked_select_colmask",

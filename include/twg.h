@@ -130,6 +130,12 @@ int twg_host_free_pinned(void* ptr);
  * desc operands: [0] = out, [1] = in. */
 int twg_copy_strided(const TwgIterDesc* desc, int itemsize, const void* in, void* out, void* stream);
 
+/* fill_.Scalar / zero_ for any dtype: every element of `out` becomes the low `itemsize` bytes
+ * (1, 2, 4 or 8) of `pattern`, i.e. the value's bit pattern in the tensor's dtype.  The reference
+ * has no fill: its tensors are born uninitialised (csrc/ops/basic.cpp:51-96) and are written by
+ * Queue.WriteBuffer from a host copy (copy.cpp:90).  desc operands: [0]=out. */
+int twg_fill(const TwgIterDesc* desc, int itemsize, uint64_t pattern, void* out, void* stream);
+
 /* ---- pointwise kernels ------------------------------------------------------------------- */
 typedef enum TwgUnaryOp {
   TWG_UNARY_COPY = 0,       /* unary.cpp:88  */

@@ -337,6 +337,36 @@ def test_masked_select_mixed_density(abi):
     assert abi.last_path() == "dense"
 
 
+@pytest.mark.parametrize("pad", [0, 1, 2, 3])
+def test_masked_select_runs_of_full_and_empty_spans(abi, pad):
+    """Whole 512-element spans selected or empty, at every output alignment: the straight-copy path
+    of full spans, its hand-over to and from staged spans, skipped spans, and output runs that start
+    and end inside a 16-byte vector."""
+    n = 37 * 4096 + 300
+    x = rnd(n, 74)
+    rng = np.random.default_rng(75 + pad)
+    mask = np.zeros(n, np.bool_)
+    for s0 in range(0, n, 512):
+        kind = rng.integers(0, 5)
+        if kind == 0:
+            mask[s0:s0 + 512] = True
+        elif kind == 1:
+            mask[s0:s0 + 512] = rng.random(min(512, n - s0)) < 0.5
+        elif kind == 2:
+            mask[s0 + rng.integers(0, 8)] = True          # a lone element: shifts the alignment of what follows
+        elif kind == 3:
+            mask[s0:s0 + 512] = rng.random(min(512, n - s0)) < 0.97
+    assert_bit_equal(abi.masked_select(x, mask, pad=pad), oracle.masked_select(x, mask), f"span runs pad={pad}")
+    ones = np.ones(n, np.bool_)
+    assert_bit_equal(abi.masked_select(x, ones, pad=pad), x, f"all true pad={pad}")
+    ones[0] = False                                          # every full span now starts one element off a vector
+    assert_bit_equal(abi.masked_select(x, ones, pad=pad), x[1:], f"all true but the first, pad={pad}")
+    rows, cols = 300, 1536                                   # row mask: selected rows are three full spans each
+    y = rnd(rows * cols, 76).reshape(rows, cols)
+    rowmask = rng.random((rows, 1)) < 0.5
+    assert_bit_equal(abi.masked_select(y, rowmask, pad=pad), oracle.masked_select(y, rowmask), f"row mask pad={pad}")
+
+
 @pytest.mark.parametrize("pad", [1, 2, 3])
 def test_masked_select_misaligned(abi, pad):
     n = 5 * 4096 + 123
@@ -453,6 +483,51 @@ def test_fused_select_equals_mask_then_masked_select(abi, n):
     assert kind == "aot"
     assert_bit_equal(sel, abi.masked_select(a, m), "fused select vs mask + masked_select")
     assert_bit_equal(sel, oracle.masked_select(a, m), "fused select vs oracle on the same mask")
+
+
+def test_fused_select_on_the_decision_boundary_of_the_chain(abi):
+    """The select form of the chain decides most elements with a cheap bound and only computes the
+    exact silu inside a narrow band around silu(a + b) + c == 0.  Inputs placed on and next to that
+    boundary, huge and non-finite values must give the same mask as the exact chain."""
+    n = 1 << 18
+    rng = np.random.default_rng(91)
+    a = (rng.random(n, dtype=np.float32) * 8 - 4).astype(np.float32)
+    bb = (rng.random(n, dtype=np.float32) * 8 - 4).astype(np.float32)
+    s = oracle.unary("silu", oracle.binary("add", a, bb))
+    c = (-s).astype(np.float32)                                   # silu(a + b) + c is within a few ulp of zero
+    k = np.arange(n) % 8
+    for step, sel in ((1, k == 1), (2, k == 2), (40, k == 3), (400, k == 4)):
+        c[sel] = (c[sel].view(np.int32) + step).view(np.float32)  # a few ulp to a few hundred ulp away
+    for step, sel in ((1, k == 5), (300, k == 6)):
+        c[sel] = (c[sel].view(np.int32) - step).view(np.float32)
+    far = rng.random(n) < 0.02                                    # and some values far outside the fast range
+    a[far] = rng.choice(np.array([100.0, -100.0, 3e38, -3e38, np.inf, -np.inf, np.nan, 1e-42, -1e-42, 0.0], np.float32), int(far.sum()))
+    c[rng.random(n) < 0.01] = np.float32(0.0)
+    (m,), _ = abi.fused(abi.CHAIN_MASK_PROGRAM, [a, bb, c], [np.bool_])
+    sel, kind = abi.fused_select(abi.CHAIN_MASK_PROGRAM, [a, bb, c], 0)
+    assert kind == "aot"
+    assert 0.2 < m.mean() < 0.8
+    assert_bit_equal(sel, oracle.masked_select(a, m), "fused select on the boundary vs the exact chain's mask")
+
+
+def test_fill_every_width_and_layout(abi):
+    rng = np.random.default_rng(92)
+    for dtype, value in ((np.uint8, 7), (np.int16, -3), (np.float32, -0.0), (np.float32, np.nan), (np.int64, -(1 << 40)),
+                         (np.float64, 2.5)):
+        for n in (1, 3, 15, 16, 17, 4099, 100003):
+            base = rng.integers(0, 100, n).astype(dtype)
+            for pad in (0, 1, 3):
+                got = abi.fill(base, value, pad=pad)
+                assert_bit_equal(got.view(np.uint8), np.full(n, value, dtype).view(np.uint8), f"fill {dtype.__name__} n={n} pad={pad}")
+        grid = rng.integers(0, 100, (33, 47)).astype(dtype)
+        got = abi.fill(grid[::2, 1::3], value).reshape(33, 47)       # only the view's elements change
+        ref = grid.copy()
+        ref[::2, 1::3] = value
+        assert_bit_equal(got.view(np.uint8), ref.view(np.uint8), f"strided fill {dtype.__name__}")
+        assert abi.last_path() in ("strided32", "dense")
+    d = abi.IterDesc()
+    abi.check(abi.lib().twg_iter_contiguous(__import__("ctypes").byref(d), 1, 4))
+    assert abi.lib().twg_fill(__import__("ctypes").byref(d), 3, 0, 1, None) == abi.TWG_ERR_INVALID
 
 
 def test_fused_select_with_a_predicate_compiled_at_run_time(abi):

@@ -121,7 +121,9 @@ def build_host(force: bool = False, verbose: bool = False) -> Path:
     sources = sorted(HOST.glob("*.cpp"))
     headers = sorted(HOST.glob("*.h")) + [INCLUDE / "twg.h"]
     inc, lib = torch_paths()
-    flags = ["-O2", "-g1", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-D_GLIBCXX_USE_CXX11_ABI=1",
+    import torch
+    cxx11_abi = int(bool(getattr(torch._C, "_GLIBCXX_USE_CXX11_ABI", True)))   # must match the installed libtorch
+    flags = ["-O2", "-g1", "-std=c++17", "-fPIC", "-fvisibility=hidden", f"-D_GLIBCXX_USE_CXX11_ABI={cxx11_abi}",
              "-DTORCH_EXTENSION_NAME=_C", "-Wall", "-Wno-unused-function", "-Wno-sign-compare"]
     key = digest(sources + headers, " ".join(flags))
     stamp = BUILD / "host.stamp"

@@ -2,6 +2,8 @@
 // csrc/ops/basic.cpp:294-307 (empty.memory_format, empty_strided, as_strided, view, resize_,
 // reshape); none of them launches a kernel.  Zero-element tensors get a null DataPtr and work
 // (the reference segfaults on them, tests/ops/test_silu.py:55).
+#include <cstring>
+
 #include <ATen/EmptyTensor.h>
 #include <ATen/NativeFunctions.h>
 #include <ATen/native/Resize.h>
@@ -102,14 +104,37 @@ at::Scalar _local_scalar_dense(const at::Tensor& self) {
   return at::_local_scalar_dense(self.cpu());
 }
 
-// fill_ is not on the hot path: build the value on the host and upload it.
+// fill_.Scalar on the device for every dtype: the scalar is converted to the tensor's dtype on the
+// host (one element, PyTorch's own conversion rules) and its bit pattern is what the kernel writes.
 at::Tensor& fill_scalar(at::Tensor& self, const at::Scalar& value) {
   if (self.numel() == 0) return self;
-  at::Tensor host = at::empty(self.sizes(), self.options().device(at::kCPU));
-  host.fill_(value);
-  self.copy_(host);
+  const size_t itemsize = self.dtype().itemsize();
+  TORCH_CHECK(itemsize == 1 || itemsize == 2 || itemsize == 4 || itemsize == 8, "torch_webgpu: fill_ supports element sizes 1, 2, 4 and 8, got ",
+              itemsize, " (", self.scalar_type(), ")");
+  TORCH_CHECK(self.dim() <= TWG_MAX_DIMS, "torch_webgpu: fill_ supports at most ", TWG_MAX_DIMS, " dimensions");
+  at::Tensor one = at::scalar_tensor(value, self.options().device(at::kCPU));
+  uint64_t pattern = 0;
+  std::memcpy(&pattern, one.const_data_ptr(), itemsize);
+  TwgIterDesc d;
+  std::memset(&d, 0, sizeof(d));
+  d.ndim = static_cast<int32_t>(self.dim());
+  d.ntensors = 1;
+  d.numel = self.numel();
+  for (int k = 0; k < d.ndim; ++k) {  // dimension 0 of the descriptor is the last logical dimension
+    const int64_t dim = d.ndim - 1 - k;
+    d.shape[k] = self.size(dim);
+    d.strides[0][k] = self.size(dim) == 1 ? 0 : self.stride(dim);
+  }
+  const c10::DeviceIndex dev = self.device().index() < 0 ? core::current_device() : self.device().index();
+  core::DeviceScope scope(dev);
+  TWG_TORCH_CHECK(twg_fill(&d, static_cast<int>(itemsize), pattern, self.data_ptr(), core::current_stream(dev)));
   return self;
 }
+
+// reshape is registered by name like the reference does (csrc/ops/basic.cpp:296-307, under both
+// PrivateUse1 and AutogradPrivateUse1); the work is PyTorch's own composite: a view where the
+// strides allow one, a copy otherwise, and its shape inference and error messages.
+at::Tensor reshape(const at::Tensor& self, c10::SymIntArrayRef shape) { return at::native::reshape_symint(self, shape); }
 
 at::Tensor& zero_(at::Tensor& self) {
   if (self.numel() == 0) return self;
@@ -131,12 +156,15 @@ TORCH_LIBRARY_IMPL(aten, PrivateUse1, m) {
   m.impl("as_strided", TORCH_FN(as_strided));
   m.impl("_reshape_alias", TORCH_FN(_reshape_alias));
   m.impl("resize_", TORCH_FN(resize_));
+  m.impl("reshape", TORCH_FN(reshape));
   m.impl("set_.source_Storage_storage_offset", TORCH_FN(set_source_storage_offset));
   m.impl("set_.source_Storage", TORCH_FN(set_source_storage));
   m.impl("set_.source_Tensor", TORCH_FN(set_source_tensor));
   m.impl("_local_scalar_dense", TORCH_FN(_local_scalar_dense));
   m.impl("fill_.Scalar", TORCH_FN(fill_scalar));
 }
+
+TORCH_LIBRARY_IMPL(aten, AutogradPrivateUse1, m) { m.impl("reshape", TORCH_FN(reshape)); }
 
 }  // namespace ops
 }  // namespace torch_webgpu

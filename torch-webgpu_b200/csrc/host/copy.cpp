@@ -127,10 +127,36 @@ static void device_to_device(at::Tensor& dst, const at::Tensor& src) {
     at::Tensor dense = src.contiguous();
     at::Tensor landed = at::empty(dense.sizes(), dst.options());
     const size_t nbytes = static_cast<size_t>(dense.numel()) * dense.dtype().itemsize();
-    // order the peer copy after the producer on the source device
-    TWG_TORCH_CHECK(twg_stream_sync(core::current_stream(dev_of(src))));
+    void* src_stream = core::current_stream(dev_of(src));
+    void* dst_stream = core::current_stream(dev_of(dst));
+    // The peer copy runs on the destination's stream.  It is ordered after the producer of `dense`
+    // by an event on the source stream, and everything the source stream does afterwards (reuse of
+    // the temporary `dense` once it is freed, in-place writes to `src`) is ordered after the copy
+    // by a second event; neither side's host thread waits.
+    // (an event belongs to the device that was current when it was created: one per side)
+    void *produced = nullptr, *copied = nullptr;
+    int rc;
+    {
+      core::DeviceScope scope(dev_of(src));
+      rc = twg_event_create(&produced);
+      if (rc == TWG_OK) rc = twg_event_record(produced, src_stream);
+    }
+    if (rc == TWG_OK) {
+      core::DeviceScope scope(dev_of(dst));
+      rc = twg_event_create(&copied);
+      if (rc == TWG_OK) rc = twg_event_wait(produced, dst_stream);
+      if (rc == TWG_OK) rc = twg_memcpy_d2d(landed.data_ptr(), dense.const_data_ptr(), nbytes, dst_stream);
+      if (rc == TWG_OK) rc = twg_event_record(copied, dst_stream);
+    }
+    if (rc == TWG_OK) {
+      core::DeviceScope scope(dev_of(src));
+      rc = twg_event_wait(copied, src_stream);
+    }
+    // destroying a recorded event is safe: its resources are released once it has completed
+    if (produced) twg_event_destroy(produced);
+    if (copied) twg_event_destroy(copied);
+    TWG_TORCH_CHECK(rc);
     core::DeviceScope scope(dev_of(dst));
-    TWG_TORCH_CHECK(twg_memcpy_d2d(landed.data_ptr(), dense.const_data_ptr(), nbytes, core::current_stream(dev_of(dst))));
     device_strided_copy(dst, landed);
     return;
   }

@@ -51,15 +51,16 @@ static int64_t run_masked_select(const at::Tensor& self_in, const at::Tensor& ma
   core::DeviceScope scope(dev);
   void* stream = core::current_stream(dev);
   TwgIterDesc desc = rowmajor_desc(shape, self, mask);
-  const size_t ws_bytes = twg_masked_select_workspace_bytes(desc.numel);
-  at::Tensor workspace = at::empty({static_cast<int64_t>(ws_bytes)}, self.options().dtype(at::kByte));
-  at::Tensor result = at::empty({2}, self.options().dtype(at::kLong));
+  // one block holds the kernel's workspace and, behind it, the two result words
+  const size_t ws_bytes = (twg_masked_select_workspace_bytes(desc.numel) + 255) / 256 * 256;
+  at::Tensor scratch = at::empty({static_cast<int64_t>(ws_bytes + 2 * sizeof(int64_t))}, self.options().dtype(at::kByte));
+  auto* result = reinterpret_cast<int64_t*>(static_cast<char*>(scratch.data_ptr()) + ws_bytes);
   TWG_TORCH_CHECK(twg_masked_select_f32(&desc, static_cast<const float*>(self.const_data_ptr()),
                                         static_cast<const uint8_t*>(mask.const_data_ptr()),
-                                        static_cast<float*>(out_storage.data_ptr()),
-                                        static_cast<int64_t*>(result.data_ptr()), workspace.data_ptr(), ws_bytes, stream));
+                                        static_cast<float*>(out_storage.data_ptr()), result, scratch.data_ptr(), ws_bytes,
+                                        stream));
   int64_t host[2] = {0, 0};
-  TWG_TORCH_CHECK(twg_memcpy_d2h(host, result.const_data_ptr(), sizeof(host), stream, 1));
+  TWG_TORCH_CHECK(twg_memcpy_d2h(host, result, sizeof(host), stream, 1));
   TORCH_CHECK(host[1] == 0, "torch_webgpu: masked_select's device-side scan failed with status ", host[1],
               host[1] == TWG_ERR_TIMEOUT ? " (a tile gave up waiting for its predecessors)" : "");
   return host[0];

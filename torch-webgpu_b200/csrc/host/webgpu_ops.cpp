@@ -106,18 +106,18 @@ at::Tensor run_fused_select(int64_t handle, at::TensorList inputs, int64_t src_i
     const c10::DeviceIndex dev = src.device().index() < 0 ? core::current_device() : src.device().index();
     core::DeviceScope scope(dev);
     void* stream = core::current_stream(dev);
-    const size_t ws_bytes = twg_masked_select_workspace_bytes(numel);
-    at::Tensor workspace = at::empty({static_cast<int64_t>(ws_bytes)}, src.options().dtype(at::kByte));
-    at::Tensor result = at::empty({2}, src.options().dtype(at::kLong));
+    // one block holds the kernel's workspace and, behind it, the two result words
+    const size_t ws_bytes = (twg_masked_select_workspace_bytes(numel) + 255) / 256 * 256;
+    at::Tensor scratch = at::empty({static_cast<int64_t>(ws_bytes + 2 * sizeof(int64_t))}, src.options().dtype(at::kByte));
+    auto* result = reinterpret_cast<int64_t*>(static_cast<char*>(scratch.data_ptr()) + ws_bytes);
     at::Tensor out = at::empty({numel}, src.options());
     std::vector<const void*> ptrs;
     for (const auto& t : inputs) ptrs.push_back(t.const_data_ptr());
     const int rc = twg_fused_select_f32(program, static_cast<int>(src_index), numel, ptrs.data(),
-                                        static_cast<float*>(out.data_ptr()), static_cast<int64_t*>(result.data_ptr()),
-                                        workspace.data_ptr(), ws_bytes, stream);
+                                        static_cast<float*>(out.data_ptr()), result, scratch.data_ptr(), ws_bytes, stream);
     if (rc == TWG_OK) {
       int64_t host[2] = {0, 0};
-      TWG_TORCH_CHECK(twg_memcpy_d2h(host, result.const_data_ptr(), sizeof(host), stream, 1));
+      TWG_TORCH_CHECK(twg_memcpy_d2h(host, result, sizeof(host), stream, 1));
       TORCH_CHECK(host[1] == 0, "torch_webgpu: the fused select's device-side scan failed with status ", host[1]);
       if (host[0] < numel) {
         TWG_TORCH_CHECK(twg_trim(out.data_ptr(), static_cast<size_t>(host[0]) * sizeof(float)));

@@ -2,6 +2,8 @@
 // bytes per element here) and the integer bitwise-and, which is the same byte-wise operation
 // for every integer width.  They share the index math of the pointwise kernels but move raw
 // bytes, so nothing is normalised or reinterpreted.
+#include <cstring>
+
 #include "twg_launch.cuh"
 
 namespace twg {
@@ -176,6 +178,69 @@ int dispatch_sized(const TwgIterDesc& d, int itemsize, const void* a, const void
   }
 }
 
+// fill: every element of `out` becomes the low `sizeof(T)` bytes of `pattern`.  Dense outputs are
+// written as 16-byte vectors between the first and last 16-byte boundary; anything else walks the
+// descriptor.
+template <class T>
+__global__ void __launch_bounds__(kBlock) fill_dense_kernel(T* out, T value, uint4 vec, i64 n) {
+  const unsigned long long addr = reinterpret_cast<unsigned long long>(out);
+  const i64 per = 16 / (i64)sizeof(T);
+  i64 head = (i64)(((16ull - (addr & 15ull)) & 15ull) / sizeof(T));
+  if (head > n) head = n;
+  const i64 nvec = (n - head) / per;
+  uint4* out4 = reinterpret_cast<uint4*>(out + head);
+  const i64 step = (i64)gridDim.x * kBlock;
+  for (i64 i = (i64)blockIdx.x * kBlock + threadIdx.x; i < nvec; i += step) st_v4(out4 + i, vec);
+  if (blockIdx.x == 0) {
+    if ((i64)threadIdx.x < head) out[threadIdx.x] = value;
+    const i64 tail0 = head + nvec * per;
+    if (tail0 + (i64)threadIdx.x < n) out[tail0 + threadIdx.x] = value;
+  }
+}
+template <class T, class IDX>
+__global__ void __launch_bounds__(kBlock) fill_strided_kernel(T* out, T value, StridedDesc<1, IDX> d, i64 n) {
+  const i64 step = (i64)gridDim.x * kBlock;
+  for (i64 e = (i64)blockIdx.x * kBlock + threadIdx.x; e < n; e += step) {
+    i64 off[1];
+    linear_to_offsets<1>(d, (IDX)e, off);
+    out[off[0]] = value;
+  }
+}
+template <class T>
+int launch_fill(const TwgIterDesc& d, unsigned long long pattern, void* out, cudaStream_t s) {
+  T value;
+  std::memcpy(&value, &pattern, sizeof(T));
+  const int64_t n = d.numel;
+  if (all_dense(d, 1)) {
+    unsigned long long two[2];
+    unsigned char* bytes = reinterpret_cast<unsigned char*>(two);
+    for (size_t i = 0; i < 16; i += sizeof(T)) std::memcpy(bytes + i, &value, sizeof(T));
+    uint4 vec;
+    std::memcpy(&vec, two, 16);
+    const int64_t nvec = n / (16 / (int64_t)sizeof(T)) + 1;
+    const unsigned grid = (unsigned)std::min<int64_t>((nvec + kBlock - 1) / kBlock, (int64_t)sm_count() * 16);
+    fill_dense_kernel<T><<<grid, kBlock, 0, s>>>(static_cast<T*>(out), value, vec, n);
+    TWG_CHECK_LAUNCH();
+    g_last_path = kPathDense;
+    return TWG_OK;
+  }
+  const unsigned grid = (unsigned)std::min<int64_t>((n + kBlock - 1) / kBlock, (int64_t)sm_count() * 32);
+  if (fits_32bit(d, 1)) {
+    StridedDesc<1, u32> sd;
+    fill_strided_desc<1>(d, &sd);
+    fill_strided_kernel<T, u32><<<grid, kBlock, 0, s>>>(static_cast<T*>(out), value, sd, n);
+    TWG_CHECK_LAUNCH();
+    g_last_path = kPathStrided32;
+  } else {
+    StridedDesc<1, u64> sd;
+    fill_strided_desc<1>(d, &sd);
+    fill_strided_kernel<T, u64><<<grid, kBlock, 0, s>>>(static_cast<T*>(out), value, sd, n);
+    TWG_CHECK_LAUNCH();
+    g_last_path = kPathStrided64;
+  }
+  return TWG_OK;
+}
+
 bool all_dense(const TwgIterDesc& d, int nt) {
   if (d.ndim > 1) return false;
   if (d.ndim == 1 && d.numel > 1)
@@ -209,6 +274,26 @@ extern "C" int twg_copy_strided(const TwgIterDesc* desc, int itemsize, const voi
   if (itemsize == 4)
     return twg_unary_f32(TWG_UNARY_COPY, desc, static_cast<const float*>(in), static_cast<float*>(out), stream);
   return dispatch_sized<1>(d, itemsize, in, nullptr, out, s);
+}
+
+extern "C" int twg_fill(const TwgIterDesc* desc, int itemsize, uint64_t pattern, void* out, void* stream) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  g_last_path = kPathNone;
+  if (int rc = check_desc(desc, 1)) return rc;
+  if (desc->numel == 0) return TWG_OK;
+  TWG_REQUIRE(out != nullptr, "twg_fill: null operand");
+  TWG_REQUIRE(itemsize == 1 || itemsize == 2 || itemsize == 4 || itemsize == 8,
+              "twg_fill: element size %d is not 1, 2, 4 or 8 bytes", itemsize);
+  TWG_REQUIRE(is_aligned(out, (size_t)itemsize), "twg_fill: the operand is not aligned to the element size %d", itemsize);
+  TwgIterDesc d = *desc;
+  d.ntensors = 1;
+  if (int rc = twg_iter_coalesce(&d)) return rc;
+  switch (itemsize) {
+    case 1: return launch_fill<uint8_t>(d, pattern, out, s);
+    case 2: return launch_fill<uint16_t>(d, pattern, out, s);
+    case 4: return launch_fill<uint32_t>(d, pattern, out, s);
+    default: return launch_fill<unsigned long long>(d, pattern, out, s);
+  }
 }
 
 extern "C" int twg_bitwise_and(const TwgIterDesc* desc, int itemsize, int is_bool, const void* a, const void* b,

@@ -69,6 +69,12 @@ struct MsShared {
 __device__ __forceinline__ u32 nonzero_bytes(u32 w) {
   return ((((w & 0x7f7f7f7fu) + 0x7f7f7f7fu) | w) >> 7) & 0x01010101u;
 }
+// four arbitrary bytes -> their "non-zero" flags in bits 28..31 (byte 0 in bit 28): bit 7 of every byte is
+// set as above, and the multiplier moves bits 7, 15, 23 and 31 to bits 28, 29, 30 and 31 (the partial
+// products land on distinct bits, so nothing carries)
+__device__ __forceinline__ u32 nonzero_nibble(u32 w) {
+  return ((((w & 0x7f7f7f7fu) + 0x7f7f7f7fu) | w) & 0x80808080u) * 0x00204081u;
+}
 // How the chunked kernel addresses its operands.
 constexpr int kMsDense = 0;    // src and mask dense
 constexpr int kMsRowMask = 1;  // src dense, one mask byte per row
@@ -132,13 +138,22 @@ __device__ __forceinline__ u32 mask_quad(const u8* mask, i64 e, i64 n, const Fas
 // four 0/1 bytes -> one nibble (the product has no colliding partial terms, so no carries)
 __device__ __forceinline__ u32 bytes_to_nibble(u32 w) { return ((w * 0x01020408u) >> 24) & 0xfu; }
 
+// Floats of a warp's staging buffer: one span (512) plus the at most three elements that wait for
+// the rest of their 16-byte vector.
+constexpr int kMsStageFloats = 516;
+
 template <int CH>
 struct MsDenseShared {
-  float stage[kMsRound];  // warp w stages into [w*512, (w+1)*512)
-  alignas(16) unsigned short cnt[CH][kMsWarps];
+  alignas(16) float stage[kMsWarps][kMsStageFloats];
+  alignas(16) unsigned short cnt[CH * kMsWarps];  // selected elements of span s (512 elements at chunk offset 512 s)
   u32 reduce[kMsWarps];
   i64 tile;
   i64 excl;
+};
+
+// A lane's sixteen elements of a span: element 32 i + lane, i = 0..15 (loaded only where needed).
+struct MsSpanRegs {
+  u32 v[16];
 };
 
 template <int CH, int MODE>
@@ -146,38 +161,43 @@ __global__ void __launch_bounds__(kMsThreads, 4)
     ms_dense_kernel(const float* src, const u8* mask, float* out, i64 n, i64 nchunks, u64* ticket, u64* desc,
                      i64* result, i64 poll_budget, FastDiv32 row_len, StridedDesc<2, u32> sd) {
   constexpr bool ROWMASK = MODE == kMsRowMask;
+  constexpr int kSpans = CH * kMsWarps;  // spans of 512 elements in a chunk
   __shared__ MsDenseShared<CH> sm;
   __shared__ u32 bits[CH * (kMsRound / 32)];  // the chunk's mask, one bit per element
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  i64 chunk = blockIdx.x;
-  if (ticket != nullptr) {
-    if (threadIdx.x == 0) sm.tile = (i64)atomicAdd(ticket, 1ull);
-    __syncthreads();
-    chunk = sm.tile;
-  }
+  if (threadIdx.x == 0) sm.tile = (i64)atomicAdd(ticket, 1ull);
+  __syncthreads();
+  const i64 chunk = sm.tile;
   if (chunk >= nchunks) return;
   const i64 chunk_base = chunk * (i64)(CH * kMsRound);
   const bool full_chunk = chunk_base + (i64)(CH * kMsRound) <= n;
 
-  // ---- phase A: mask -> bits, counts per (tile, warp span), chunk count ----
+  // ---- phase A: mask -> bits, count per span, chunk count ----
   u32 c = 0;
+  // In phase B warp w owns the CH consecutive spans [w CH, (w + 1) CH) of the chunk, i.e. one
+  // contiguous stretch of CH * 512 elements, so its output is one contiguous run.
+  const int span0 = warp * CH;
   if (MODE == kMsDense && full_chunk) {
+    // every warp reads the mask of its own stretch: it knows its bits and counts without waiting
+    // for anybody and can start fetching src before the CTA meets at the barrier
     unsigned short* bits16 = reinterpret_cast<unsigned short*>(bits);
+    const u8* mp = mask + chunk_base + (i64)span0 * 512 + lane * 16;
 #pragma unroll
     for (int i = 0; i < CH; ++i) {
-      uint4 q = ld_v4(mask + chunk_base + (i64)i * kMsRound + threadIdx.x * 16);
-      const u32 sixteen = bytes_to_nibble(nonzero_bytes(q.x)) | (bytes_to_nibble(nonzero_bytes(q.y)) << 4) |
-                          (bytes_to_nibble(nonzero_bytes(q.z)) << 8) | (bytes_to_nibble(nonzero_bytes(q.w)) << 12);
+      uint4 q = ld_v4(mp + i * 512);
+      const u32 sixteen = (nonzero_nibble(q.x) >> 28) | ((nonzero_nibble(q.y) >> 24) & 0xf0u) |
+                          ((nonzero_nibble(q.z) >> 20) & 0xf00u) | ((nonzero_nibble(q.w) >> 16) & 0xf000u);
       const u32 ci = __popc(sixteen);
       c += ci;
-      bits16[i * kMsThreads + threadIdx.x] = (unsigned short)sixteen;
-      const u32 span = __reduce_add_sync(0xffffffffu, ci);  // this warp's 512 bytes are exactly its span of tile i
-      if (lane == 0) sm.cnt[i][warp] = (unsigned short)span;
+      bits16[(span0 + i) * 32 + lane] = (unsigned short)sixteen;
+      const u32 span = __reduce_add_sync(0xffffffffu, ci);
+      if (lane == 0) sm.cnt[span0 + i] = (unsigned short)span;
     }
+    __syncwarp();
   } else if constexpr (MODE == kMsStrided) {
     // a warp takes whole spans; lane l looks at element 32 g + l of word g, so that neighbouring
     // lanes read neighbouring mask bytes, and a ballot is the word
-    for (int sidx = warp; sidx < CH * kMsWarps; sidx += kMsWarps) {
+    for (int sidx = warp; sidx < kSpans; sidx += kMsWarps) {
       u32 span_count = 0;
 #pragma unroll 4
       for (int k = 0; k < 16; ++k) {
@@ -194,12 +214,12 @@ __global__ void __launch_bounds__(kMsThreads, 4)
         span_count += __popc(word);
       }
       if (lane == 0) {
-        sm.cnt[sidx >> 3][sidx & 7] = (unsigned short)span_count;
+        sm.cnt[sidx] = (unsigned short)span_count;
         c += span_count;
       }
     }
   } else {
-    // one word of bits = 32 consecutive elements, 16 words = one warp span: half a warp per span
+    // one word of bits = 32 consecutive elements, 16 words = one span: half a warp per span
     const bool row_words = ROWMASK && full_chunk && (row_len.d % 32u) == 0u;
     for (int g = threadIdx.x; g < CH * (kMsRound / 32); g += kMsThreads) {
       u32 word = 0, cw = 0;
@@ -218,9 +238,49 @@ __global__ void __launch_bounds__(kMsThreads, 4)
       c += cw;
 #pragma unroll
       for (int o = 8; o > 0; o >>= 1) cw += __shfl_xor_sync(0xffffffffu, cw, o);
-      if ((lane & 15) == 0) sm.cnt[g >> 7][(g & 127) >> 4] = (unsigned short)cw;
+      if ((lane & 15) == 0) sm.cnt[g >> 4] = (unsigned short)cw;
     }
   }
+  // ---- phase B: every warp compacts its stretch of the chunk on its own ----
+  // Lane l owns elements 32 i + l (i = 0..15) of a span: a warp-wide access is one 128-byte run,
+  // word i of the span's mask bits is the selection bitmap of row i, and popc of its low bits is a
+  // lane's rank in the row - consecutive selected lanes get consecutive stage slots, so the
+  // staging stores are free of bank conflicts whatever the density.  Spans that select a quarter
+  // of their elements or more are loaded whole (nearly every sector is needed anyway); sparser
+  // ones load selected elements only, so untouched sectors are never fetched.
+  auto load_span = [&](MsSpanRegs& r, int s) {
+    const i64 e0 = chunk_base + (i64)s * 512 + lane;
+    if constexpr (MODE == kMsStrided) {
+      u32 os = 0, om, c0 = 0;
+      bool have = false;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        if ((bits[s * 16 + i] >> lane) & 1u) {  // set bits only exist below n
+          if (!have || c0 >= sd.shape[0].d) {
+            c0 = ms_offsets(sd, (u32)(e0 + i * 32), os, om);
+            have = true;
+          }
+          r.v[i] = __float_as_uint(__ldg(src + os));
+        }
+        if (have) {  // the next row lies 32 elements further along dimension 0 (or wraps: recomputed on use)
+          c0 += 32u;
+          os += 32u * sd.strides[0][0];
+        }
+      }
+    } else if (full_chunk && sm.cnt[s] >= 128u) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) r.v[i] = ld_b32(src + e0 + i * 32);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        if ((bits[s * 16 + i] >> lane) & 1u) r.v[i] = ld_b32(src + e0 + i * 32);  // 0 bits beyond n
+    }
+  };
+  // A warp that made its own bits (dense mode) starts fetching its first span right away: the
+  // loads are in flight across the barrier and the look-back below.
+  MsSpanRegs next;
+  const bool early = MODE == kMsDense && full_chunk;
+  if (early) load_span(next, span0);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
   if (lane == 0) sm.reduce[warp] = c;
@@ -229,7 +289,11 @@ __global__ void __launch_bounds__(kMsThreads, 4)
 #pragma unroll
   for (int w = 0; w < kMsWarps; ++w) chunk_total += sm.reduce[w];
   if (threadIdx.x == 0) lookback_publish(chunk, chunk_total, desc, poll_budget);
-  const int tiles_here = full_chunk ? CH : (int)((n - chunk_base + kMsRound - 1) / kMsRound);
+
+  // the warp's run starts `before` elements into the chunk's output
+  u32 before = 0;
+  for (int k = lane; k < span0; k += 32) before += sm.cnt[k];
+  before = __reduce_add_sync(0xffffffffu, before);
 
   // ---- phase B for sparse chunks (fewer than one element in sixteen selected) ----
   // Ranking, staging and quad loads cost the same whether anything is selected or not; here a
@@ -244,167 +308,117 @@ __global__ void __launch_bounds__(kMsThreads, 4)
       }
     }
     __syncthreads();
-    float* chunk_out = out + sm.excl;
-    u32 tile_off = 0;
-    for (int t = 0; t < tiles_here; ++t) {
-      const u32 mine = sm.cnt[t][warp];
-      u32 before = 0, tile_total = 0;  // selected by the spans in front of this one / by the whole tile
+    float* to_span = out + sm.excl + before;
+    for (int i = 0; i < CH; ++i) {
+      const int s = span0 + i;
+      const u32 mine = sm.cnt[s];
+      if (mine == 0u) continue;
+      const u32 word = bits[s * 16 + (lane >> 1)];
+      u32 half = (word >> ((lane & 1) * 16)) & 0xffffu;  // this lane's 16 consecutive elements
+      const u32 cnt = __popc(half);
+      u32 incl = cnt;
 #pragma unroll
-      for (int w = 0; w < kMsWarps; ++w) {
-        const u32 x = sm.cnt[t][w];
-        if (w < warp) before += x;
-        tile_total += x;
+      for (int o = 1; o < 32; o <<= 1) {
+        const u32 x = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += x;
       }
-      if (mine != 0u) {
-        const u32 word = bits[t * (kMsRound / 32) + warp * 16 + (lane >> 1)];
-        u32 half = (word >> ((lane & 1) * 16)) & 0xffffu;  // this lane's 16 consecutive elements
-        const u32 cnt = __popc(half);
-        u32 incl = cnt;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          const u32 x = __shfl_up_sync(0xffffffffu, incl, o);
-          if (lane >= o) incl += x;
-        }
-        const i64 first = chunk_base + (i64)t * kMsRound + (i64)warp * 512 + lane * 16;
-        float* to = chunk_out + tile_off + before + (incl - cnt);
-        u32 first_os = 0, first_c0 = 0;
+      const i64 first = chunk_base + (i64)s * 512 + lane * 16;
+      float* to = to_span + (incl - cnt);
+      u32 first_os = 0, first_c0 = 0;
+      if constexpr (MODE == kMsStrided) {
+        u32 om;
+        if (half != 0u) first_c0 = ms_offsets(sd, (u32)first, first_os, om);
+      }
+      while (half != 0u) {
+        const int bit = __ffs(half) - 1;
+        half &= half - 1u;
         if constexpr (MODE == kMsStrided) {
-          u32 om;
-          if (half != 0u) first_c0 = ms_offsets(sd, (u32)first, first_os, om);
-        }
-        while (half != 0u) {
-          const int bit = __ffs(half) - 1;
-          half &= half - 1u;
-          if constexpr (MODE == kMsStrided) {
-            u32 o = first_os + bit * sd.strides[0][0], om;
-            if (first_c0 + bit >= sd.shape[0].d) ms_offsets(sd, (u32)(first + bit), o, om);
-            *to++ = __uint_as_float(ld_b32(src + o));
-          } else {
-            *to++ = __uint_as_float(ld_b32(src + first + bit));
-          }
+          u32 o = first_os + bit * sd.strides[0][0], om;
+          if (first_c0 + bit >= sd.shape[0].d) ms_offsets(sd, (u32)(first + bit), o, om);
+          *to++ = __uint_as_float(ld_b32(src + o));
+        } else {
+          *to++ = __uint_as_float(ld_b32(src + first + bit));
         }
       }
-      tile_off += tile_total;
+      to_span += mine;
     }
     return;
   }
 
-  // ---- phase B: every warp compacts its span of every tile on its own ----
-  struct TileRegs {
-    u32 m[4];     // the four mask bits of this lane's quad in each sub-round
-    u32 v[4][4];  // its src values (loaded only where a bit is set)
-  };
-  auto load_tile = [&](TileRegs& r, int t) {
-    const i64 tb = chunk_base + (i64)t * kMsRound + (i64)warp * 512;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int q = warp * 128 + j * 32 + lane;
-      const i64 e = tb + (i64)(j * 32 + lane) * 4;
-      r.m[j] = (bits[t * (kMsRound / 32) + (q >> 3)] >> ((q & 7) * 4)) & 0xfu;  // 0 beyond n
-      if constexpr (MODE == kMsStrided) {
-        if (r.m[j] != 0u) {  // set bits only exist below n
-          u32 os0, om;
-          const u32 c0 = ms_offsets(sd, (u32)e, os0, om);
-          if (sd.strides[0][0] == 1u && c0 + 3 < sd.shape[0].d && ((reinterpret_cast<unsigned long long>(src + os0) & 15ull) == 0)) {
-            const uint4 x = ld_v4(src + os0);  // the quad is one aligned 16-byte piece of src
-            r.v[j][0] = x.x; r.v[j][1] = x.y; r.v[j][2] = x.z; r.v[j][3] = x.w;
-          } else {
-            // neighbouring elements share sectors: let L1 serve the repeats
-#pragma unroll
-            for (int b = 0; b < 4; ++b)
-              if ((r.m[j] >> b) & 1u) {
-                u32 o = os0 + b * sd.strides[0][0];
-                if (c0 + b >= sd.shape[0].d) ms_offsets(sd, (u32)(e + b), o, om);  // the quad runs into the next row
-                r.v[j][b] = __float_as_uint(__ldg(src + o));
-              }
-          }
-        }
-      } else if (r.m[j] != 0u) {
-        if (full_chunk || e + 3 < n) {
-          const uint4 x = ld_v4(src + e);
-          r.v[j][0] = x.x; r.v[j][1] = x.y; r.v[j][2] = x.z; r.v[j][3] = x.w;
-        } else {
-#pragma unroll
-          for (int b = 0; b < 4; ++b) r.v[j][b] = (e + b < n) ? ld_b32(src + e + b) : 0u;
-        }
-      }
+  if (!early) load_span(next, span0);  // in flight while warp 0 walks the look-back
+  if (warp == 0) {
+    const i64 excl = lookback_resolve(chunk, chunk_total, desc, result, poll_budget);
+    if (lane == 0) {
+      sm.excl = excl;
+      if (chunk == nchunks - 1) result[0] = excl + (i64)chunk_total;
     }
-  };
-  float* region = sm.stage + warp * 512;
-  u32 tile_off = 0;  // selected elements of the chunk's earlier tiles
-  auto compact_tile = [&](const TileRegs& r, int t) {
-    // where this warp's run starts inside the chunk: the table of phase A
-    const uint4 row = *reinterpret_cast<const uint4*>(sm.cnt[t]);
-    const u32 c01 = row.x, c23 = row.y, c45 = row.z, c67 = row.w;
-    const u32 pair[4] = {(c01 & 0xffffu) + (c01 >> 16), (c23 & 0xffffu) + (c23 >> 16), (c45 & 0xffffu) + (c45 >> 16),
-                         (c67 & 0xffffu) + (c67 >> 16)};
-    u32 warp_off = 0;
-#pragma unroll
-    for (int p = 0; p < 4; ++p)
-      if (2 * p + 1 < warp) warp_off += pair[p];
-    if (warp & 1) {
-      const u32 lo[4] = {c01 & 0xffffu, c23 & 0xffffu, c45 & 0xffffu, c67 & 0xffffu};
-      warp_off += lo[warp >> 1];
-    }
-    const u32 tile_total = pair[0] + pair[1] + pair[2] + pair[3];
-
-    // ranks inside the warp: per-sub-round counts packed into one word (each field <= 128)
-    const u32 cnt = __popc(r.m[0]) | (__popc(r.m[1]) << 8) | (__popc(r.m[2]) << 16) | (__popc(r.m[3]) << 24);
-    u32 incl = cnt;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const u32 x = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += x;
-    }
-    const u32 tot = __shfl_sync(0xffffffffu, incl, 31);
-    const u32 t0 = tot & 0xffu, t1 = (tot >> 8) & 0xffu, t2 = (tot >> 16) & 0xffu, t3 = tot >> 24;
-    const u32 excl_w = incl - cnt;
-    const u32 sub_base[4] = {0u, t0, t0 + t1, t0 + t1 + t2};
-    const u32 run = t0 + t1 + t2 + t3;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      if (r.m[j] != 0u) {
-        u32 pos = sub_base[j] + ((excl_w >> (8 * j)) & 0xffu);
-#pragma unroll
-        for (int b = 0; b < 4; ++b)
-          if ((r.m[j] >> b) & 1u) region[pos++] = __uint_as_float(r.v[j][b]);
-      }
-    }
-    if (t == 0) {
-      // the look-back as late as possible: tile 0 is staged, most predecessors have published
-      if (warp == 0) {
-        const i64 excl = lookback_resolve(chunk, chunk_total, desc, result, poll_budget);
-        if (lane == 0) {
-          sm.excl = excl;
-          if (chunk == nchunks - 1) result[0] = excl + (i64)chunk_total;
-        }
-      }
-      __syncthreads();
-    } else {
-      __syncwarp();
-    }
-    // this warp's run: 128-bit stores between the first and last 16-byte boundary
-    float* dst = out + sm.excl + tile_off + warp_off;
-    const u32 head = min(run, (u32)(((16u - (u32)(reinterpret_cast<unsigned long long>(dst) & 15ull)) & 15u) >> 2));
-    if ((u32)lane < head) dst[lane] = region[lane];
-    const u32 nvec = (run - head) >> 2;
-    float4* dst4 = reinterpret_cast<float4*>(dst + head);
-    for (u32 i = lane; i < nvec; i += 32) {
-      const float* s4 = region + head + 4 * i;
-      dst4[i] = make_float4(s4[0], s4[1], s4[2], s4[3]);
-    }
-    const u32 tail0 = head + 4 * nvec;
-    if (tail0 + lane < run) dst[tail0 + lane] = region[tail0 + lane];
-    tile_off += tile_total;
-    __syncwarp();  // the region is rewritten by the next tile
-  };
-  TileRegs next;
-  load_tile(next, 0);
-  for (int t = 0; t < tiles_here; ++t) {
-    const TileRegs cur = next;
-    if (t + 1 < tiles_here) load_tile(next, t + 1);  // in flight while this tile is ranked and written out
-    compact_tile(cur, t);
   }
+  __syncthreads();
+
+  // Output positions are counted in a "virtual" index v = a0 + position inside the chunk's output,
+  // where a0 is the misalignment (in elements) of the chunk's first output element: out_v + v is
+  // 16-byte aligned exactly when v is a multiple of 4.  A staged element with virtual index v sits
+  // at stage[v - vbase] (vbase a multiple of 4), so aligned vectors of the output are aligned
+  // vectors of the stage and go out as one 128-bit shared load and one 128-bit store.  Elements
+  // below vf are already in global memory; after every span the complete vectors are written and
+  // the at most three elements left over move to the front of the stage.
+  float* const chunk_out = out + sm.excl;
+  const u32 a0 = (u32)(reinterpret_cast<unsigned long long>(chunk_out) >> 2) & 3u;
+  float* const out_v = chunk_out - a0;
+  float* const stage = sm.stage[warp];
+  const u32 below = (1u << lane) - 1u;
+  u32 v = a0 + before, vf = v, vbase = v & ~3u;
+  for (int i = 0; i < CH; ++i) {
+    const int s = span0 + i;
+    const MsSpanRegs cur = next;
+    if (i + 1 < CH) load_span(next, s + 1);  // in flight while this span is ranked and written out
+    const u32 run = sm.cnt[s];
+    if (run == 0u) continue;
+    if (run == 512u) {
+      // everything selected: after the few elements still waiting in the stage the span is a straight copy
+      if ((u32)lane < v - vf) out_v[vf + lane] = stage[vf - vbase + lane];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) out_v[v + k * 32 + lane] = __uint_as_float(cur.v[k]);
+      v += 512u;
+      vf = v;
+      vbase = v & ~3u;
+      __syncwarp();
+      continue;
+    }
+    u32 pos = v - vbase;  // stage index of the span's first selected element
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const u32 word = bits[s * 16 + k];
+      if ((word >> lane) & 1u) stage[pos + __popc(word & below)] = __uint_as_float(cur.v[k]);
+      pos += __popc(word);
+    }
+    const u32 v_end = v + run;
+    __syncwarp();
+    if (vf & 3u) {  // the run starts inside a vector that earlier output shares: scalars up to the boundary
+      const u32 head_end = min((vf + 3u) & ~3u, v_end);
+      if ((u32)lane < head_end - vf) out_v[vf + lane] = stage[vf - vbase + lane];
+      vf = head_end;
+    }
+    if ((vf & 3u) == 0u) {
+      const u32 nvec = (v_end - vf) >> 2;
+      const float4* from = reinterpret_cast<const float4*>(stage + (vf - vbase));
+      float4* to4 = reinterpret_cast<float4*>(out_v + vf);
+      for (u32 k = lane; k < nvec; k += 32) to4[k] = from[k];
+      vf += 4u * nvec;
+      if (vf != vbase) {
+        const u32 rem = v_end - vf;  // 0..3 elements wait for the rest of their vector
+        __syncwarp();
+        float x = 0.f;
+        if ((u32)lane < rem) x = stage[vf - vbase + lane];
+        __syncwarp();
+        if ((u32)lane < rem) stage[lane] = x;
+        vbase = vf;
+      }
+    }
+    v = v_end;
+    __syncwarp();
+  }
+  if ((u32)lane < v - vf) out_v[vf + lane] = stage[vf - vbase + lane];  // the stretch's last partial vector
 }
 
 // ------------------------------------------------------------------------------------------
@@ -473,14 +487,8 @@ __global__ void __launch_bounds__(kMsThreads)
 
 // Tiles per dense chunk: the largest power of two up to 32 that still leaves about four waves
 // of chunks on the device, so that large tensors amortise the look-back over long chunks and small
-// ones still fill every SM.  TWG_MS_CHUNK (1..32, power of two) overrides it for experiments.
+// ones still fill every SM.
 static int dense_chunk_tiles(int64_t n) {
-  static const int forced = [] {
-    const char* env = getenv("TWG_MS_CHUNK");
-    const int r = env ? atoi(env) : 0;
-    return (r == 1 || r == 2 || r == 4 || r == 8 || r == 16 || r == 32) ? r : 0;
-  }();
-  if (forced) return forced;
   const int64_t tiles = (n + kMsRound - 1) / kMsRound;
   const int64_t want_chunks = 4ll * 4 * sm_count();
   int ch = 32;
@@ -489,17 +497,6 @@ static int dense_chunk_tiles(int64_t n) {
 }
 
 long long ms_poll_budget() { return g_poll_budget.load(); }
-
-// Tile order.  Default: tickets from a global counter (forward progress does not depend on the
-// order in which the hardware starts CTAs).  TWG_MS_ORDER=blockidx uses blockIdx.x instead, for
-// measuring what the ticket costs.
-bool ms_use_ticket() {
-  static const bool v = [] {
-    const char* env = getenv("TWG_MS_ORDER");
-    return !(env && std::string(env) == "blockidx");
-  }();
-  return v;
-}
 
 template <int MODE>
 static void launch_dense(int chunk_tiles, unsigned nchunks, cudaStream_t s, const float* src, const u8* mask, float* out,
@@ -552,7 +549,7 @@ extern "C" int twg_masked_select_f32(const TwgIterDesc* desc, const float* src, 
   TwgIterDesc d = *desc;
   d.ntensors = 2;
   if (int rc = twg_iter_coalesce(&d)) return rc;
-  u64* ticket = ms_use_ticket() ? static_cast<u64*>(workspace) : nullptr;
+  u64* ticket = static_cast<u64*>(workspace);
   u64* tdesc = reinterpret_cast<u64*>(static_cast<char*>(workspace) + kMsHeaderBytes);
   i64* result = reinterpret_cast<i64*>(result_dev);
   const long long budget = g_poll_budget.load();

@@ -125,7 +125,8 @@ bool plan_tile(const TwgIterDesc& d, int nt, int tile_edge, PwPlan* plan) {
     plan->sb0 = (plan->tiles0 + kTileSuper - 1) / kTileSuper;
     plan->ntiles = plan->sb0 * ((plan->tiles1 + kTileSuper - 1) / kTileSuper) * kTileSuper * kTileSuper;
   }
-  plan->grid = (unsigned)std::min<int64_t>(plan->ntiles, 0x7fffffff);
+  if (plan->ntiles > 0x7fffffff) return false;  // the kernels index tiles with 32 bits
+  plan->grid = (unsigned)plan->ntiles;
   return true;
 }
 
@@ -647,6 +648,9 @@ extern "C" int twg_trim(void* ptr, size_t new_nbytes) {
   if (keep >= b->size) return TWG_OK;
   const size_t remaining = b->size - keep;
   if ((b->small && remaining < kRound) || (!b->small && remaining <= kSmallLimit)) return TWG_OK;
+  // A block that other streams also use (twg_record_stream) keeps its tail: those streams may
+  // still touch it, and only twg_free orders a block's reuse after them.
+  if (!b->extra_streams.empty()) return TWG_OK;
   Pool& p = g_pools[b->device];
   Block* rest = new Block();
   rest->device = b->device;

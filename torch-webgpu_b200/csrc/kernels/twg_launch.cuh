@@ -64,6 +64,8 @@ void fill_tile_desc(const PwPlan& p, TileDesc<NT>* td, void* const* ptrs = nullp
   td->tiles0 = p.tiles0;
   td->tiles1 = p.tiles1;
   td->sb0 = p.sb0;
+  td->sb0_div.d = (uint32_t)p.sb0;
+  make_fastdiv(td->sb0_div.d, &td->sb0_div.m, &td->sb0_div.s);
   td->ntiles = p.ntiles;
   for (int t = 0; t < NT; ++t) { td->s0[t] = p.d.strides[t][0]; td->s1[t] = p.d.strides[t][1]; }
   td->dim1_mask = p.dim1_mask;
@@ -74,6 +76,13 @@ void fill_tile_desc(const PwPlan& p, TileDesc<NT>* td, void* const* ptrs = nullp
     vec = dense == 1 && other % 4 == 0 && (reinterpret_cast<uintptr_t>(ptrs[t]) & 15u) == 0;
   }
   td->vec = vec ? 1u : 0u;
+}
+// Grid of a tile launch: one CTA per slot, except for the pipelined kernel (one f32 input, 128-bit
+// capable layout), whose CTAs stay resident and walk the slots with a grid stride.
+inline unsigned tile_grid(const PwSig& sig, bool vec, unsigned slots) {
+  if (sig.nin == 1 && sig.in_byte_mask == 0u && sig.out_byte_mask == 0u && vec)
+    return std::min<unsigned>(slots, (unsigned)(sm_count() * kTilePersistCtas));
+  return slots;
 }
 template <int NT>
 void fill_strided_desc(const TwgIterDesc& d, StridedDesc<NT, u32>* sd) {
@@ -109,7 +118,7 @@ int launch_pointwise(const F& f, const TwgIterDesc* desc, void* const* ptrs_in, 
     case kPathTile: {
       TileDesc<NT> td;
       fill_tile_desc<NT>(plan, &td, ptrs_in, F::kInByteMask == 0u && F::kOutByteMask == 0u);
-      pw_tile_kernel<F><<<plan.grid, dim3(kTileX, kTileRows), 0, stream>>>(ptrs, f, td);
+      pw_tile_kernel<F><<<tile_grid(sig_of<F>(), td.vec != 0u, plan.grid), dim3(kTileX, kPwRows), 0, stream>>>(ptrs, f, td);
       break;
     }
     case kPathStrided32: {

@@ -342,8 +342,11 @@ __device__ __forceinline__ void pw_strided_body(const PwPtrs<PwTraits<F>::NT>& p
 // ------------------------------------------------------------------------------------------
 // 2-D permuted path (a true transpose: some operands are dense along dimension 0, the others
 // along dimension 1).  A CTA of 32x8 threads owns a 64x64 tile, 16 elements per thread, so that a
-// CTA has 16 KB per operand in flight.  In registers a thread holds the tile in "dimension-0
-// order": elements (tx + 32a, ty + 8r).  Operands dense along dimension 0 are accessed directly
+// CTA has 16 KB per operand in flight.  (Measured: 512 threads with 8 elements each - more warps,
+// fewer bytes in flight per SM - is slower for every functor: 0.92 / 0.76 / 0.70 of the copy peak
+// for relu / silu / gelu on a 16384^2 transpose against 0.97 / 0.83 / 0.76; what this shape needs
+// is bytes in flight, not warps.)  In registers a thread holds the tile in "dimension-0 order":
+// elements (tx + 32a, ty + 8r).  Operands dense along dimension 0 are accessed directly
 // in that order; operands dense along dimension 1 are accessed with tx running along dimension 1
 // and pass through one padded shared-memory tile (row pitch 65: both the row-wise writes and
 // the column-wise reads are conflict-free), so every global access is a 128-byte run.
@@ -352,10 +355,13 @@ __device__ __forceinline__ void pw_strided_body(const PwPtrs<PwTraits<F>::NT>& p
 constexpr int kTile = 32;      // tile edge of the element-size-generic kernels (copy.cu)
 constexpr int kPwTile = 64;    // tile edge of the functor kernels
 constexpr int kTileX = 32;
-constexpr int kTileRows = 8;
+constexpr int kTileRows = 8;                  // thread rows of the element-size-generic kernels (copy.cu)
+constexpr int kPwRows = 8;                    // thread rows of the functor kernels: 32 x 8 = 256 threads
 constexpr int kTileXR = kPwTile / kTileX;     // 2
-constexpr int kTileYR = kPwTile / kTileRows;  // 8
+constexpr int kTileYR = kPwTile / kPwRows;    // 8
 constexpr int kTileElems = kTileXR * kTileYR; // 16 per thread
+constexpr int kTileVecRows = kTileX * kPwRows / 16;  // rows one pass of the 128-bit path covers (16 threads per row)
+constexpr int kTilePersistCtas = 4;           // CTAs per SM of the pipelined one-input tile kernel
 constexpr int kTileSuper = 8;                 // tiles per super-block edge
 
 template <int NT>
@@ -363,6 +369,7 @@ struct TileDesc {
   i64 shape0, shape1;
   i64 tiles0, tiles1;  // ceil(shape / tile edge) along dimension 0 / 1
   i64 sb0;             // super-blocks along dimension 0 (functor kernels)
+  FastDiv32 sb0_div;   // the same as a multiply-shift divisor
   i64 ntiles;          // CTAs' worth of work: tiles, or padded super-block slots
   i64 s0[NT], s1[NT];
   u32 dim1_mask;
@@ -386,32 +393,32 @@ __device__ __forceinline__ void tile_load_inputs(const PwPtrs<PwTraits<F>::NT>& 
     if ((d.dim1_mask >> T) & 1u) {
       // tx runs along dimension 1: element (i0 = t0 + ty + 8r, i1 = t1 + tx + 32a)
       const i64 base = (t0 + ty) * s0 + (t1 + tx) * s1;
-      const i64 step_r = kTileRows * s0, step_a = kTileX * s1;
+      const i64 step_r = kPwRows * s0, step_a = kTileX * s1;
       __syncthreads();  // the tile is free (previous operand gathered, previous tile stored)
 #pragma unroll
       for (int a = 0; a < kTileXR; ++a)
 #pragma unroll
         for (int r = 0; r < kTileYR; ++r) {
           u32 x = 0;
-          if (INTERIOR || (t0 + ty + r * kTileRows < d.shape0 && t1 + tx + a * kTileX < d.shape1))
+          if (INTERIOR || (t0 + ty + r * kPwRows < d.shape0 && t1 + tx + a * kTileX < d.shape1))
             x = load_elem<BYTE>(ptrs.p[T], base + r * step_r + a * step_a);
-          smem[ty + r * kTileRows][tx + a * kTileX] = x;
+          smem[ty + r * kPwRows][tx + a * kTileX] = x;
         }
       __syncthreads();
 #pragma unroll
       for (int a = 0; a < kTileXR; ++a)
 #pragma unroll
-        for (int r = 0; r < kTileYR; ++r) v[a * kTileYR + r][K] = smem[tx + a * kTileX][ty + r * kTileRows];
+        for (int r = 0; r < kTileYR; ++r) v[a * kTileYR + r][K] = smem[tx + a * kTileX][ty + r * kPwRows];
     } else {
       // tx runs along dimension 0: element (i0 = t0 + tx + 32a, i1 = t1 + ty + 8r)
       const i64 base = (t0 + tx) * s0 + (t1 + ty) * s1;
-      const i64 step_a = kTileX * s0, step_r = kTileRows * s1;
+      const i64 step_a = kTileX * s0, step_r = kPwRows * s1;
 #pragma unroll
       for (int a = 0; a < kTileXR; ++a)
 #pragma unroll
         for (int r = 0; r < kTileYR; ++r) {
           u32 x = 0;
-          if (INTERIOR || (t0 + tx + a * kTileX < d.shape0 && t1 + ty + r * kTileRows < d.shape1))
+          if (INTERIOR || (t0 + tx + a * kTileX < d.shape0 && t1 + ty + r * kPwRows < d.shape1))
             x = load_elem<BYTE>(ptrs.p[T], base + a * step_a + r * step_r);
           v[a * kTileYR + r][K] = x;
         }
@@ -432,27 +439,27 @@ __device__ __forceinline__ void tile_store_outputs(const PwPtrs<PwTraits<F>::NT>
     const i64 s0 = d.s0[K], s1 = d.s1[K];
     if ((d.dim1_mask >> K) & 1u) {
       const i64 base = (t0 + ty) * s0 + (t1 + tx) * s1;
-      const i64 step_r = kTileRows * s0, step_a = kTileX * s1;
+      const i64 step_r = kPwRows * s0, step_a = kTileX * s1;
       __syncthreads();  // previous use of the tile is finished
 #pragma unroll
       for (int a = 0; a < kTileXR; ++a)
 #pragma unroll
-        for (int r = 0; r < kTileYR; ++r) smem[tx + a * kTileX][ty + r * kTileRows] = v[a * kTileYR + r][K];
+        for (int r = 0; r < kTileYR; ++r) smem[tx + a * kTileX][ty + r * kPwRows] = v[a * kTileYR + r][K];
       __syncthreads();
 #pragma unroll
       for (int a = 0; a < kTileXR; ++a)
 #pragma unroll
         for (int r = 0; r < kTileYR; ++r)
-          if (INTERIOR || (t0 + ty + r * kTileRows < d.shape0 && t1 + tx + a * kTileX < d.shape1))
-            store_elem<BYTE>(ptrs.p[K], base + r * step_r + a * step_a, smem[ty + r * kTileRows][tx + a * kTileX]);
+          if (INTERIOR || (t0 + ty + r * kPwRows < d.shape0 && t1 + tx + a * kTileX < d.shape1))
+            store_elem<BYTE>(ptrs.p[K], base + r * step_r + a * step_a, smem[ty + r * kPwRows][tx + a * kTileX]);
     } else {
       const i64 base = (t0 + tx) * s0 + (t1 + ty) * s1;
-      const i64 step_a = kTileX * s0, step_r = kTileRows * s1;
+      const i64 step_a = kTileX * s0, step_r = kPwRows * s1;
 #pragma unroll
       for (int a = 0; a < kTileXR; ++a)
 #pragma unroll
         for (int r = 0; r < kTileYR; ++r)
-          if (INTERIOR || (t0 + tx + a * kTileX < d.shape0 && t1 + ty + r * kTileRows < d.shape1))
+          if (INTERIOR || (t0 + tx + a * kTileX < d.shape0 && t1 + ty + r * kPwRows < d.shape1))
             store_elem<BYTE>(ptrs.p[K], base + a * step_a + r * step_r, v[a * kTileYR + r][K]);
     }
     tile_store_outputs<F, INTERIOR, K + 1>(ptrs, d, t0, t1, smem, v);
@@ -477,6 +484,80 @@ __device__ __forceinline__ void pw_tile_one(const PwPtrs<PwTraits<F>::NT>& ptrs,
 // along dimension 1 - thread (vx, vy) takes (i1 = 4 vx .. 4 vx + 3, i0 = vy + 16 r) - and turned
 // through a 64x64 shared tile whose 16-byte chunks are XOR-swizzled with (i0 >> 2), which makes
 // both the float4 row accesses and the scalar column accesses conflict-free without padding.
+constexpr int kTileVecR = kTileElems / 4;  // float4 per thread and operand
+
+// The float4 of operand t that thread (vx, vy) touches in pass r lies at base + r * step.
+template <int NT>
+__device__ __forceinline__ void tile_vec_address(const TileDesc<NT>& d, int t, i64 t0, i64 t1, int vx, int vy, i64& base,
+                                                 i64& step) {
+  if ((d.dim1_mask >> t) & 1u) {
+    base = (t0 + vy) * d.s0[t] + (t1 + 4 * vx);
+    step = kTileVecRows * d.s0[t];
+  } else {
+    base = (t0 + 4 * vx) + (t1 + vy) * d.s1[t];
+    step = kTileVecRows * d.s1[t];
+  }
+}
+// Raw float4 of an input tile -> the thread's 16 elements (through the shared tile if the operand
+// is dense along dimension 1).
+template <int NS>
+__device__ __forceinline__ void tile_vec_unpack(const uint4 (&q)[kTileVecR], bool along1, int vx, int vy, u32* smem,
+                                                u32 (&vin)[kTileElems][NS], int k) {
+  if (along1) {
+    __syncthreads();  // the tile is free (previous operand gathered, previous tile stored)
+#pragma unroll
+    for (int r = 0; r < kTileVecR; ++r) {
+      const int i0 = vy + kTileVecRows * r;
+      *reinterpret_cast<uint4*>(smem + i0 * kPwTile + ((vx ^ ((i0 >> 2) & 15)) << 2)) = q[r];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < kTileVecR; ++r) {
+      const int i1 = vy + kTileVecRows * r;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)  // row i0 = 4 vx + c, whose swizzle key is vx
+        vin[r * 4 + c][k] = smem[(4 * vx + c) * kPwTile + ((((i1 >> 2) ^ vx) & 15) << 2) + (i1 & 3)];
+    }
+  } else {
+#pragma unroll
+    for (int r = 0; r < kTileVecR; ++r) {
+      vin[r * 4 + 0][k] = q[r].x; vin[r * 4 + 1][k] = q[r].y; vin[r * 4 + 2][k] = q[r].z; vin[r * 4 + 3][k] = q[r].w;
+    }
+  }
+}
+template <class F>
+__device__ __forceinline__ void tile_vec_store(const PwPtrs<PwTraits<F>::NT>& ptrs, const TileDesc<PwTraits<F>::NT>& d,
+                                               i64 t0, i64 t1, int vx, int vy, u32* smem,
+                                               const u32 (&vout)[kTileElems][F::NOUT]) {
+#pragma unroll
+  for (int k = 0; k < F::NOUT; ++k) {
+    u32* p = static_cast<u32*>(ptrs.p[k]);
+    i64 base, step;
+    tile_vec_address(d, k, t0, t1, vx, vy, base, step);
+    if ((d.dim1_mask >> k) & 1u) {
+      __syncthreads();  // previous use of the tile is finished
+#pragma unroll
+      for (int r = 0; r < kTileVecR; ++r) {
+        const int i1 = vy + kTileVecRows * r;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          smem[(4 * vx + c) * kPwTile + ((((i1 >> 2) ^ vx) & 15) << 2) + (i1 & 3)] = vout[r * 4 + c][k];
+      }
+      __syncthreads();
+#pragma unroll
+      for (int r = 0; r < kTileVecR; ++r) {
+        const int i0 = vy + kTileVecRows * r;
+        const uint4 q = *reinterpret_cast<const uint4*>(smem + i0 * kPwTile + ((vx ^ ((i0 >> 2) & 15)) << 2));
+        st_v4(p + base + r * step, q);
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < kTileVecR; ++r)
+        st_v4(p + base + r * step, make_uint4(vout[r * 4 + 0][k], vout[r * 4 + 1][k], vout[r * 4 + 2][k], vout[r * 4 + 3][k]));
+    }
+  }
+}
+
 template <class F>
 __device__ __forceinline__ void pw_tile_one_vec(const PwPtrs<PwTraits<F>::NT>& ptrs, const F& f,
                                                 const TileDesc<PwTraits<F>::NT>& d, i64 t0, i64 t1, u32* smem) {
@@ -488,77 +569,242 @@ __device__ __forceinline__ void pw_tile_one_vec(const PwPtrs<PwTraits<F>::NT>& p
   for (int k = 0; k < F::NIN; ++k) {
     const int t = F::NOUT + k;
     const u32* p = static_cast<const u32*>(ptrs.p[t]);
-    if ((d.dim1_mask >> t) & 1u) {
-      __syncthreads();  // the tile is free (previous operand gathered, previous tile stored)
+    i64 base, step;
+    tile_vec_address(d, t, t0, t1, vx, vy, base, step);
+    uint4 q[kTileVecR];
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const int i0 = vy + 16 * r;
-        const uint4 q = ld_v4(p + (t0 + i0) * d.s0[t] + (t1 + 4 * vx));
-        *reinterpret_cast<uint4*>(smem + i0 * kPwTile + ((vx ^ ((i0 >> 2) & 15)) << 2)) = q;
-      }
-      __syncthreads();
-#pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const int i1 = vy + 16 * r;
-#pragma unroll
-        for (int c = 0; c < 4; ++c)  // row i0 = 4 vx + c, whose swizzle key is vx
-          vin[r * 4 + c][k] = smem[(4 * vx + c) * kPwTile + ((((i1 >> 2) ^ vx) & 15) << 2) + (i1 & 3)];
-      }
-    } else {
-#pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const uint4 q = ld_v4(p + (t0 + 4 * vx) + (t1 + vy + 16 * r) * d.s1[t]);
-        vin[r * 4 + 0][k] = q.x; vin[r * 4 + 1][k] = q.y; vin[r * 4 + 2][k] = q.z; vin[r * 4 + 3][k] = q.w;
-      }
-    }
+    for (int r = 0; r < kTileVecR; ++r) q[r] = ld_v4(p + base + r * step);
+    tile_vec_unpack<NS>(q, (d.dim1_mask >> t) & 1u, vx, vy, smem, vin, k);
   }
 #pragma unroll
   for (int e = 0; e < kTileElems; ++e) f(vin[e], vout[e]);
+  tile_vec_store<F>(ptrs, d, t0, t1, vx, vy, smem, vout);
+}
+
+// Tile coordinates of a slot.  Tiles are walked in super-blocks of 8x8, so that the CTAs running
+// side by side touch neighbouring pieces of the rows they share along dimension 0 and dimension 1
+// alike.  Slots fit 32 bits (the planner refuses more), so the coordinates come from shifts and
+// one multiply-shift division.  Returns 0 for a padding slot, 1 for a tile that lies wholly inside
+// the tensor, 2 for an edge tile.
+template <int NT>
+__device__ __forceinline__ int tile_coords(const TileDesc<NT>& d, u32 slot, i64& t0, i64& t1) {
+  static_assert(kTileSuper == 8, "the shifts below assume 8x8 super-blocks");
+  const u32 sb = slot >> 6, within = slot & 63u;
+  const u32 sb_hi = d.sb0_div.div(sb);
+  const i64 b0 = (i64)(sb - sb_hi * d.sb0_div.d) * kTileSuper + (within & 7u);
+  const i64 b1 = (i64)sb_hi * kTileSuper + (within >> 3);
+  if (b0 >= d.tiles0 || b1 >= d.tiles1) return 0;
+  t0 = b0 * kPwTile;
+  t1 = b1 * kPwTile;
+  return (t0 + kPwTile <= d.shape0 && t1 + kPwTile <= d.shape1) ? 1 : 2;
+}
+
+// One-input functors on 128-bit-capable layouts: a CTA walks several tiles and issues the global
+// loads of its next tile before it computes and stores the current one, so a tile's worth of
+// loads is in flight per CTA at all times - also while the transcendental functors (silu, gelu)
+// keep the warps busy.  Launched with kTilePersistCtas CTAs per SM.
+template <class F>
+__device__ __forceinline__ void pw_tile_pipelined(const PwPtrs<PwTraits<F>::NT>& ptrs, const F& f,
+                                                  const TileDesc<PwTraits<F>::NT>& d, PwTileSmem smem2d) {
+  static_assert(F::NIN == 1, "one input");
+  constexpr int T = F::NOUT;  // operand index of the input
+  u32* smem = &smem2d[0][0];
+  const int lin = threadIdx.y * kTileX + threadIdx.x;
+  const int vx = lin & 15, vy = lin >> 4;
+  const u32* p = static_cast<const u32*>(ptrs.p[T]);
+  const bool along1 = (d.dim1_mask >> T) & 1u;
+  const u32 nslots = (u32)d.ntiles;
+  uint4 q[kTileVecR];
+  auto prefetch = [&](i64 t0, i64 t1) {
+    i64 base, step;
+    tile_vec_address(d, T, t0, t1, vx, vy, base, step);
 #pragma unroll
-  for (int k = 0; k < F::NOUT; ++k) {
-    u32* p = static_cast<u32*>(ptrs.p[k]);
-    if ((d.dim1_mask >> k) & 1u) {
-      __syncthreads();  // previous use of the tile is finished
+    for (int r = 0; r < kTileVecR; ++r) q[r] = ld_v4(p + base + r * step);
+  };
+  u32 slot = blockIdx.x;
+  i64 t0 = 0, t1 = 0;
+  int kind = slot < nslots ? tile_coords(d, slot, t0, t1) : 0;
+  if (kind == 1) prefetch(t0, t1);
+  while (slot < nslots) {
+    const u32 nslot = slot + gridDim.x;
+    i64 n0 = 0, n1 = 0;
+    const int nkind = nslot < nslots ? tile_coords(d, nslot, n0, n1) : 0;
+    if (kind == 1) {
+      u32 vin[kTileElems][1], vout[kTileElems][F::NOUT];
+      tile_vec_unpack<1>(q, along1, vx, vy, smem, vin, 0);
+      if (nkind == 1) prefetch(n0, n1);  // in flight while this tile is computed and stored
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const int i1 = vy + 16 * r;
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-          smem[(4 * vx + c) * kPwTile + ((((i1 >> 2) ^ vx) & 15) << 2) + (i1 & 3)] = vout[r * 4 + c][k];
-      }
-      __syncthreads();
-#pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        const int i0 = vy + 16 * r;
-        const uint4 q = *reinterpret_cast<const uint4*>(smem + i0 * kPwTile + ((vx ^ ((i0 >> 2) & 15)) << 2));
-        st_v4(p + (t0 + i0) * d.s0[k] + (t1 + 4 * vx), q);
-      }
+      for (int e = 0; e < kTileElems; ++e) f(vin[e], vout[e]);
+      tile_vec_store<F>(ptrs, d, t0, t1, vx, vy, smem, vout);
     } else {
-#pragma unroll
-      for (int r = 0; r < 4; ++r)
-        st_v4(p + (t0 + 4 * vx) + (t1 + vy + 16 * r) * d.s1[k],
-              make_uint4(vout[r * 4 + 0][k], vout[r * 4 + 1][k], vout[r * 4 + 2][k], vout[r * 4 + 3][k]));
+      if (kind == 2) pw_tile_one<F, false>(ptrs, f, d, t0, t1, smem2d);
+      if (nkind == 1) prefetch(n0, n1);
     }
+    slot = nslot;
+    kind = nkind;
+    t0 = n0;
+    t1 = n1;
   }
 }
+
+// ------------------------------------------------------------------------------------------
+// One f32 input that is dense along dimension 1, outputs dense along dimension 0 (y = f(x.t())):
+// the input tile has to pass through shared memory anyway, so it is brought there with
+// asynchronous 16-byte copies (cp.async) into a ring of three 16 KB stages.  While a CTA computes
+// and stores tile j, the copies of tiles j + 1 and j + 2 are in flight and occupy no registers;
+// four such CTAs keep 128 KB of loads in flight per SM whatever the functor costs.
+// ------------------------------------------------------------------------------------------
+constexpr int kTileStages = 3;
+constexpr int kTileStageWords = kPwTile * kPwTile;
+
+__device__ __forceinline__ void cp_async_16(u32* smem_dst, const void* gmem_src) {
+  const u32 dst = (u32)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Edge tile without shared memory: every element on its own, bounds-checked (tiles on the rim of
+// the tensor are few; the async kernel's stages are busy with other tiles' copies meanwhile).
+template <class F>
+__device__ __forceinline__ void tile_edge_direct(const PwPtrs<PwTraits<F>::NT>& ptrs, const F& f,
+                                                 const TileDesc<PwTraits<F>::NT>& d, i64 t0, i64 t1) {
+  constexpr int NT = PwTraits<F>::NT;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+#pragma unroll
+  for (int a = 0; a < kTileXR; ++a)
+#pragma unroll
+    for (int r = 0; r < kTileYR; ++r) {
+      const i64 i0 = t0 + tx + a * kTileX, i1 = t1 + ty + r * kPwRows;
+      if (i0 < d.shape0 && i1 < d.shape1) {
+        i64 off[NT];
+#pragma unroll
+        for (int t = 0; t < NT; ++t) off[t] = i0 * d.s0[t] + i1 * d.s1[t];
+        u32 in[F::NIN > 0 ? F::NIN : 1], out[F::NOUT];
+        load_inputs_elem<F>(ptrs, off, in);
+        f(in, out);
+        store_outputs_elem<F>(ptrs, off, out);
+      }
+    }
+}
+
+template <class F>
+__device__ __forceinline__ void pw_tile_async(const PwPtrs<PwTraits<F>::NT>& ptrs, const F& f,
+                                              const TileDesc<PwTraits<F>::NT>& d, u32* smem) {
+  static_assert(F::NIN == 1, "one input");
+  constexpr int T = F::NOUT;  // operand index of the input
+  const int lin = threadIdx.y * kTileX + threadIdx.x;
+  // copy phase: thread (cx, cy) copies the 16-byte piece cx of rows cy + 16 r
+  const int cx = lin & 15, cy = lin >> 4;
+  // compute phase: thread (vx, vy) holds elements (i0 = 4 vx + c, i1 = vy + 16 r).  Inside a warp vx
+  // takes 8 consecutive values and vy 4 consecutive ones, so the 32 lanes read 8 different
+  // (swizzled) 16-byte pieces times 4 different words of a piece: every bank once.
+  const int lane = lin & 31, wrp = lin >> 5;
+  const int vx = (lane & 7) + 8 * (wrp & 1), vy = (lane >> 3) + 4 * (wrp >> 1);
+  const u32* p = static_cast<const u32*>(ptrs.p[T]);
+  const u32 nslots = (u32)d.ntiles;
+  // per-thread constants of the addresses: a tile at (t0, t1) adds t0 * s0 + t1 (input) or
+  // t0 + t1 * s1 (outputs)
+  const i64 in_s0 = d.s0[T];
+  const i64 in_base = cy * in_s0 + 4 * cx, in_step = kTileVecRows * in_s0;
+  u32 rd[kTileVecR];  // word index of the thread's element (c = 0) of pass r inside a stage
+#pragma unroll
+  for (int r = 0; r < kTileVecR; ++r) {
+    const int i1 = vy + kTileVecRows * r;
+    rd[r] = (u32)((4 * vx) * kPwTile + ((((i1 >> 2) ^ vx) & 15) << 2) + (i1 & 3));
+  }
+  u32 wr[kTileVecR];  // word index of the 16-byte piece the thread copies in pass r
+#pragma unroll
+  for (int r = 0; r < kTileVecR; ++r) {
+    const int i0 = cy + kTileVecRows * r;
+    wr[r] = (u32)(i0 * kPwTile + ((cx ^ ((i0 >> 2) & 15)) << 2));
+  }
+  // The coordinates of a slot are worked out once, when its copies are issued, and travel with the
+  // stage until the tile is consumed.  kind: 0 padding slot / past the end, 1 interior, 2 edge.
+  struct Coord {
+    i64 t0, t1;
+    int kind;
+  };
+  auto issue = [&](u32 slot, int stage) {
+    Coord c{0, 0, 0};
+    if (slot < nslots) c.kind = tile_coords(d, slot, c.t0, c.t1);
+    if (c.kind == 1) {
+      const u32* g = p + in_base + c.t0 * in_s0 + c.t1;
+      u32* st = smem + stage * kTileStageWords;
+#pragma unroll
+      for (int r = 0; r < kTileVecR; ++r) cp_async_16(st + wr[r], g + r * in_step);
+    }
+    cp_async_commit();  // also when nothing was copied: "all but the newest group" then always means the same tiles
+    return c;
+  };
+  u32 slot = blockIdx.x;
+  Coord cur = issue(slot, 0);
+  Coord nxt = issue(slot + gridDim.x, 1);
+  int stage = 0;
+  for (; slot < nslots; slot += gridDim.x) {
+    cp_async_wait<1>();  // this tile's copies have landed (one newer group may still be in flight)
+    __syncthreads();     // ... for every thread; and everybody has finished reading the stage refilled next
+    const Coord after = issue(slot + 2 * gridDim.x, stage == 0 ? kTileStages - 1 : stage - 1);
+    if (cur.kind == 1) {
+      const u32* st = smem + stage * kTileStageWords;
+      u32 vin[kTileElems][1], vout[kTileElems][F::NOUT];
+#pragma unroll
+      for (int r = 0; r < kTileVecR; ++r)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) vin[r * 4 + c][0] = st[rd[r] + c * kPwTile];
+#pragma unroll
+      for (int e = 0; e < kTileElems; ++e) f(vin[e], vout[e]);
+#pragma unroll
+      for (int k = 0; k < F::NOUT; ++k) {
+        const i64 s1 = d.s1[k];
+        u32* po = static_cast<u32*>(ptrs.p[k]) + (cur.t0 + 4 * vx) + (cur.t1 + vy) * s1;
+#pragma unroll
+        for (int r = 0; r < kTileVecR; ++r)
+          st_v4(po + r * (kTileVecRows * s1),
+                make_uint4(vout[r * 4 + 0][k], vout[r * 4 + 1][k], vout[r * 4 + 2][k], vout[r * 4 + 3][k]));
+      }
+    } else if (cur.kind == 2) {
+      tile_edge_direct<F>(ptrs, f, d, cur.t0, cur.t1);
+    }
+    cur = nxt;
+    nxt = after;
+    stage = stage == kTileStages - 1 ? 0 : stage + 1;
+  }
+  cp_async_wait<0>();
+}
+
+// Shared memory of a tile kernel: the three stages of the asynchronous path for one-input f32
+// functors, one padded tile otherwise.
+template <class F>
+struct TileSmemWords {
+  static constexpr bool kOneF32Input = F::NIN == 1 && F::kInByteMask == 0u && F::kOutByteMask == 0u;
+  static constexpr int value = kOneF32Input ? kTileStages * kTileStageWords : kPwTile * (kPwTile + 1);
+};
 
 template <class F>
 __device__ __forceinline__ void pw_tile_body(const PwPtrs<PwTraits<F>::NT>& ptrs, const F& f,
                                              const TileDesc<PwTraits<F>::NT>& d) {
-  __shared__ __align__(16) u32 smem[kPwTile][kPwTile + 1];
-  for (i64 slot = blockIdx.x; slot < d.ntiles; slot += gridDim.x) {
-    // Tiles are walked in super-blocks of 8x8, so that the CTAs running side by side touch
-    // neighbouring pieces of the rows they share along dimension 0 and dimension 1 alike.
-    const i64 sb = slot / (kTileSuper * kTileSuper);
-    const int within = (int)(slot % (kTileSuper * kTileSuper));
-    const i64 b0 = (sb % d.sb0) * kTileSuper + within % kTileSuper;
-    const i64 b1 = (sb / d.sb0) * kTileSuper + within / kTileSuper;
-    if (b0 >= d.tiles0 || b1 >= d.tiles1) continue;
-    const i64 t0 = b0 * kPwTile, t1 = b1 * kPwTile;
-    if (t0 + kPwTile <= d.shape0 && t1 + kPwTile <= d.shape1) {
+  __shared__ __align__(128) u32 smem_words[TileSmemWords<F>::value];
+  PwTileSmem smem = reinterpret_cast<PwTileSmem>(smem_words);
+  if constexpr (TileSmemWords<F>::kOneF32Input) {
+    if (d.vec) {
+      // input through shared memory, outputs written directly: the asynchronous ring; any other
+      // mix of directions: the next tile's loads are prefetched into registers
+      if (d.dim1_mask == (1u << F::NOUT)) pw_tile_async<F>(ptrs, f, d, smem_words);
+      else pw_tile_pipelined<F>(ptrs, f, d, smem);
+      return;
+    }
+  }
+  const u32 nslots = (u32)d.ntiles;
+  for (u32 slot = blockIdx.x; slot < nslots; slot += gridDim.x) {
+    i64 t0, t1;
+    const int kind = tile_coords(d, slot, t0, t1);
+    if (kind == 0) continue;
+    if (kind == 1) {
       if constexpr (F::kInByteMask == 0u && F::kOutByteMask == 0u) {
         if (d.vec) {
-          pw_tile_one_vec<F>(ptrs, f, d, t0, t1, &smem[0][0]);
+          pw_tile_one_vec<F>(ptrs, f, d, t0, t1, smem_words);
           continue;
         }
       }
@@ -579,8 +825,13 @@ __global__ void __launch_bounds__(kBlock)
     pw_strided_kernel(PwPtrs<PwTraits<F>::NT> ptrs, F f, StridedDesc<PwTraits<F>::NT, IDX> d, i64 n) {
   pw_strided_body<F, U, IDX>(ptrs, f, d, n);
 }
+// CTAs per SM the tile kernels are compiled for: the pipelined one-input kernel keeps a second
+// tile in registers (64 registers, 4 CTAs); two-input functors get the same budget and larger ones
+// 80 registers (3 CTAs), which is what they need to stay clear of spills.
+__host__ __device__ constexpr int tile_min_ctas(int nin) { return nin == 1 ? kTilePersistCtas : (nin == 2 ? 4 : 3); }
+
 template <class F>
-__global__ void __launch_bounds__(kTileX* kTileRows, 5)
+__global__ void __launch_bounds__(kTileX* kPwRows, tile_min_ctas(F::NIN))
     pw_tile_kernel(PwPtrs<PwTraits<F>::NT> ptrs, F f, TileDesc<PwTraits<F>::NT> d) {
   pw_tile_body<F>(ptrs, f, d);
 }

@@ -96,6 +96,7 @@ SIGNATURES = {
     "twg_host_alloc_pinned": (c_int, [POINTER(c_void_p), c_size_t]),
     "twg_host_free_pinned": (c_int, [c_void_p]),
     "twg_copy_strided": (c_int, [POINTER(IterDesc), c_int, c_void_p, c_void_p, c_void_p]),
+    "twg_fill": (c_int, [POINTER(IterDesc), c_int, ctypes.c_uint64, c_void_p, c_void_p]),
     "twg_unary_f32": (c_int, [c_int, POINTER(IterDesc), c_void_p, c_void_p, c_void_p]),
     "twg_binary_f32": (c_int, [c_int, POINTER(IterDesc), c_void_p, c_void_p, c_float, c_void_p, c_void_p]),
     "twg_compare_f32": (c_int, [c_int, POINTER(IterDesc), c_void_p, c_void_p, c_float, c_void_p, c_void_p]),
@@ -396,6 +397,16 @@ def copy(x: np.ndarray, *, stream=None) -> np.ndarray:
     d = make_desc(x.shape, [do, dx])
     check(lib().twg_copy_strided(byref(d), x.itemsize, dx.ptr, do.ptr, stream))
     return do.numpy(stream)
+
+
+def fill(like: np.ndarray, value, *, pad: int = 0, stream=None) -> np.ndarray:
+    """Upload `like` (a view: its layout is what gets filled), fill the view with `value`, download."""
+    do = DeviceArray(like, stream=stream, pad_front=pad)
+    d = make_desc(like.shape, [do])
+    pattern = int.from_bytes(np.array(value, dtype=like.dtype).tobytes().ljust(8, b"\0"), "little")
+    check(lib().twg_fill(byref(d), like.itemsize, pattern, do.ptr, stream))
+    flat = do.buf.download(like.dtype, do.root_size, stream, offset_bytes=do.pad)
+    return flat
 
 
 def masked_select(x: np.ndarray, mask: np.ndarray, *, pad: int = 0, stream=None, return_status: bool = False):
