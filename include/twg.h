@@ -273,6 +273,8 @@ int twg_fused_compile(const TwgFusedInstr* prog, int ninstr, TwgFusedProgram** o
 int twg_fused_kind(const TwgFusedProgram* p, int* kind);
 /* desc operands: outputs (slot order) first, then inputs (slot order).  ptrs likewise. */
 int twg_fused_launch(const TwgFusedProgram* p, const TwgIterDesc* desc, void* const* ptrs, void* stream);
+/* Drops one reference; the last one unloads the program's modules (blocks until the devices that
+ * ran it are idle) and frees it.  A handle must not be used after its release. */
 int twg_fused_release(TwgFusedProgram* p);
 /* Fused predicate + select: out = inputs[src_input][ prog(inputs) ] in ONE pass, for a program
  * that is a predicate (exactly one bool output over dense f32 inputs of `numel` elements each,

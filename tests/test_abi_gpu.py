@@ -367,6 +367,49 @@ def test_masked_select_runs_of_full_and_empty_spans(abi, pad):
     assert_bit_equal(abi.masked_select(y, rowmask, pad=pad), oracle.masked_select(y, rowmask), f"row mask pad={pad}")
 
 
+@pytest.mark.parametrize("p", [0.0, 0.01, 0.3, 0.5, 0.99, 1.0])
+def test_masked_select_large_inputs(abi, p):
+    """About ten million elements: chunks of the longest kind, several per CTA slot, a partial last one."""
+    n = 320 * 32768 + 12345
+    x = rnd(n, 77)
+    mask = np.random.default_rng(78).random(n) < p
+    assert_bit_equal(abi.masked_select(x, mask), oracle.masked_select(x, mask), f"large n p={p}")
+    assert abi.last_path() == "dense"
+
+
+def test_masked_select_large_mixed_density_and_row_mask(abi):
+    n = 310 * 32768 + 4099
+    x = rnd(n, 79)
+    rng = np.random.default_rng(80)
+    mask = np.zeros(n, np.bool_)
+    for c0 in range(0, n, 32768):               # every chunk gets its own density, some are sparse, some full
+        kind = rng.integers(0, 6)
+        seg = slice(c0, min(c0 + 32768, n))
+        width = seg.stop - seg.start
+        if kind == 0:
+            mask[seg] = True
+        elif kind == 1:
+            mask[seg] = rng.random(width) < 0.002
+        elif kind == 2:
+            mask[seg] = rng.random(width) < 0.05
+        elif kind == 3:
+            mask[seg] = rng.random(width) < 0.6
+        elif kind == 4:
+            mask[seg] = np.repeat(rng.random((width + 511) // 512) < 0.5, 512)[:width]   # whole spans on or off
+    assert_bit_equal(abi.masked_select(x, mask), oracle.masked_select(x, mask), "large mixed density")
+    assert_bit_equal(abi.masked_select(x, mask, pad=1), oracle.masked_select(x, mask), "large mixed density, misaligned (strided path)")
+    rows, cols = 5000, 2048
+    y = rnd(rows * cols, 81).reshape(rows, cols)
+    for density in (0.5, 0.02):
+        rowmask = rng.random((rows, 1)) < density
+        assert_bit_equal(abi.masked_select(y, rowmask), oracle.masked_select(y, rowmask), f"large row mask {density}")
+        assert abi.last_path() == "dense"
+    rows, cols = 7001, 1500                     # rows that are not a multiple of 32 elements long
+    y = rnd(rows * cols, 82).reshape(rows, cols)
+    rowmask = rng.random((rows, 1)) < 0.5
+    assert_bit_equal(abi.masked_select(y, rowmask), oracle.masked_select(y, rowmask), "large row mask, odd row length")
+
+
 @pytest.mark.parametrize("pad", [1, 2, 3])
 def test_masked_select_misaligned(abi, pad):
     n = 5 * 4096 + 123
@@ -483,6 +526,28 @@ def test_fused_select_equals_mask_then_masked_select(abi, n):
     assert kind == "aot"
     assert_bit_equal(sel, abi.masked_select(a, m), "fused select vs mask + masked_select")
     assert_bit_equal(sel, oracle.masked_select(a, m), "fused select vs oracle on the same mask")
+
+
+def test_fused_programs_are_reference_counted(abi):
+    F = abi
+    L = abi.lib()
+    prog = [(F.F_INPUT_F32, 0, 0, 0.0), (F.F_CONST_F32, 0, 0, 1.25), (F.F_MUL, 0, 1, 0.0), (F.F_ABS, 2, 0, 0.0),
+            (F.F_OUTPUT, 3, 0, 0.0)]
+    x = rnd(5000, 93)
+    h1 = abi.fused_compile(prog)
+    h2 = abi.fused_compile(prog)                      # same program: same handle, second reference
+    assert h1 == h2 and abi.fused_kind(h1) == "nvrtc"
+    (y,), _ = abi.fused(prog, [x], [np.float32])      # third reference, launches the kernel
+    assert_bit_equal(y, np.abs(x * np.float32(1.25)), "abs(1.25 x)")
+    assert L.twg_fused_release(h1) == abi.TWG_OK
+    assert L.twg_fused_release(h1) == abi.TWG_OK
+    assert abi.fused_kind(h1) == "nvrtc"              # still alive: one reference left
+    assert L.twg_fused_release(h1) == abi.TWG_OK      # last one: module unloaded, program freed
+    assert L.twg_fused_release(h1) == abi.TWG_ERR_INVALID
+    assert b"not a live program handle" in L.twg_last_error()
+    (y2,), kind = abi.fused(prog, [x], [np.float32])  # compiling again after the release works
+    assert kind == "nvrtc"
+    assert_bit_equal(y2, y, "after recompilation")
 
 
 def test_fused_select_on_the_decision_boundary_of_the_chain(abi):

@@ -427,7 +427,7 @@ def test_config5_compiled_chain():
     torch_webgpu._C.reset_launch_count()
     sel, m = torch.compile(chain, backend=webgpu_backend)(da, db, dc)
     assert wc.last_compile_report["fused_kernels"] == 1 and wc.last_compile_report["kinds"] == ["aot"]
-    assert torch_webgpu._C.launch_count() == 2                   # one fused kernel + one compaction
+    assert torch_webgpu._C.launch_count() == 3                   # one fused kernel, the workspace clear, one compaction
     y_ref = torch.relu(F.silu(a + b) + c)
     m_ref = torch.bitwise_and(torch.eq(y_ref, 0), torch.ne(a, 0))
     m_cpu = m.cpu()
@@ -467,7 +467,7 @@ def test_compiled_chain_with_the_select_in_the_graph_is_one_launch():
         torch_webgpu._C.reset_launch_count()
         one = torch.compile(chain, backend=webgpu_backend)(da, db, dc)
         assert wc.last_compile_report["fused_selects"] == 1 and wc.last_compile_report["kinds"] == ["aot"]
-        assert torch_webgpu._C.launch_count() == 1
+        assert torch_webgpu._C.launch_count() == 2                 # the workspace clear and the fused select
         torch._dynamo.reset()
         two = torch.compile(chain, backend=webgpu_backend, options={"fuse_select": False})(da, db, dc)
         assert wc.last_compile_report["fused_selects"] == 0

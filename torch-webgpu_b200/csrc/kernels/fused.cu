@@ -475,6 +475,7 @@ struct TwgFusedProgram {
   std::vector<char> cubin;
   std::mutex mu;
   std::map<int, DeviceModule> modules;  // per device ordinal
+  int refs = 0;                         // handles handed out by twg_fused_compile and not yet released
 };
 
 namespace twg {
@@ -581,6 +582,7 @@ extern "C" int twg_fused_compile(const TwgFusedInstr* prog, int ninstr, TwgFused
   std::lock_guard<std::mutex> lock(g_cache_mu);
   auto it = g_cache.find(source);
   if (it != g_cache.end()) {
+    it->second->refs++;
     *out = it->second;
     return TWG_OK;
   }
@@ -599,6 +601,7 @@ extern "C" int twg_fused_compile(const TwgFusedInstr* prog, int ninstr, TwgFused
       return rc;
     }
   }
+  p->refs = 1;
   g_cache[source] = p;
   *out = p;
   return TWG_OK;
@@ -634,11 +637,38 @@ extern "C" int twg_fused_launch(const TwgFusedProgram* cp, const TwgIterDesc* de
   }
 }
 
-// Programs are owned by the cache and shared between callers; release is a no-op kept for
-// symmetry with compile so that callers can treat handles as owned.
+// Programs are shared through the cache and counted: every twg_fused_compile hands out one
+// reference, the last twg_fused_release drops the program from the cache, waits for the devices
+// that loaded its module (a kernel of it may still be running), unloads the modules and frees the
+// cubin and the generated source.
 extern "C" int twg_fused_release(TwgFusedProgram* p) {
-  (void)p;
-  return TWG_OK;
+  if (p == nullptr) return TWG_OK;
+  {
+    std::lock_guard<std::mutex> lock(g_cache_mu);
+    auto it = g_cache.begin();
+    for (; it != g_cache.end(); ++it)
+      if (it->second == p) break;
+    TWG_REQUIRE(it != g_cache.end(), "twg_fused_release: %p is not a live program handle", (void*)p);
+    if (--p->refs > 0) return TWG_OK;
+    g_cache.erase(it);
+  }
+  int rc = TWG_OK;
+  if (!p->modules.empty()) {
+    int prev = 0;
+    cudaGetDevice(&prev);
+    for (auto& kv : p->modules) {
+      if (kv.second.mod == nullptr) continue;
+      if (cudaSetDevice(kv.first) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
+        cudaGetLastError();
+        rc = set_error(TWG_ERR_CUDA, "twg_fused_release: could not quiesce device %d before unloading the module", kv.first);
+        continue;  // the module stays loaded rather than being pulled from under a kernel
+      }
+      g_dyn.ModuleUnload(kv.second.mod);
+    }
+    cudaSetDevice(prev);
+  }
+  delete p;
+  return rc;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -675,8 +705,7 @@ extern "C" int twg_fused_select_f32(const TwgFusedProgram* cp, int src_input, in
   TWG_REQUIRE(src_input >= 0 && src_input < p->an.nin, "twg_fused_select_f32: src_input %d out of range", src_input);
   TWG_REQUIRE(numel >= 0, "twg_fused_select_f32: negative numel");
   g_last_path = kPathNone;
-  TWG_CUDA(cudaMemsetAsync(result_dev, 0, 2 * sizeof(int64_t), s));
-  if (numel == 0) return TWG_OK;
+  if (numel == 0) return ms_clear(nullptr, 0, result_dev, s);
   TWG_REQUIRE(out != nullptr && is_aligned(out, 4), "twg_fused_select_f32: out is null or misaligned");
   for (int k = 0; k < p->an.nin; ++k) {
     TWG_REQUIRE(inputs[k] != nullptr, "twg_fused_select_f32: input %d is null", k);
@@ -690,7 +719,7 @@ extern "C" int twg_fused_select_f32(const TwgFusedProgram* cp, int src_input, in
   TWG_REQUIRE(workspace != nullptr && workspace_bytes >= need && is_aligned(workspace, 256),
               "twg_fused_select_f32: workspace of %zu bytes is smaller than the %zu required or not 256-byte aligned",
               workspace_bytes, need);
-  TWG_CUDA(cudaMemsetAsync(workspace, 0, need, s));
+  if (int rc = ms_clear(workspace, need, result_dev, s)) return rc;
   SelectArgs a;
   a.inputs = inputs;
   a.out = out;

@@ -163,7 +163,7 @@ __global__ void __launch_bounds__(kMsThreads, 4)
   constexpr bool ROWMASK = MODE == kMsRowMask;
   constexpr int kSpans = CH * kMsWarps;  // spans of 512 elements in a chunk
   __shared__ MsDenseShared<CH> sm;
-  __shared__ u32 bits[CH * (kMsRound / 32)];  // the chunk's mask, one bit per element
+  __shared__ __align__(16) u32 bits[CH * (kMsRound / 32)];  // the chunk's mask, one bit per element
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (threadIdx.x == 0) sm.tile = (i64)atomicAdd(ticket, 1ull);
   __syncthreads();
@@ -272,8 +272,13 @@ __global__ void __launch_bounds__(kMsThreads, 4)
       for (int i = 0; i < 16; ++i) r.v[i] = ld_b32(src + e0 + i * 32);
     } else {
 #pragma unroll
-      for (int i = 0; i < 16; ++i)
-        if ((bits[s * 16 + i] >> lane) & 1u) r.v[i] = ld_b32(src + e0 + i * 32);  // 0 bits beyond n
+      for (int h = 0; h < 4; ++h) {
+        const uint4 q = reinterpret_cast<const uint4*>(bits + s * 16)[h];
+        const u32 w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if ((w[k] >> lane) & 1u) r.v[4 * h + k] = ld_b32(src + e0 + (4 * h + k) * 32);  // 0 bits beyond n
+      }
     }
   };
   // A warp that made its own bits (dense mode) starts fetching its first span right away: the
@@ -361,13 +366,14 @@ __global__ void __launch_bounds__(kMsThreads, 4)
   // at stage[v - vbase] (vbase a multiple of 4), so aligned vectors of the output are aligned
   // vectors of the stage and go out as one 128-bit shared load and one 128-bit store.  Elements
   // below vf are already in global memory; after every span the complete vectors are written and
-  // the at most three elements left over move to the front of the stage.
+  // the at most three elements left over ride in a register to the front of the next span's stage.
   float* const chunk_out = out + sm.excl;
   const u32 a0 = (u32)(reinterpret_cast<unsigned long long>(chunk_out) >> 2) & 3u;
   float* const out_v = chunk_out - a0;
   float* const stage = sm.stage[warp];
   const u32 below = (1u << lane) - 1u;
   u32 v = a0 + before, vf = v, vbase = v & ~3u;
+  float carry = 0.f;  // lane i < v - vf holds the element with virtual index vf + i
   for (int i = 0; i < CH; ++i) {
     const int s = span0 + i;
     const MsSpanRegs cur = next;
@@ -375,22 +381,27 @@ __global__ void __launch_bounds__(kMsThreads, 4)
     const u32 run = sm.cnt[s];
     if (run == 0u) continue;
     if (run == 512u) {
-      // everything selected: after the few elements still waiting in the stage the span is a straight copy
-      if ((u32)lane < v - vf) out_v[vf + lane] = stage[vf - vbase + lane];
+      // everything selected: after the few elements still waiting the span is a straight copy
+      if ((u32)lane < v - vf) out_v[vf + lane] = carry;
 #pragma unroll
       for (int k = 0; k < 16; ++k) out_v[v + k * 32 + lane] = __uint_as_float(cur.v[k]);
       v += 512u;
       vf = v;
       vbase = v & ~3u;
-      __syncwarp();
       continue;
     }
+    if ((u32)lane < v - vf) stage[vf - vbase + lane] = carry;
     u32 pos = v - vbase;  // stage index of the span's first selected element
 #pragma unroll
-    for (int k = 0; k < 16; ++k) {
-      const u32 word = bits[s * 16 + k];
-      if ((word >> lane) & 1u) stage[pos + __popc(word & below)] = __uint_as_float(cur.v[k]);
-      pos += __popc(word);
+    for (int h = 0; h < 2; ++h) {  // the span's mask words, eight at a time (two 128-bit broadcast loads)
+      const uint4 qa = reinterpret_cast<const uint4*>(bits + s * 16)[2 * h];
+      const uint4 qb = reinterpret_cast<const uint4*>(bits + s * 16)[2 * h + 1];
+      const u32 w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        if ((w[k] >> lane) & 1u) stage[pos + __popc(w[k] & below)] = __uint_as_float(cur.v[8 * h + k]);
+        pos += __popc(w[k]);
+      }
     }
     const u32 v_end = v + run;
     __syncwarp();
@@ -403,22 +414,21 @@ __global__ void __launch_bounds__(kMsThreads, 4)
       const u32 nvec = (v_end - vf) >> 2;
       const float4* from = reinterpret_cast<const float4*>(stage + (vf - vbase));
       float4* to4 = reinterpret_cast<float4*>(out_v + vf);
-      for (u32 k = lane; k < nvec; k += 32) to4[k] = from[k];
-      vf += 4u * nvec;
-      if (vf != vbase) {
-        const u32 rem = v_end - vf;  // 0..3 elements wait for the rest of their vector
-        __syncwarp();
-        float x = 0.f;
-        if ((u32)lane < rem) x = stage[vf - vbase + lane];
-        __syncwarp();
-        if ((u32)lane < rem) stage[lane] = x;
-        vbase = vf;
+      for (u32 k = lane; k < nvec; k += 64) {  // two rounds per trip: both loads are issued before the stores
+        const float4 x0 = from[k];
+        float4 x1 = x0;
+        if (k + 32 < nvec) x1 = from[k + 32];
+        to4[k] = x0;
+        if (k + 32 < nvec) to4[k + 32] = x1;
       }
+      vf += 4u * nvec;
+      if ((u32)lane < v_end - vf) carry = stage[vf - vbase + lane];  // 0..3 elements wait for the rest of their vector
+      vbase = vf;
     }
     v = v_end;
-    __syncwarp();
+    __syncwarp();  // the stage is rewritten by the next span
   }
-  if ((u32)lane < v - vf) out_v[vf + lane] = stage[vf - vbase + lane];  // the stretch's last partial vector
+  if ((u32)lane < v - vf) out_v[vf + lane] = carry;  // the stretch's last partial vector
 }
 
 // ------------------------------------------------------------------------------------------
@@ -485,6 +495,25 @@ __global__ void __launch_bounds__(kMsThreads)
   flush_stage(sm.stage, out, sm.excl, tile_total);
 }
 
+// Zeroes the part of the workspace a call uses (ticket header + descriptors) and the two result
+// words with ONE small kernel.  Two cudaMemsetAsync calls in front of the compaction kernel cost
+// about 20 us per call on B200 (measured: 196 us from event to event for a kernel that runs 174 us);
+// a kernel in front of a kernel on the same stream costs a microsecond or two.
+__global__ void __launch_bounds__(256) ms_clear_kernel(u64* workspace, unsigned nwords, i64* result) {
+  const unsigned i = blockIdx.x * 256u + threadIdx.x;  // one 16-byte pair of words per thread
+  if (2u * i + 1u < nwords) *reinterpret_cast<uint4*>(workspace + 2u * i) = make_uint4(0u, 0u, 0u, 0u);
+  else if (2u * i < nwords) workspace[2u * i] = 0ull;
+  if (i < 2u) result[i] = 0;
+}
+// workspace == nullptr: only the result words
+int ms_clear(void* workspace, size_t nbytes, int64_t* result, cudaStream_t s) {
+  const unsigned nwords = workspace ? (unsigned)(nbytes / 8) : 0u;  // sized in 8-byte words, 256-byte aligned
+  const unsigned threads = (nwords + 1u) / 2u > 2u ? (nwords + 1u) / 2u : 2u;
+  ms_clear_kernel<<<(threads + 255u) / 256u, 256, 0, s>>>(static_cast<u64*>(workspace), nwords, reinterpret_cast<i64*>(result));
+  TWG_CHECK_LAUNCH();
+  return TWG_OK;
+}
+
 // Tiles per dense chunk: the largest power of two up to 32 that still leaves about four waves
 // of chunks on the device, so that large tensors amortise the look-back over long chunks and small
 // ones still fill every SM.
@@ -536,9 +565,8 @@ extern "C" int twg_masked_select_f32(const TwgIterDesc* desc, const float* src, 
   g_last_path = kPathNone;
   if (int rc = check_desc(desc, 2)) return rc;
   TWG_REQUIRE(result_dev != nullptr, "twg_masked_select_f32: result_dev is null");
-  TWG_CUDA(cudaMemsetAsync(result_dev, 0, 2 * sizeof(int64_t), s));
   const int64_t n = desc->numel;
-  if (n == 0) return TWG_OK;
+  if (n == 0) return ms_clear(nullptr, 0, result_dev, s);
   TWG_REQUIRE(src && mask && out, "twg_masked_select_f32: null operand");
   const size_t need = twg_masked_select_workspace_bytes(n);
   TWG_REQUIRE(workspace != nullptr && workspace_bytes >= need,
@@ -568,7 +596,7 @@ extern "C" int twg_masked_select_f32(const TwgIterDesc* desc, const float* src, 
     const int64_t tile_elems = (int64_t)chunk_tiles * kMsRound;
     const int64_t ntiles = (n + tile_elems - 1) / tile_elems;
     TWG_REQUIRE(ntiles <= 0x7fffffff, "twg_masked_select_f32: %lld elements exceed the tile limit", (long long)n);
-    TWG_CUDA(cudaMemsetAsync(workspace, 0, kMsHeaderBytes + (size_t)ntiles * sizeof(u64), s));
+    if (int rc = ms_clear(workspace, kMsHeaderBytes + (size_t)ntiles * sizeof(u64), result_dev, s)) return rc;
     FastDiv32 row_len;
     row_len.d = rowmask ? (uint32_t)d.shape[0] : 1u;
     make_fastdiv(row_len.d, &row_len.m, &row_len.s);
@@ -585,7 +613,7 @@ extern "C" int twg_masked_select_f32(const TwgIterDesc* desc, const float* src, 
 
   const int64_t ntiles = (n + kMsRound - 1) / kMsRound;
   TWG_REQUIRE(ntiles <= 0x7fffffff, "twg_masked_select_f32: %lld elements exceed the tile limit", (long long)n);
-  TWG_CUDA(cudaMemsetAsync(workspace, 0, need, s));
+  if (int rc = ms_clear(workspace, need, result_dev, s)) return rc;
   if (fits_32bit(d, 2)) {
     StridedDesc<2, u32> sd;
     fill_strided_desc<2>(d, &sd);

@@ -42,6 +42,8 @@ int check_desc(const TwgIterDesc* d, int ntensors);
 int64_t max_offset(const TwgIterDesc& d, int t);
 // Settings of the look-back shared by masked_select and the fused select (masked_select.cu).
 long long ms_poll_budget();
+// Zero a compaction workspace prefix and the two result words with one kernel (masked_select.cu).
+int ms_clear(void* workspace, size_t nbytes, int64_t* result, cudaStream_t s);
 // After coalescing: every one of the first `nt` operands is one contiguous run (copy.cu).
 bool all_dense(const TwgIterDesc& d, int nt);
 // Host-side multiply-shift divisor for u32 numerators below 2^31.
