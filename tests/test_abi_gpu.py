@@ -551,9 +551,8 @@ def test_fused_programs_are_reference_counted(abi):
 
 
 def test_fused_select_on_the_decision_boundary_of_the_chain(abi):
-    """The select form of the chain decides most elements with a cheap bound and only computes the
-    exact silu inside a narrow band around silu(a + b) + c == 0.  Inputs placed on and next to that
-    boundary, huge and non-finite values must give the same mask as the exact chain."""
+    """Inputs placed on and next to the boundary silu(a + b) + c == 0, huge and non-finite values:
+    the one-launch form must select exactly what the chain's mask says."""
     n = 1 << 18
     rng = np.random.default_rng(91)
     a = (rng.random(n, dtype=np.float32) * 8 - 4).astype(np.float32)

@@ -37,6 +37,7 @@ enum ValType { kF32 = 0, kBool = 1, kNone = 2 };
 struct Analysis {
   int nin = 0, nout = 0;
   unsigned in_byte_mask = 0, out_byte_mask = 0;
+  bool heavy = false;  // the program contains a transcendental activation
   std::vector<int> type;  // per instruction
   // a predicate: one bool output over f32 inputs - can drive the fused select
   bool is_predicate() const { return nout == 1 && out_byte_mask == 1u && in_byte_mask == 0u && nin >= 1; }
@@ -80,6 +81,7 @@ static int analyse(const TwgFusedInstr* prog, int n, Analysis* a) {
       case TWG_F_ABS:
         if (int rc = operand(I.a, kF32)) return rc;
         a->type[i] = kF32;
+        if (I.opcode == TWG_F_SILU || I.opcode == TWG_F_GELU_ERF || I.opcode == TWG_F_GELU_TANH) a->heavy = true;
         break;
       case TWG_F_EQ:
       case TWG_F_NE:
@@ -137,6 +139,7 @@ static std::string generate_source(const TwgFusedInstr* prog, int n, const Analy
            "  static constexpr int NIN = %d, NOUT = %d;\n  static constexpr unsigned kInByteMask = %uu, kOutByteMask = %uu;\n",
            a.nin, a.nout, a.in_byte_mask, a.out_byte_mask);
   s += line;
+  s += a.heavy ? "  static constexpr bool kHeavy = true;\n" : "  static constexpr bool kHeavy = false;\n";
   s += "  __device__ __forceinline__ void operator()(const u32* in, u32* out) const {\n";
   static const char* unary[] = {"f_relu", "f_silu", "f_gelu_erf", "f_gelu_tanh", "f_abs"};
   static const char* cmp[] = {"f_eq", "f_ne", "f_lt", "f_le", "f_gt", "f_ge"};
@@ -181,7 +184,7 @@ static std::string generate_source(const TwgFusedInstr* prog, int n, const Analy
            "extern \"C\" __global__ void __launch_bounds__(kBlock) twg_fused_dense(PwPtrs<NT> p, i64 nunits, i64 n) "
            "{ pw_contig_body<Prog, %d>(p, Prog{}, nunits, n); }\n", dense_unroll(a.nin));
   s += line;
-  s += "extern \"C\" __global__ void __launch_bounds__(kTileX * kPwRows, tile_min_ctas(Prog::NIN)) twg_fused_tile(PwPtrs<NT> p, TileDesc<NT> d) "
+  s += "extern \"C\" __global__ void __launch_bounds__(kTileX * kPwRows, tile_min_ctas<Prog>()) twg_fused_tile(PwPtrs<NT> p, TileDesc<NT> d) "
        "{ pw_tile_body<Prog>(p, Prog{}, d); }\n";
   snprintf(line, sizeof(line),
            "extern \"C\" __global__ void __launch_bounds__(kBlock) twg_fused_strided32(PwPtrs<NT> p, StridedDesc<NT, u32> d, i64 n) "
@@ -224,38 +227,6 @@ struct AotChainMask {
     const float a = as_f(in[0]), b = as_f(in[1]), c = as_f(in[2]);
     const float y = f_relu(f_add(f_silu(f_add(a, b, 1.0f)), c, 1.0f));
     out[0] = f_and(f_eq(y, 0.0f), f_ne(a, 0.0f));
-  }
-};
-// The same predicate for the fused predicate + select kernel, which is bound by instruction issue
-// rather than by memory: decide cheaply where that is safe, fall back to the exact chain otherwise.
-//   relu(t) == 0  <=>  t <= 0, and t = fl(s + c) <= 0  <=>  s + c <= 0 exactly (the sum of two floats
-//   is either zero or at least one denormal away from it, so rounding never moves it across zero),
-//   i.e.  s <= -c  with  s = f_silu(a + b).
-// For |a + b| <= 80 a fast s' (ex2/rcp approximations) is within 1.3e-5 |s| of s (documented bounds:
-// __expf 2 + 1.173 |x| ulp, __fdividef 2 ulp, accurate path <= 3 ulp); whenever s' is further than
-// 2^-14 |s'| + 1e-30 from -c the comparison is already decided.  Only elements inside that band
-// (a few in a hundred thousand), non-finite values and |a + b| > 80 take the exact path, so the
-// mask is bit-identical to AotChainMask's.
-struct AotChainMaskQuick {
-  static constexpr int NIN = 3, NOUT = 1;
-  static constexpr unsigned kInByteMask = 0u, kOutByteMask = 1u;
-  __device__ __forceinline__ void operator()(const u32* in, u32* out) const {
-    const float a = as_f(in[0]), b = as_f(in[1]), c = as_f(in[2]);
-    const float u = f_add(a, b, 1.0f);
-    const float nc = -c;
-    bool le = false, decided = false;
-    if (fabsf(u) <= 80.0f) {  // false for NaN
-      const float s = __fdividef(u, 1.0f + __expf(-u));
-      const float tol = fmaf(fabsf(s), 6.103515625e-5f, 1e-30f);
-      if (s + tol < nc) {
-        le = true;
-        decided = true;
-      } else if (s - tol > nc) {
-        decided = true;
-      }
-    }
-    if (!decided) le = f_add(f_silu(u), c, 1.0f) <= 0.0f;
-    out[0] = (le && a != 0.0f) ? 1u : 0u;
   }
 };
 // Same chain that also keeps y.
@@ -322,7 +293,7 @@ struct AotEntry {
 };
 static const AotEntry kAot[] = {
     {kProgAddRelu, (int)(sizeof(kProgAddRelu) / sizeof(TwgFusedInstr)), &aot_launch<AotAddRelu>, nullptr},
-    {kProgChainMask, (int)(sizeof(kProgChainMask) / sizeof(TwgFusedInstr)), &aot_launch<AotChainMask>, &aot_select0<AotChainMaskQuick>},
+    {kProgChainMask, (int)(sizeof(kProgChainMask) / sizeof(TwgFusedInstr)), &aot_launch<AotChainMask>, &aot_select0<AotChainMask>},
     {kProgChainMaskY, (int)(sizeof(kProgChainMaskY) / sizeof(TwgFusedInstr)), &aot_launch<AotChainMaskY>, nullptr},
 };
 
@@ -537,7 +508,8 @@ static int jit_launch(TwgFusedProgram* p, const TwgIterDesc* desc, void* const* 
       TileDesc<NT> td;
       fill_tile_desc<NT>(plan, &td, ptrs_in, p->an.in_byte_mask == 0u && p->an.out_byte_mask == 0u);
       void* args[] = {&ptrs, &td};
-      r = g_dyn.LaunchKernel(m->tile, tile_grid(sig, td.vec != 0u, plan.grid), 1, 1, kTileX, kPwRows, 1, 0, cs, args, nullptr);
+      const bool pipelined = p->an.heavy && p->an.nin == 1 && p->an.in_byte_mask == 0u && p->an.out_byte_mask == 0u;  // TilePipelined<Prog>
+      r = g_dyn.LaunchKernel(m->tile, tile_grid(pipelined, td.vec != 0u, plan.grid), 1, 1, kTileX, kPwRows, 1, 0, cs, args, nullptr);
       break;
     }
     case kPathStrided32: {

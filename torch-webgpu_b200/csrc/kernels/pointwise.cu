@@ -9,6 +9,8 @@ template <int OP>
 struct UnaryF32 {
   static constexpr int NIN = 1, NOUT = 1;
   static constexpr unsigned kInByteMask = 0u, kOutByteMask = 0u;
+  // the transcendental activations cost tens of instructions per element
+  static constexpr bool kHeavy = OP == TWG_UNARY_GELU_TANH || OP == TWG_UNARY_SILU || OP == TWG_UNARY_GELU_ERF;
   __device__ __forceinline__ void operator()(const u32* in, u32* out) const {
     const float x = as_f(in[0]);
     float y;

@@ -77,11 +77,10 @@ void fill_tile_desc(const PwPlan& p, TileDesc<NT>* td, void* const* ptrs = nullp
   }
   td->vec = vec ? 1u : 0u;
 }
-// Grid of a tile launch: one CTA per slot, except for the pipelined kernel (one f32 input, 128-bit
-// capable layout), whose CTAs stay resident and walk the slots with a grid stride.
-inline unsigned tile_grid(const PwSig& sig, bool vec, unsigned slots) {
-  if (sig.nin == 1 && sig.in_byte_mask == 0u && sig.out_byte_mask == 0u && vec)
-    return std::min<unsigned>(slots, (unsigned)(sm_count() * kTilePersistCtas));
+// Grid of a tile launch: one CTA per slot, except for the pipelined kernel (a heavy one-input f32
+// functor on a 128-bit capable layout), whose CTAs stay resident and walk the slots with a grid stride.
+inline unsigned tile_grid(bool pipelined, bool vec, unsigned slots) {
+  if (pipelined && vec) return std::min<unsigned>(slots, (unsigned)(sm_count() * kTilePersistCtas));
   return slots;
 }
 template <int NT>
@@ -118,7 +117,7 @@ int launch_pointwise(const F& f, const TwgIterDesc* desc, void* const* ptrs_in, 
     case kPathTile: {
       TileDesc<NT> td;
       fill_tile_desc<NT>(plan, &td, ptrs_in, F::kInByteMask == 0u && F::kOutByteMask == 0u);
-      pw_tile_kernel<F><<<tile_grid(sig_of<F>(), td.vec != 0u, plan.grid), dim3(kTileX, kPwRows), 0, stream>>>(ptrs, f, td);
+      pw_tile_kernel<F><<<tile_grid(TilePipelined<F>::value, td.vec != 0u, plan.grid), dim3(kTileX, kPwRows), 0, stream>>>(ptrs, f, td);
       break;
     }
     case kPathStrided32: {

@@ -361,7 +361,7 @@ constexpr int kTileXR = kPwTile / kTileX;     // 2
 constexpr int kTileYR = kPwTile / kPwRows;    // 8
 constexpr int kTileElems = kTileXR * kTileYR; // 16 per thread
 constexpr int kTileVecRows = kTileX * kPwRows / 16;  // rows one pass of the 128-bit path covers (16 threads per row)
-constexpr int kTilePersistCtas = 4;           // CTAs per SM of the pipelined one-input tile kernel
+constexpr int kTilePersistCtas = 4;           // CTAs per SM of the pipelined tile kernel (heavy one-input functors)
 constexpr int kTileSuper = 8;                 // tiles per super-block edge
 
 template <int NT>
@@ -647,152 +647,33 @@ __device__ __forceinline__ void pw_tile_pipelined(const PwPtrs<PwTraits<F>::NT>&
   }
 }
 
-// ------------------------------------------------------------------------------------------
-// One f32 input that is dense along dimension 1, outputs dense along dimension 0 (y = f(x.t())):
-// the input tile has to pass through shared memory anyway, so it is brought there with
-// asynchronous 16-byte copies (cp.async) into a ring of three 16 KB stages.  While a CTA computes
-// and stores tile j, the copies of tiles j + 1 and j + 2 are in flight and occupy no registers;
-// four such CTAs keep 128 KB of loads in flight per SM whatever the functor costs.
-// ------------------------------------------------------------------------------------------
-constexpr int kTileStages = 3;
-constexpr int kTileStageWords = kPwTile * kPwTile;
-
-__device__ __forceinline__ void cp_async_16(u32* smem_dst, const void* gmem_src) {
-  const u32 dst = (u32)__cvta_generic_to_shared(smem_dst);
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gmem_src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-// Edge tile without shared memory: every element on its own, bounds-checked (tiles on the rim of
-// the tensor are few; the async kernel's stages are busy with other tiles' copies meanwhile).
+// Functors that cost tens of instructions per element (silu, gelu) say so with
+// `static constexpr bool kHeavy = true`; the tile kernel then prefetches the next tile's loads into
+// registers (pw_tile_pipelined).  Measured on a 16384^2 transpose, fractions of the copy peak for
+// relu / silu / gelu(erf): one tile per CTA, 5 CTAs per SM 0.97 / 0.88 / 0.80; register prefetch,
+// 4 persistent CTAs per SM 0.91 / 0.90 / 0.86; a three-stage cp.async ring in shared memory
+// 0.86 / 0.78 / 0.85 (dropped).  Cheap functors want CTAs, expensive ones want the loads of the next
+// tile in flight while the arithmetic runs.
+template <class F, class = void>
+struct PwHeavy {
+  static constexpr bool value = false;
+};
 template <class F>
-__device__ __forceinline__ void tile_edge_direct(const PwPtrs<PwTraits<F>::NT>& ptrs, const F& f,
-                                                 const TileDesc<PwTraits<F>::NT>& d, i64 t0, i64 t1) {
-  constexpr int NT = PwTraits<F>::NT;
-  const int tx = threadIdx.x, ty = threadIdx.y;
-#pragma unroll
-  for (int a = 0; a < kTileXR; ++a)
-#pragma unroll
-    for (int r = 0; r < kTileYR; ++r) {
-      const i64 i0 = t0 + tx + a * kTileX, i1 = t1 + ty + r * kPwRows;
-      if (i0 < d.shape0 && i1 < d.shape1) {
-        i64 off[NT];
-#pragma unroll
-        for (int t = 0; t < NT; ++t) off[t] = i0 * d.s0[t] + i1 * d.s1[t];
-        u32 in[F::NIN > 0 ? F::NIN : 1], out[F::NOUT];
-        load_inputs_elem<F>(ptrs, off, in);
-        f(in, out);
-        store_outputs_elem<F>(ptrs, off, out);
-      }
-    }
-}
-
+struct PwHeavy<F, decltype((void)F::kHeavy)> {
+  static constexpr bool value = F::kHeavy;
+};
 template <class F>
-__device__ __forceinline__ void pw_tile_async(const PwPtrs<PwTraits<F>::NT>& ptrs, const F& f,
-                                              const TileDesc<PwTraits<F>::NT>& d, u32* smem) {
-  static_assert(F::NIN == 1, "one input");
-  constexpr int T = F::NOUT;  // operand index of the input
-  const int lin = threadIdx.y * kTileX + threadIdx.x;
-  // copy phase: thread (cx, cy) copies the 16-byte piece cx of rows cy + 16 r
-  const int cx = lin & 15, cy = lin >> 4;
-  // compute phase: thread (vx, vy) holds elements (i0 = 4 vx + c, i1 = vy + 16 r).  Inside a warp vx
-  // takes 8 consecutive values and vy 4 consecutive ones, so the 32 lanes read 8 different
-  // (swizzled) 16-byte pieces times 4 different words of a piece: every bank once.
-  const int lane = lin & 31, wrp = lin >> 5;
-  const int vx = (lane & 7) + 8 * (wrp & 1), vy = (lane >> 3) + 4 * (wrp >> 1);
-  const u32* p = static_cast<const u32*>(ptrs.p[T]);
-  const u32 nslots = (u32)d.ntiles;
-  // per-thread constants of the addresses: a tile at (t0, t1) adds t0 * s0 + t1 (input) or
-  // t0 + t1 * s1 (outputs)
-  const i64 in_s0 = d.s0[T];
-  const i64 in_base = cy * in_s0 + 4 * cx, in_step = kTileVecRows * in_s0;
-  u32 rd[kTileVecR];  // word index of the thread's element (c = 0) of pass r inside a stage
-#pragma unroll
-  for (int r = 0; r < kTileVecR; ++r) {
-    const int i1 = vy + kTileVecRows * r;
-    rd[r] = (u32)((4 * vx) * kPwTile + ((((i1 >> 2) ^ vx) & 15) << 2) + (i1 & 3));
-  }
-  u32 wr[kTileVecR];  // word index of the 16-byte piece the thread copies in pass r
-#pragma unroll
-  for (int r = 0; r < kTileVecR; ++r) {
-    const int i0 = cy + kTileVecRows * r;
-    wr[r] = (u32)(i0 * kPwTile + ((cx ^ ((i0 >> 2) & 15)) << 2));
-  }
-  // The coordinates of a slot are worked out once, when its copies are issued, and travel with the
-  // stage until the tile is consumed.  kind: 0 padding slot / past the end, 1 interior, 2 edge.
-  struct Coord {
-    i64 t0, t1;
-    int kind;
-  };
-  auto issue = [&](u32 slot, int stage) {
-    Coord c{0, 0, 0};
-    if (slot < nslots) c.kind = tile_coords(d, slot, c.t0, c.t1);
-    if (c.kind == 1) {
-      const u32* g = p + in_base + c.t0 * in_s0 + c.t1;
-      u32* st = smem + stage * kTileStageWords;
-#pragma unroll
-      for (int r = 0; r < kTileVecR; ++r) cp_async_16(st + wr[r], g + r * in_step);
-    }
-    cp_async_commit();  // also when nothing was copied: "all but the newest group" then always means the same tiles
-    return c;
-  };
-  u32 slot = blockIdx.x;
-  Coord cur = issue(slot, 0);
-  Coord nxt = issue(slot + gridDim.x, 1);
-  int stage = 0;
-  for (; slot < nslots; slot += gridDim.x) {
-    cp_async_wait<1>();  // this tile's copies have landed (one newer group may still be in flight)
-    __syncthreads();     // ... for every thread; and everybody has finished reading the stage refilled next
-    const Coord after = issue(slot + 2 * gridDim.x, stage == 0 ? kTileStages - 1 : stage - 1);
-    if (cur.kind == 1) {
-      const u32* st = smem + stage * kTileStageWords;
-      u32 vin[kTileElems][1], vout[kTileElems][F::NOUT];
-#pragma unroll
-      for (int r = 0; r < kTileVecR; ++r)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) vin[r * 4 + c][0] = st[rd[r] + c * kPwTile];
-#pragma unroll
-      for (int e = 0; e < kTileElems; ++e) f(vin[e], vout[e]);
-#pragma unroll
-      for (int k = 0; k < F::NOUT; ++k) {
-        const i64 s1 = d.s1[k];
-        u32* po = static_cast<u32*>(ptrs.p[k]) + (cur.t0 + 4 * vx) + (cur.t1 + vy) * s1;
-#pragma unroll
-        for (int r = 0; r < kTileVecR; ++r)
-          st_v4(po + r * (kTileVecRows * s1),
-                make_uint4(vout[r * 4 + 0][k], vout[r * 4 + 1][k], vout[r * 4 + 2][k], vout[r * 4 + 3][k]));
-      }
-    } else if (cur.kind == 2) {
-      tile_edge_direct<F>(ptrs, f, d, cur.t0, cur.t1);
-    }
-    cur = nxt;
-    nxt = after;
-    stage = stage == kTileStages - 1 ? 0 : stage + 1;
-  }
-  cp_async_wait<0>();
-}
-
-// Shared memory of a tile kernel: the three stages of the asynchronous path for one-input f32
-// functors, one padded tile otherwise.
-template <class F>
-struct TileSmemWords {
-  static constexpr bool kOneF32Input = F::NIN == 1 && F::kInByteMask == 0u && F::kOutByteMask == 0u;
-  static constexpr int value = kOneF32Input ? kTileStages * kTileStageWords : kPwTile * (kPwTile + 1);
+struct TilePipelined {
+  static constexpr bool value = F::NIN == 1 && F::kInByteMask == 0u && F::kOutByteMask == 0u && PwHeavy<F>::value;
 };
 
 template <class F>
 __device__ __forceinline__ void pw_tile_body(const PwPtrs<PwTraits<F>::NT>& ptrs, const F& f,
                                              const TileDesc<PwTraits<F>::NT>& d) {
-  __shared__ __align__(128) u32 smem_words[TileSmemWords<F>::value];
-  PwTileSmem smem = reinterpret_cast<PwTileSmem>(smem_words);
-  if constexpr (TileSmemWords<F>::kOneF32Input) {
+  __shared__ __align__(16) u32 smem[kPwTile][kPwTile + 1];
+  if constexpr (TilePipelined<F>::value) {
     if (d.vec) {
-      // input through shared memory, outputs written directly: the asynchronous ring; any other
-      // mix of directions: the next tile's loads are prefetched into registers
-      if (d.dim1_mask == (1u << F::NOUT)) pw_tile_async<F>(ptrs, f, d, smem_words);
-      else pw_tile_pipelined<F>(ptrs, f, d, smem);
+      pw_tile_pipelined<F>(ptrs, f, d, smem);
       return;
     }
   }
@@ -804,7 +685,7 @@ __device__ __forceinline__ void pw_tile_body(const PwPtrs<PwTraits<F>::NT>& ptrs
     if (kind == 1) {
       if constexpr (F::kInByteMask == 0u && F::kOutByteMask == 0u) {
         if (d.vec) {
-          pw_tile_one_vec<F>(ptrs, f, d, t0, t1, smem_words);
+          pw_tile_one_vec<F>(ptrs, f, d, t0, t1, &smem[0][0]);
           continue;
         }
       }
@@ -825,13 +706,16 @@ __global__ void __launch_bounds__(kBlock)
     pw_strided_kernel(PwPtrs<PwTraits<F>::NT> ptrs, F f, StridedDesc<PwTraits<F>::NT, IDX> d, i64 n) {
   pw_strided_body<F, U, IDX>(ptrs, f, d, n);
 }
-// CTAs per SM the tile kernels are compiled for: the pipelined one-input kernel keeps a second
-// tile in registers (64 registers, 4 CTAs); two-input functors get the same budget and larger ones
-// 80 registers (3 CTAs), which is what they need to stay clear of spills.
-__host__ __device__ constexpr int tile_min_ctas(int nin) { return nin == 1 ? kTilePersistCtas : (nin == 2 ? 4 : 3); }
+// CTAs per SM the tile kernels are compiled for: the pipelined kernel keeps a second tile in
+// registers (64 registers, 4 CTAs); one-input kernels otherwise fit 48 registers (5 CTAs),
+// two-input ones get 64 and larger ones 80 (3 CTAs), which keeps all of them clear of spills.
+template <class F>
+__host__ __device__ constexpr int tile_min_ctas() {
+  return TilePipelined<F>::value ? kTilePersistCtas : (F::NIN <= 1 ? 5 : (F::NIN == 2 ? 4 : 3));
+}
 
 template <class F>
-__global__ void __launch_bounds__(kTileX* kPwRows, tile_min_ctas(F::NIN))
+__global__ void __launch_bounds__(kTileX* kPwRows, tile_min_ctas<F>())
     pw_tile_kernel(PwPtrs<PwTraits<F>::NT> ptrs, F f, TileDesc<PwTraits<F>::NT> d) {
   pw_tile_body<F>(ptrs, f, d);
 }
