@@ -256,7 +256,7 @@ def run_reference_arm(args) -> None:
 
 def workload_config(n_gpus: int, depth: int) -> dict:
     cfg = {"workload": "cfg5: y=relu(silu(a+b)+c); m=(y==0)&(a!=0); masked_select(a,m) over 64 x f32[4096,4096]; "
-                       "`value` = C ABI calls twg_fused_launch + twg_masked_select_f32 + count exchange per step, "
+                       "`value` = C ABI calls twg_fused_launch + twg_masked_select_f32_publish + twg_exchange_collect per step, "
                        "`public_api` / `e2e` = the same through torch.compile(backend=webgpu_backend)",
            "global_batch": BATCH, "elements_per_step": BATCH * SLAB, "parallelism": f"batch-sharded x{n_gpus}",
            "l2": "inputs (>= 1.5 GiB per rank) are larger than the 126 MB L2; no flush needed"}
@@ -426,6 +426,25 @@ def per_op_table(abi, stream, peak: float) -> dict:
     ms = time_op(abi, stream, run, iters=10)
     k = int(res.download(np.int64, 2, stream)[0])
     put("masked_select_rowmask_16384x1", 4 * n2 + r + 4 * k, ms, f"k={k}; broadcast mask through the strided path")
+
+    # the chain's mask kernel: the ahead-of-time instantiation beside the same chain with a constant
+    # changed in the last place, which no ahead-of-time program matches and NVRTC compiles at run time
+    g = torch.Generator().manual_seed(4)
+    for buf in (dx, dy):
+        buf.upload(torch.randn(n2, generator=g).numpy(), stream)
+    dc0 = abi.DeviceBuffer(4 * n2)
+    dc0.upload(torch.randn(n2, generator=g).numpy(), stream)
+    d4 = dense_desc(4, n2)
+    chain_ptrs = (ctypes.c_void_p * 4)(dm.ptr, dx.ptr, dy.ptr, dc0.ptr)
+    jit_prog = [list(i) for i in abi.CHAIN_MASK_PROGRAM]
+    jit_prog[3][3] = float(np.nextafter(np.float32(1.0), np.float32(2.0)))   # alpha of the first add
+    for name, prog in (("chain_mask_aot_2^28", abi.CHAIN_MASK_PROGRAM), ("chain_mask_nvrtc_2^28", [tuple(i) for i in jit_prog])):
+        handle = abi.fused_compile(prog)
+        kind = abi.fused_kind(handle)
+        put(name, 13 * n2, time_op(abi, stream, lambda: abi.check(
+            L.twg_fused_launch(handle, ctypes.byref(d4), chain_ptrs, stream))), f"kernel kind: {kind}")
+        abi.check(L.twg_fused_release(handle))
+    del dc0
 
     # predicate + select: mask kernel then masked_select (two launches) against the one-launch form
     g = torch.Generator().manual_seed(4)
@@ -714,8 +733,8 @@ def run_gpu_arm(args) -> None:
     seq_next = [1]
 
     def launch(i: int | None) -> int:
-        """Everything one step puts on the GPU: fused chain and compaction on the compute stream,
-        the publication of this rank's count to every rank, and (second stream) the kernel that
+        """Everything one step puts on the GPU: fused chain and compaction (which also publishes this
+        rank's count to every rank) on the compute stream, and on a second stream the kernel that
         gathers all ranks' counts for the host."""
         t_issue = time.perf_counter()
         seq = seq_next[0]
@@ -726,9 +745,9 @@ def run_gpu_arm(args) -> None:
         abi.check(L.twg_fused_launch(program, ctypes.byref(desc4), ptrs, stream))
         if i is not None:
             ev.record(3 + 2 * i, stream)
-        abi.check(L.twg_masked_select_f32(ctypes.byref(desc2), dev_in[0].ptr, d_mask.ptr, d_out[slot].ptr,
-                                          d_res[slot].ptr, d_ws[slot].ptr, ws_bytes, stream))
-        xchg.publish(seq, d_res[slot].ptr, stream)
+        # compaction; its last chunk stores this rank's count into every rank's mailbox
+        xchg.masked_select_publish(seq, desc2, dev_in[0].ptr, d_mask.ptr, d_out[slot].ptr, d_res[slot].ptr,
+                                   d_ws[slot].ptr, ws_bytes, stream)
         compacted.record(slot, stream)
         abi.check(L.twg_event_wait(compacted.ev[slot], side))
         xchg.collect(seq, side)

@@ -337,6 +337,13 @@ int twg_exchange_connect_ipc(void* xchg, int peer_rank, const void* handle64);
 int twg_exchange_connect_local(void* xchg, int peer_rank, void* peer_xchg);
 int twg_exchange_publish(void* xchg, int64_t seq, const int64_t* result_dev, void* stream);
 int twg_exchange_collect(void* xchg, int64_t seq, void* stream);
+/* twg_masked_select_f32 and twg_exchange_publish as ONE call: the compaction kernel's last chunk,
+ * which knows the total, stores {count, seq, status} into every rank's mailbox itself, so the
+ * exchange costs no launch of its own.  (Layouts that the chunked kernel does not serve, and empty
+ * inputs, get the publish kernel behind the compaction - same effect.)  Arguments as the two calls. */
+int twg_masked_select_f32_publish(const TwgIterDesc* desc, const float* src, const uint8_t* mask, float* out,
+                                  int64_t* result_dev, void* workspace, size_t workspace_bytes, void* xchg, int64_t seq,
+                                  void* stream);
 int twg_exchange_wait(void* xchg, int64_t seq, int64_t* counts, int64_t* statuses, int64_t* offset, int64_t* total,
                       int timeout_ms);
 /* Device copy of the record of `seq`: int64[2*nranks + 2] = counts, statuses, offset, total; valid

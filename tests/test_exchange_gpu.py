@@ -76,6 +76,45 @@ def test_three_ranks_on_one_device_exchange_in_stream_order(abi):
             x.close()
 
 
+@pytest.mark.parametrize("n", [0, 5, 4096 * 3 + 17, (1 << 22) + 3])
+def test_compaction_publishes_its_own_count(abi, n):
+    """twg_masked_select_f32_publish: the compaction's last chunk writes the mailboxes itself (the
+    publish kernel is only used for empty inputs and for layouts of the one-tile-per-CTA kernel)."""
+    from torch_webgpu.sharding import PeerStoreExchange
+    L = abi.lib()
+    world = 3
+    xs = [PeerStoreExchange(abi, r, world, ring=4) for r in range(world)]
+    try:
+        for x in xs:
+            x.connect_local(xs)
+        rng = np.random.default_rng(n + 1)
+        for seq in (1, 2):
+            expect, keep = [], []
+            for r, x in enumerate(xs):
+                src = rng.standard_normal(n).astype(np.float32)
+                mask = rng.random(n) < (0.2 + 0.3 * r)
+                dsrc, dmask = abi.DeviceArray(src), abi.DeviceArray(mask.view(np.uint8))
+                out, res = abi.DeviceBuffer(max(4 * n, 4)), abi.DeviceBuffer(16)
+                ws_bytes = L.twg_masked_select_workspace_bytes(n)
+                ws = abi.DeviceBuffer(max(ws_bytes, 256))
+                d = abi.IterDesc()
+                abi.check(L.twg_iter_contiguous(ctypes.byref(d), 2, n))
+                L.twg_reset_launch_count()
+                x.masked_select_publish(seq, d, dsrc.ptr, dmask.ptr, out.ptr, res.ptr, ws.ptr, ws_bytes, None)
+                assert L.twg_launch_count() == 2        # clear + compaction, or clear + publish for the empty input
+                expect.append(oracle.masked_select(src, mask))
+                keep.append((dsrc, dmask, out, res, ws))
+            for x in xs:
+                x.collect(seq, None)
+            for r, x in enumerate(xs):
+                counts, offset, total = x.wait(seq, timeout_ms=5000)
+                assert counts == [e.size for e in expect] and offset == sum(counts[:r]) and total == sum(counts)
+                assert_bit_equal(keep[r][2].download(np.float32, counts[r]), expect[r], f"rank {r} values")
+    finally:
+        for x in xs:
+            x.close()
+
+
 def test_a_device_status_travels_with_the_count(abi):
     from torch_webgpu.sharding import PeerStoreExchange
     xs = [PeerStoreExchange(abi, r, 2, ring=2) for r in range(2)]

@@ -385,6 +385,21 @@ static int xchg_ready(Xchg* x, const char* who) {
   return TWG_OK;
 }
 
+namespace twg {
+int xchg_publish_slots(void* xchg, int64_t seq, MsPublish* out) {
+  Xchg* x = as_xchg(xchg);
+  TWG_REQUIRE(x != nullptr && out != nullptr, "count exchange: not an exchange object");
+  TWG_REQUIRE(seq >= 1 && seq < (int64_t(1) << 55), "count exchange: sequence numbers start at 1 (got %lld)", (long long)seq);
+  if (int rc = xchg_ready(x, "count exchange")) return rc;
+  const int slot = (int)(seq % x->ring);
+  for (int r = 0; r < kXchgMaxRanks; ++r)
+    out->slot[r] = r < x->nranks ? x->peer[r] + ((size_t)slot * x->nranks + x->rank) * 2 : nullptr;
+  out->nranks = x->nranks;
+  out->seq = (u64)seq;
+  return TWG_OK;
+}
+}  // namespace twg
+
 extern "C" int twg_exchange_publish(void* xchg, int64_t seq, const int64_t* result_dev, void* stream) {
   Xchg* x = as_xchg(xchg);
   TWG_REQUIRE(x != nullptr && result_dev != nullptr, "twg_exchange_publish: bad argument");

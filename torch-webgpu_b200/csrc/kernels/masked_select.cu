@@ -1,16 +1,16 @@
 // masked_select as a single-pass stream compaction.
 //
-// One CTA owns a run of consecutive logical elements (a chunk of tiles on the dense path, one tile
-// on the strided path).  Inside a tile, selected elements are ranked with popc on the packed mask
-// bytes plus a warp scan (dense path) or with warp ballots (strided path); the run's base offset in
-// the output comes from a decoupled look-back over the preceding runs' published counts, so one
-// launch does everything, src is read exactly once and no global scan kernel is needed.  Selected values are first packed into shared memory in output order and
-// then written as contiguous runs.
+// One CTA owns a run of consecutive logical elements (a chunk of tiles in the chunked kernel, one
+// tile in the kernel for 64-bit offsets).  Selected elements are ranked with popc on mask words
+// that are warp ballots of 32 consecutive elements; the run's base offset in the output comes from
+// a decoupled look-back over the preceding runs' published counts, so one launch does everything,
+// src is read exactly once and no global scan kernel is needed.  Selected values are first packed
+// into shared memory in output order and then written as contiguous, aligned runs.
 //
-// Forward progress: a tile's index is a ticket drawn from a global counter when its CTA starts,
-// not blockIdx, so every tile a CTA may wait for belongs to a CTA that is already running.  The
-// wait is nevertheless bounded: after `poll_budget` polls the tile gives up, records
-// TWG_ERR_TIMEOUT in result[1], publishes a prefix so that later tiles do not wait on it, and the
+// Forward progress: a run's index is a ticket drawn from a global counter when its CTA starts,
+// not blockIdx, so every run a CTA may wait for belongs to a CTA that is already running.  The
+// wait is nevertheless bounded: after `poll_budget` polls the run gives up, records
+// TWG_ERR_TIMEOUT in result[1], publishes a prefix so that later runs do not wait on it, and the
 // kernel drains normally.
 #include "twg_launch.cuh"
 #include "twg_compact.cuh"
@@ -38,31 +38,31 @@ struct MsShared {
 };
 
 // ------------------------------------------------------------------------------------------
-// Dense path: src contiguous and 16-byte aligned; the mask is either a dense bool array (16-byte
-// aligned) or, with ROWMASK, one bool per row of `row_len` elements (a [R,1] mask broadcast over
-// [R,C] with C % 4 == 0).  A third mode walks both operands through the iteration descriptor
-// (element index -> offsets with 32-bit multiply-shift division): slices, broadcast masks and
-// other non-dense layouts get the same chunking, at one index computation per mask byte and per
-// selected element.
+// The chunked kernel.  src contiguous and 16-byte aligned; the mask is either a dense bool array
+// (16-byte aligned) or, with kMsRowMask, one bool per row of `row_len` elements (a [R,1] mask
+// broadcast over [R,C] with C % 4 == 0).  A third mode walks both operands through the iteration
+// descriptor (element index -> offsets with 32-bit multiply-shift division): slices, broadcast
+// masks and other non-dense layouts get the same chunking, at one index computation per mask byte
+// and per selected element.
 //
-// A CTA owns a chunk of CH consecutive tiles of 4096 elements.
-//   Phase A  reads the chunk's mask (1 byte per element), keeps it in shared memory packed to one
-//            bit per element, and counts the selected elements of every warp span (512 elements)
-//            of every tile.  The chunk count is published at once: the chain of dependent CTAs has
-//            one link per chunk, not per tile, and its latency is amortised over CH tiles.
-//   Phase B  With the table of phase A each warp knows where its run of every tile starts inside
-//            the chunk before it has looked at a single src value, so there is no barrier and no
-//            exchange between warps: a warp loads its span (src quads whose four mask bits are
-//            all zero are never fetched; the next tile's loads are issued before the current one
-//            is ranked), ranks it with popc + a warp scan, stages into its own 2 KB region and
-//            writes its run out, tile after tile.  The look-back is resolved as late as possible
-//            - after tile 0 is staged, right before its flush - so that most predecessors have
-//            published by then; the two barriers around it are the only CTA-wide ones.
-// In a tile a warp covers 512 consecutive elements as 4 sub-rounds of 32 quads; lane l owns quad
-// j*32+l of sub-round j, so src is read as 512-byte runs.  HBM sees every mask byte and every
-// selected sector of src once.  (An earlier form ranked across the eight warps of a tile with two
-// barriers per tile; ncu showed it issue-bound at 31 instructions per element with the barrier
-// among the top stalls.  Measured, 2^30 elements at 41 % density: 1.246 ms -> 1.197 ms.)
+// A CTA owns a chunk of CH consecutive tiles of 4096 elements; warp w owns the CH consecutive
+// spans (512 elements each) [w CH, (w + 1) CH) of it, so its output is one contiguous run.
+//   Phase A  turns the chunk's mask into one bit per element in shared memory and counts the
+//            selected elements of every span.  In the dense mode every warp does this for its own
+//            stretch and starts fetching its first span right away.  The chunk count is published
+//            at once: the chain of dependent CTAs has one link per chunk, and warp 0 resolves it
+//            while those first loads are in flight.
+//   Phase B  Lane l owns elements 32 k + l (k = 0..15) of a span: a warp-wide access is one
+//            128-byte run, word k of the span's bits is the selection bitmap of row k, and popc of
+//            its low bits is a lane's rank in the row - consecutive selected lanes get consecutive
+//            stage slots, so the staging stores are free of bank conflicts whatever the density.
+//            The staged run leaves as aligned 128-bit vectors; spans that select everything are
+//            copied straight from registers; the next span's loads are in flight while the current
+//            one is ranked and written out.
+// HBM sees every mask byte once and every selected sector of src once.  (Earlier forms, measured
+// on 2^27 elements at 41 % density: eight warps ranking a tile together with two barriers per tile
+// 169.7 us; lanes owning quads of four consecutive elements with a packed warp scan 165.8 us and
+// 32 instructions per element; this form 149.5 us and 20.)
 // ------------------------------------------------------------------------------------------
 // four arbitrary bytes -> four 0/1 bytes (non-zero counts as true): the carry of (b & 0x7f) + 0x7f
 // reaches bit 7 exactly when the low seven bits are non-zero
@@ -156,10 +156,26 @@ struct MsSpanRegs {
   u32 v[16];
 };
 
+// The compaction's last chunk knows the total; when a count exchange rides along, the thread that
+// writes it also stores {count, sequence | status} into this rank's slot of every rank's mailbox -
+// plain stores to peer memory over NVLink, the flag word with release semantics at system scope -
+// so the exchange costs no launch of its own.  A status written by a chunk that gave up waiting is
+// fenced before that chunk's prefix becomes visible, so it is seen here.
+__device__ __forceinline__ void ms_publish(const MsPublish& pub, i64 count, const i64* result) {
+  if (pub.nranks == 0) return;
+  __threadfence();
+  const u64 status = (u64)(*reinterpret_cast<const volatile i64*>(result + 1)) & 0xffull;
+  for (int r = 0; r < pub.nranks; ++r) {
+    u64* p = pub.slot[r];
+    p[0] = (u64)count;
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p + 1), "l"((pub.seq << 8) | status) : "memory");
+  }
+}
+
 template <int CH, int MODE>
 __global__ void __launch_bounds__(kMsThreads, 4)
     ms_dense_kernel(const float* src, const u8* mask, float* out, i64 n, i64 nchunks, u64* ticket, u64* desc,
-                     i64* result, i64 poll_budget, FastDiv32 row_len, StridedDesc<2, u32> sd) {
+                     i64* result, i64 poll_budget, FastDiv32 row_len, StridedDesc<2, u32> sd, MsPublish pub) {
   constexpr bool ROWMASK = MODE == kMsRowMask;
   constexpr int kSpans = CH * kMsWarps;  // spans of 512 elements in a chunk
   __shared__ MsDenseShared<CH> sm;
@@ -309,7 +325,10 @@ __global__ void __launch_bounds__(kMsThreads, 4)
       const i64 excl = lookback_resolve(chunk, chunk_total, desc, result, poll_budget);
       if (lane == 0) {
         sm.excl = excl;
-        if (chunk == nchunks - 1) result[0] = excl + (i64)chunk_total;
+        if (chunk == nchunks - 1) {
+          result[0] = excl + (i64)chunk_total;
+          ms_publish(pub, excl + (i64)chunk_total, result);
+        }
       }
     }
     __syncthreads();
@@ -355,7 +374,10 @@ __global__ void __launch_bounds__(kMsThreads, 4)
     const i64 excl = lookback_resolve(chunk, chunk_total, desc, result, poll_budget);
     if (lane == 0) {
       sm.excl = excl;
-      if (chunk == nchunks - 1) result[0] = excl + (i64)chunk_total;
+      if (chunk == nchunks - 1) {
+        result[0] = excl + (i64)chunk_total;
+        ms_publish(pub, excl + (i64)chunk_total, result);
+      }
     }
   }
   __syncthreads();
@@ -534,9 +556,9 @@ long long ms_poll_budget() { return g_poll_budget.load(); }
 template <int MODE>
 static void launch_dense(int chunk_tiles, unsigned nchunks, cudaStream_t s, const float* src, const u8* mask, float* out,
                          i64 n, u64* ticket, u64* tdesc, i64* result, i64 budget, FastDiv32 row_len,
-                         const StridedDesc<2, u32>& sd) {
+                         const StridedDesc<2, u32>& sd, const MsPublish& pub) {
 #define TWG_MS_LAUNCH(CH) \
-  ms_dense_kernel<CH, MODE><<<nchunks, kMsThreads, 0, s>>>(src, mask, out, n, nchunks, ticket, tdesc, result, budget, row_len, sd)
+  ms_dense_kernel<CH, MODE><<<nchunks, kMsThreads, 0, s>>>(src, mask, out, n, nchunks, ticket, tdesc, result, budget, row_len, sd, pub)
   switch (chunk_tiles) {
     case 1: TWG_MS_LAUNCH(1); break;
     case 2: TWG_MS_LAUNCH(2); break;
@@ -563,10 +585,15 @@ extern "C" int twg_masked_select_set_poll_budget(int64_t polls) {
   return TWG_OK;
 }
 
-extern "C" int twg_masked_select_f32(const TwgIterDesc* desc, const float* src, const uint8_t* mask, float* out,
-                                     int64_t* result_dev, void* workspace, size_t workspace_bytes, void* stream) {
+// `fused_publish` in: the caller wants this rank's count published to `pub`; out: whether the
+// compaction kernel did it (false: the caller launches the publish kernel behind this call).
+static int masked_select_impl(const TwgIterDesc* desc, const float* src, const uint8_t* mask, float* out,
+                              int64_t* result_dev, void* workspace, size_t workspace_bytes, void* stream,
+                              const MsPublish& pub_in, bool* fused_publish) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   g_last_path = kPathNone;
+  MsPublish pub = pub_in;
+  if (fused_publish) *fused_publish = false;
   if (int rc = check_desc(desc, 2)) return rc;
   TWG_REQUIRE(result_dev != nullptr, "twg_masked_select_f32: result_dev is null");
   const int64_t n = desc->numel;
@@ -607,10 +634,11 @@ extern "C" int twg_masked_select_f32(const TwgIterDesc* desc, const float* src, 
     StridedDesc<2, u32> sd;
     std::memset(&sd, 0, sizeof(sd));
     if (strided32) fill_strided_desc<2>(d, &sd);
-    if (dense) launch_dense<kMsDense>(chunk_tiles, (unsigned)ntiles, s, src, mask, out, n, ticket, tdesc, result, budget, row_len, sd);
-    else if (rowmask) launch_dense<kMsRowMask>(chunk_tiles, (unsigned)ntiles, s, src, mask, out, n, ticket, tdesc, result, budget, row_len, sd);
-    else launch_dense<kMsStrided>(chunk_tiles, (unsigned)ntiles, s, src, mask, out, n, ticket, tdesc, result, budget, row_len, sd);
+    if (dense) launch_dense<kMsDense>(chunk_tiles, (unsigned)ntiles, s, src, mask, out, n, ticket, tdesc, result, budget, row_len, sd, pub);
+    else if (rowmask) launch_dense<kMsRowMask>(chunk_tiles, (unsigned)ntiles, s, src, mask, out, n, ticket, tdesc, result, budget, row_len, sd, pub);
+    else launch_dense<kMsStrided>(chunk_tiles, (unsigned)ntiles, s, src, mask, out, n, ticket, tdesc, result, budget, row_len, sd, pub);
     TWG_CHECK_LAUNCH();
+    if (fused_publish) *fused_publish = pub.nranks != 0;
     g_last_path = strided32 ? kPathStrided32 : kPathDense;
     return TWG_OK;
   }
@@ -631,6 +659,26 @@ extern "C" int twg_masked_select_f32(const TwgIterDesc* desc, const float* src, 
     TWG_CHECK_LAUNCH();
     g_last_path = kPathStrided64;
   }
+  return TWG_OK;
+}
+
+extern "C" int twg_masked_select_f32(const TwgIterDesc* desc, const float* src, const uint8_t* mask, float* out,
+                                     int64_t* result_dev, void* workspace, size_t workspace_bytes, void* stream) {
+  MsPublish none;
+  std::memset(&none, 0, sizeof(none));
+  return masked_select_impl(desc, src, mask, out, result_dev, workspace, workspace_bytes, stream, none, nullptr);
+}
+
+extern "C" int twg_masked_select_f32_publish(const TwgIterDesc* desc, const float* src, const uint8_t* mask, float* out,
+                                             int64_t* result_dev, void* workspace, size_t workspace_bytes, void* xchg,
+                                             int64_t seq, void* stream) {
+  MsPublish pub;
+  std::memset(&pub, 0, sizeof(pub));
+  if (int rc = xchg_publish_slots(xchg, seq, &pub)) return rc;
+  bool fused = false;
+  if (int rc = masked_select_impl(desc, src, mask, out, result_dev, workspace, workspace_bytes, stream, pub, &fused)) return rc;
+  // layouts served by the one-tile-per-CTA kernel, and empty inputs: the publish kernel behind the compaction
+  if (!fused) return twg_exchange_publish(xchg, seq, result_dev, stream);
   return TWG_OK;
 }
 

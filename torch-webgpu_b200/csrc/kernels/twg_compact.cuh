@@ -78,7 +78,10 @@ __device__ __forceinline__ i64 lookback_resolve(i64 tile, u32 tile_total, u64* d
   }
   if (timed_out) {
     excl = 0;
-    if (lane == 0) result[1] = (i64)kErrTimeout;
+    if (lane == 0) {
+      result[1] = (i64)kErrTimeout;
+      __threadfence();  // the status is visible before the prefix that lets later runs finish
+    }
   }
   if (lane == 0) st_relaxed_u64(desc + tile, kMsPrefix | ((excl + (u64)tile_total) & kMsValueMask));
   return (i64)excl;
@@ -149,7 +152,10 @@ __device__ __forceinline__ i64 lookback_resolve_deep(i64 tile, u32 tile_total, u
   }
   if (timed_out) {
     excl = 0;
-    if (lane == 0) result[1] = (i64)kErrTimeout;
+    if (lane == 0) {
+      result[1] = (i64)kErrTimeout;
+      __threadfence();  // the status is visible before the prefix that lets later runs finish
+    }
   }
   if (lane == 0) st_relaxed_u64(desc + tile, kMsPrefix | ((excl + (u64)tile_total) & kMsValueMask));
   return (i64)excl;

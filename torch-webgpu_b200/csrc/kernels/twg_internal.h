@@ -42,6 +42,14 @@ int check_desc(const TwgIterDesc* d, int ntensors);
 int64_t max_offset(const TwgIterDesc& d, int t);
 // Settings of the look-back shared by masked_select and the fused select (masked_select.cu).
 long long ms_poll_budget();
+// Where the last chunk of a compaction stores this rank's {count, sequence | status} for the count
+// exchange: this rank's slot of every rank's mailbox (comm.cu fills it, masked_select.cu uses it).
+struct MsPublish {
+  unsigned long long* slot[TWG_EXCHANGE_MAX_RANKS];
+  int nranks;  // 0: no publication
+  unsigned long long seq;
+};
+int xchg_publish_slots(void* xchg, int64_t seq, MsPublish* out);
 // Zero a compaction workspace prefix and the two result words with one kernel (masked_select.cu).
 int ms_clear(void* workspace, size_t nbytes, int64_t* result, cudaStream_t s);
 // After coalescing: every one of the first `nt` operands is one contiguous run (copy.cu).

@@ -130,6 +130,8 @@ SIGNATURES = {
     "twg_exchange_connect_local": (c_int, [c_void_p, c_int, c_void_p]),
     "twg_exchange_publish": (c_int, [c_void_p, c_int64, c_void_p, c_void_p]),
     "twg_exchange_collect": (c_int, [c_void_p, c_int64, c_void_p]),
+    "twg_masked_select_f32_publish": (c_int, [POINTER(IterDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                              c_size_t, c_void_p, c_int64, c_void_p]),
     "twg_exchange_wait": (c_int, [c_void_p, c_int64, POINTER(c_int64), POINTER(c_int64), POINTER(c_int64),
                                   POINTER(c_int64), c_int]),
     "twg_exchange_gathered": (c_int, [c_void_p, c_int64, POINTER(c_void_p)]),

@@ -157,6 +157,12 @@ class PeerStoreExchange:
     def publish(self, seq: int, result_ptr: int, stream) -> None:
         self.abi.check(self.abi.lib().twg_exchange_publish(self.handle, seq, result_ptr, stream))
 
+    def masked_select_publish(self, seq: int, desc, src_ptr: int, mask_ptr: int, out_ptr: int, result_ptr: int,
+                              ws_ptr: int, ws_bytes: int, stream) -> None:
+        """masked_select whose last chunk publishes this rank's count itself (one launch less)."""
+        self.abi.check(self.abi.lib().twg_masked_select_f32_publish(
+            ctypes.byref(desc), src_ptr, mask_ptr, out_ptr, result_ptr, ws_ptr, ws_bytes, self.handle, seq, stream))
+
     def collect(self, seq: int, stream) -> None:
         self.abi.check(self.abi.lib().twg_exchange_collect(self.handle, seq, stream))
 
@@ -211,6 +217,12 @@ class NcclExchange:
 
     def publish(self, seq: int, result_ptr: int, stream) -> None:
         self._pending[seq] = result_ptr
+
+    def masked_select_publish(self, seq: int, desc, src_ptr: int, mask_ptr: int, out_ptr: int, result_ptr: int,
+                              ws_ptr: int, ws_bytes: int, stream) -> None:
+        self.abi.check(self.abi.lib().twg_masked_select_f32(ctypes.byref(desc), src_ptr, mask_ptr, out_ptr, result_ptr,
+                                                            ws_ptr, ws_bytes, stream))
+        self.publish(seq, result_ptr, stream)
 
     def collect(self, seq: int, stream) -> None:
         L, slot = self.abi.lib(), seq % self.ring
