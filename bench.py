@@ -377,9 +377,11 @@ def per_op_table(abi, stream, peak: float) -> dict:
     # true transpose: input viewed as [16384,16384].t(), dense output
     r = 16384
     dt = abi.make_desc((r, r), [((r, r), (r, 1)), ((r, r), (1, r))])
+    # (output in the buffer next to the input: with a 64 KiB row pitch the throughput of a transpose
+    # depends on how far apart the two operands lie - 1 GiB here, 2 GiB costs about 5 %)
     for name, op in (("relu", 1), ("silu", 3), ("gelu_erf", 4)):
         put(f"{name}_transposed_into_dense", 8 * n2, time_op(abi, stream, lambda op=op: abi.check(
-            L.twg_unary_f32(op, ctypes.byref(dt), dx.ptr, dz.ptr, stream)), iters=10), "2-D tile kernel")
+            L.twg_unary_f32(op, ctypes.byref(dt), dx.ptr, dy.ptr, stream)), iters=10), "2-D tile kernel")
     ds = abi.make_desc((r, r // 2), [((r, r // 2), (r // 2, 1)), ((r, r // 2), (r, 2))])
     put("relu_stride2_slice", 8 * (n2 // 2), time_op(abi, stream, lambda: abi.check(
         L.twg_unary_f32(1, ctypes.byref(ds), dx.ptr, dz.ptr, stream)), iters=10),

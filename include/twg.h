@@ -110,6 +110,13 @@ int twg_block_size(void* ptr, size_t* nbytes, int* device);
 int twg_empty_cache(int device);                           /* device < 0: all devices; blocks */
 int twg_memory_stats(int device, TwgMemStats* stats);
 int twg_reset_peak_stats(int device);
+/* Debugging aid (the pool offers no memory checker): while enabled, every block allocated from then
+ * on carries at least 512 guard bytes behind the caller's, filled with a pattern.
+ * twg_check_guard_words (blocks: synchronises the device, reads every live guarded block's guard)
+ * reports how many blocks have had their guard overwritten and the lowest such block's address.
+ * A write that lands in the guard stays inside the block, so nothing faults.  Off by default. */
+int twg_set_guard_words(int enabled);
+int twg_check_guard_words(int device, int64_t* corrupted_blocks, void** first_block);
 /* Host-side fault injection for tests: cap on reserved bytes per device (0 = no cap). */
 int twg_set_memory_budget(int device, size_t max_reserved_bytes);
 
@@ -289,6 +296,14 @@ int twg_fused_select_f32(const TwgFusedProgram* p, int src_input, int64_t numel,
 /* Path of the NVRTC shared library to load on first use (default: the loader's search path for
  * libnvrtc.so.12, then /usr/local/cuda/lib64).  Honoured only before the first NVRTC build. */
 int twg_fused_set_nvrtc_path(const char* path);
+/* Directory for an on-disk cache of NVRTC results (one file per program, keyed by a hash of the
+ * generated source, the device headers and the library version; written atomically, safe to share
+ * between processes).  NULL or "" turns the cache off, which is the default unless TWG_CACHE_DIR
+ * is set in the environment when the library is first used.  The reference compiles its WGSL on
+ * every process start and keeps pipelines in a per-process map (csrc/ops/binary.cpp:23-54). */
+int twg_fused_set_cache_dir(const char* dir);
+/* Programs served from / added to that directory by this process. */
+int twg_fused_cache_stats(int64_t* hits, int64_t* misses);
 /* Generated CUDA source of a program (ahead-of-time programs report the same text NVRTC would
  * be given); the pointer stays valid until twg_fused_release. */
 int twg_fused_source(const TwgFusedProgram* p, const char** source);
@@ -352,6 +367,13 @@ int twg_exchange_gathered(void* xchg, int64_t seq, const int64_t** dev_record);
 /* Time limit of the collect kernel's wait (default 2 s; <= 0 restores the default). */
 int twg_exchange_set_timeout_ns(void* xchg, int64_t timeout_ns);
 int twg_exchange_destroy(void* xchg);   /* blocks */
+
+/* ---- tracing: NVTX ranges named after the entry points around the compute, copy and exchange
+ *      calls, so that a profiler's timeline shows which library call a kernel or copy belongs to.
+ *      Off by default (TWG_NVTX=1 in the environment turns it on at first use); without a profiler
+ *      attached a range costs a function call.  The reference has no tracing. */
+int twg_set_tracing(int enabled);
+int twg_get_tracing(void);
 
 /* ---- launch accounting: number of kernels this library launched on the calling thread's
  *      behalf since the last reset (all threads), used by the benchmark's gpu_launches ----- */

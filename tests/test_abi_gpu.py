@@ -550,6 +550,48 @@ def test_fused_programs_are_reference_counted(abi):
     assert_bit_equal(y2, y, "after recompilation")
 
 
+def test_nvrtc_results_are_cached_on_disk(abi, tmp_path):
+    """With a cache directory set, a program NVRTC has compiled once is loaded from its file the
+    next time (here: after its last handle was released, which frees the in-memory copy)."""
+    F = abi
+    L = abi.lib()
+    import ctypes
+    prog = [(F.F_INPUT_F32, 0, 0, 0.0), (F.F_CONST_F32, 0, 0, 0.8125), (F.F_MUL, 0, 1, 0.0), (F.F_RELU, 2, 0, 0.0),
+            (F.F_OUTPUT, 3, 0, 0.0)]
+    x = rnd(7000, 94)
+    hits, misses = ctypes.c_int64(), ctypes.c_int64()
+    abi.check(L.twg_fused_set_cache_dir(str(tmp_path).encode()))
+    try:
+        abi.check(L.twg_fused_cache_stats(ctypes.byref(hits), ctypes.byref(misses)))
+        h0, m0 = hits.value, misses.value
+        (y1,), kind = abi.fused(prog, [x], [np.float32])
+        assert kind == "nvrtc"
+        abi.check(L.twg_fused_cache_stats(ctypes.byref(hits), ctypes.byref(misses)))
+        assert (hits.value, misses.value) == (h0, m0 + 1)
+        files = list(tmp_path.glob("twg_*.cubin"))
+        assert len(files) == 1 and files[0].stat().st_size > 1000 and not list(tmp_path.glob("*.tmp.*"))
+        handle = abi.fused_compile(prog)                     # same process: the in-memory cache, no file access
+        abi.check(L.twg_fused_cache_stats(ctypes.byref(hits), ctypes.byref(misses)))
+        assert (hits.value, misses.value) == (h0, m0 + 1)
+        abi.check(L.twg_fused_release(handle))
+        abi.check(L.twg_fused_release(handle))               # abi.fused's reference: the program is gone now
+        (y2,), kind = abi.fused(prog, [x], [np.float32])     # compiled "again": served from the file
+        abi.check(L.twg_fused_cache_stats(ctypes.byref(hits), ctypes.byref(misses)))
+        assert kind == "nvrtc" and (hits.value, misses.value) == (h0 + 1, m0 + 1)
+        assert_bit_equal(y2, y1, "cubin from the disk cache")
+        assert_bit_equal(y1, np.maximum(x * np.float32(0.8125), 0), "relu(0.8125 x)")
+        files[0].write_bytes(files[0].read_bytes()[:100])    # a damaged file is ignored and rewritten
+        handle = abi.fused_compile(prog)
+        abi.check(L.twg_fused_release(handle))
+        abi.check(L.twg_fused_release(handle))
+        (y3,), _ = abi.fused(prog, [x], [np.float32])
+        abi.check(L.twg_fused_cache_stats(ctypes.byref(hits), ctypes.byref(misses)))
+        assert (hits.value, misses.value) == (h0 + 1, m0 + 2) and files[0].stat().st_size > 1000
+        assert_bit_equal(y3, y1, "after the damaged file")
+    finally:
+        abi.check(L.twg_fused_set_cache_dir(None))
+
+
 def test_fused_select_on_the_decision_boundary_of_the_chain(abi):
     """Inputs placed on and next to the boundary silu(a + b) + c == 0, huge and non-finite values:
     the one-launch form must select exactly what the chain's mask says."""
@@ -696,6 +738,36 @@ def test_allocator_caches_splits_trims_and_reports(abi):
     assert s4.reserved_bytes <= s0.reserved_bytes
     assert abi.DeviceBuffer(0).ptr == 0
     assert L.twg_free(12345) == abi.TWG_ERR_INVALID
+
+
+def test_guard_words_report_a_write_past_the_end(abi):
+    """With guard words on, bytes behind a block's requested size carry a pattern; a write that runs
+    a few bytes over (still inside the block: nothing faults) is found by the check."""
+    import ctypes
+    L = abi.lib()
+    bad, first = ctypes.c_int64(), ctypes.c_void_p()
+    abi.check(L.twg_set_guard_words(1))
+    try:
+        a = abi.DeviceBuffer(1000)
+        b = abi.DeviceBuffer(3 << 20)
+        abi.check(L.twg_memset(a.ptr, 0, 1000, None))                 # exactly what was asked for
+        x = rnd(1 << 18, 95)
+        assert_bit_equal(abi.unary("relu", x), oracle.unary("relu", x), "relu with guarded blocks")
+        abi.check(L.twg_check_guard_words(0, ctypes.byref(bad), ctypes.byref(first)))
+        assert bad.value == 0 and first.value is None
+        abi.check(L.twg_memset(b.ptr + (3 << 20) - 8, 0, 12, None))   # four bytes too many
+        abi.check(L.twg_check_guard_words(0, ctypes.byref(bad), ctypes.byref(first)))
+        assert bad.value == 1 and first.value == b.ptr
+        abi.check(L.twg_trim(a.ptr, 100))                             # guarded blocks keep their tail
+        size = ctypes.c_size_t()
+        abi.check(L.twg_block_size(a.ptr, ctypes.byref(size), None))
+        assert size.value >= 1000 + 512
+        del a, b
+    finally:
+        abi.check(L.twg_set_guard_words(0))
+    c = abi.DeviceBuffer(1000)                                         # blocks made afterwards are plain again
+    abi.check(L.twg_check_guard_words(0, ctypes.byref(bad), ctypes.byref(first)))
+    assert bad.value == 0
 
 
 def test_allocator_budget_injects_out_of_memory(abi):

@@ -245,6 +245,20 @@ def test_two_rank_sharding_reproduces_the_single_rank_result(tmp_path):
     assert np.array_equal(out.view(np.uint32), ref.view(np.uint32))
 
 
+def test_tracing_switch_and_ranges_without_a_profiler(abi):
+    """NVTX ranges are off by default, can be switched on and off, and a traced call behaves like an
+    untraced one (here: a call that fails its argument check, so no GPU is needed)."""
+    L = abi.lib()
+    assert L.twg_get_tracing() == (1 if os.environ.get("TWG_NVTX", "0") not in ("", "0") else 0)
+    abi.check(L.twg_set_tracing(1))
+    assert L.twg_get_tracing() == 1
+    assert L.twg_unary_f32(1, None, None, None, None) == abi.TWG_ERR_INVALID
+    assert b"descriptor" in L.twg_last_error()
+    abi.check(L.twg_set_tracing(0))
+    assert L.twg_get_tracing() == 0
+    assert L.twg_unary_f32(1, None, None, None, None) == abi.TWG_ERR_INVALID
+
+
 def _share_main(rank: int, world: int, port: int, out_dir: str) -> None:
     from torch_webgpu.sharding import Rendezvous
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))

@@ -273,6 +273,7 @@ extern "C" int twg_comm_destroy(void* comm) {
 }
 
 extern "C" int twg_allgather_i64(void* comm, const int64_t* send_dev, int64_t* recv_dev, int n, void* stream) {
+  TWG_TRACE("twg_allgather_i64");
   Comm* c = static_cast<Comm*>(comm);
   TWG_REQUIRE(c != nullptr && c->magic == kCommMagic, "twg_allgather_i64: not a communicator");
   TWG_REQUIRE(n >= 0, "twg_allgather_i64: negative count");
@@ -401,6 +402,7 @@ int xchg_publish_slots(void* xchg, int64_t seq, MsPublish* out) {
 }  // namespace twg
 
 extern "C" int twg_exchange_publish(void* xchg, int64_t seq, const int64_t* result_dev, void* stream) {
+  TWG_TRACE("twg_exchange_publish");
   Xchg* x = as_xchg(xchg);
   TWG_REQUIRE(x != nullptr && result_dev != nullptr, "twg_exchange_publish: bad argument");
   TWG_REQUIRE(seq >= 1 && seq < (int64_t(1) << 55), "twg_exchange_publish: sequence numbers start at 1 (got %lld)",
@@ -415,6 +417,7 @@ extern "C" int twg_exchange_publish(void* xchg, int64_t seq, const int64_t* resu
 }
 
 extern "C" int twg_exchange_collect(void* xchg, int64_t seq, void* stream) {
+  TWG_TRACE("twg_exchange_collect");
   Xchg* x = as_xchg(xchg);
   TWG_REQUIRE(x != nullptr, "twg_exchange_collect: bad argument");
   TWG_REQUIRE(seq >= 1 && seq < (int64_t(1) << 55), "twg_exchange_collect: sequence numbers start at 1 (got %lld)",
@@ -429,6 +432,7 @@ extern "C" int twg_exchange_collect(void* xchg, int64_t seq, void* stream) {
 
 extern "C" int twg_exchange_wait(void* xchg, int64_t seq, int64_t* counts, int64_t* statuses, int64_t* offset,
                                  int64_t* total, int timeout_ms) {
+  TWG_TRACE("twg_exchange_wait");
   Xchg* x = as_xchg(xchg);
   TWG_REQUIRE(x != nullptr, "twg_exchange_wait: bad argument");
   TWG_REQUIRE(seq >= 1, "twg_exchange_wait: sequence numbers start at 1");

@@ -160,6 +160,7 @@ static int dtype_size(int dtype) {
 using namespace twg;
 
 extern "C" int twg_convert(const TwgIterDesc* desc, int src_dtype, int dst_dtype, const void* in, void* out, void* stream) {
+  TWG_TRACE("twg_convert");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   g_last_path = kPathNone;
   if (int rc = check_desc(desc, 2)) return rc;

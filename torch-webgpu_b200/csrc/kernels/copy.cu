@@ -254,6 +254,7 @@ bool all_dense(const TwgIterDesc& d, int nt) {
 using namespace twg;
 
 extern "C" int twg_copy_strided(const TwgIterDesc* desc, int itemsize, const void* in, void* out, void* stream) {
+  TWG_TRACE("twg_copy_strided");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   g_last_path = kPathNone;
   if (int rc = check_desc(desc, 2)) return rc;
@@ -277,6 +278,7 @@ extern "C" int twg_copy_strided(const TwgIterDesc* desc, int itemsize, const voi
 }
 
 extern "C" int twg_fill(const TwgIterDesc* desc, int itemsize, uint64_t pattern, void* out, void* stream) {
+  TWG_TRACE("twg_fill");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   g_last_path = kPathNone;
   if (int rc = check_desc(desc, 1)) return rc;
@@ -298,6 +300,7 @@ extern "C" int twg_fill(const TwgIterDesc* desc, int itemsize, uint64_t pattern,
 
 extern "C" int twg_bitwise_and(const TwgIterDesc* desc, int itemsize, int is_bool, const void* a, const void* b,
                                void* out, void* stream) {
+  TWG_TRACE("twg_bitwise_and");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (is_bool) {
     TWG_REQUIRE(itemsize == 1, "twg_bitwise_and: bool operands are 1 byte, got itemsize %d", itemsize);

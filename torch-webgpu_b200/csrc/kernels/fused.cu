@@ -7,8 +7,11 @@
 // turned into a small CUDA translation unit around the same header and compiled for sm_100a with
 // NVRTC on first use (loaded with the driver API, cached per device).
 #include <dlfcn.h>
+#include <unistd.h>
 
+#include <atomic>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -426,6 +429,87 @@ static int nvrtc_compile(const std::string& source, std::vector<char>* cubin) {
   return TWG_OK;
 }
 
+// ------------------------------------------------------------------------------------------
+// On-disk cache of the cubins NVRTC produced.  A program's generated source includes the device
+// headers only by name, so the key hashes the source text, both header texts and the library
+// version; the file holds the hash key's source length, and the cubin.  Files are written to a
+// temporary name and renamed, so concurrent processes (one per GPU) never see half a file.  The
+// cache is off until a directory is given (twg_fused_set_cache_dir, or TWG_CACHE_DIR in the
+// environment when the library is first used).
+// ------------------------------------------------------------------------------------------
+static std::mutex g_disk_mu;
+static std::string g_disk_dir;
+static bool g_disk_env_read = false;
+static std::atomic<long long> g_disk_hits{0}, g_disk_misses{0};
+
+static std::string disk_dir() {
+  std::lock_guard<std::mutex> lock(g_disk_mu);
+  if (!g_disk_env_read) {
+    g_disk_env_read = true;
+    if (g_disk_dir.empty()) {
+      const char* env = getenv("TWG_CACHE_DIR");
+      if (env && *env) g_disk_dir = env;
+    }
+  }
+  return g_disk_dir;
+}
+static unsigned long long fnv1a(const char* data, size_t n, unsigned long long h) {
+  for (size_t i = 0; i < n; ++i) {
+    h ^= (unsigned char)data[i];
+    h *= 1099511628211ull;
+  }
+  return h;
+}
+static std::string disk_path(const std::string& dir, const std::string& source) {
+  unsigned long long h1 = 14695981039346656037ull, h2 = 0x9e3779b97f4a7c15ull;
+  const char* parts[] = {source.c_str(), kPointwiseHeader, kCompactHeader, twg_version()};
+  for (const char* part : parts) {
+    const size_t n = strlen(part);
+    h1 = fnv1a(part, n, h1);
+    h2 = fnv1a(part, n, h2 ^ n);
+  }
+  char name[64];
+  snprintf(name, sizeof(name), "/twg_%016llx%016llx.cubin", h1, h2);
+  return dir + name;
+}
+static bool disk_load(const std::string& path, size_t source_len, std::vector<char>* cubin) {
+  FILE* f = fopen(path.c_str(), "rb");
+  if (!f) return false;
+  unsigned long long head[2] = {0, 0};  // source length, cubin size
+  bool ok = fread(head, sizeof(head), 1, f) == 1 && head[0] == source_len && head[1] > 0 && head[1] < (1ull << 30);
+  if (ok) {
+    cubin->resize((size_t)head[1]);
+    ok = fread(cubin->data(), 1, cubin->size(), f) == cubin->size() && fgetc(f) == EOF;
+  }
+  fclose(f);
+  if (!ok) cubin->clear();
+  return ok;
+}
+static void disk_store(const std::string& path, size_t source_len, const std::vector<char>& cubin) {
+  char tmp_suffix[48];
+  snprintf(tmp_suffix, sizeof(tmp_suffix), ".tmp.%ld.%p", (long)getpid(), (const void*)&cubin);
+  const std::string tmp = path + tmp_suffix;
+  FILE* f = fopen(tmp.c_str(), "wb");
+  if (!f) return;  // an unwritable directory only means: no cache
+  const unsigned long long head[2] = {source_len, cubin.size()};
+  const bool ok = fwrite(head, sizeof(head), 1, f) == 1 && fwrite(cubin.data(), 1, cubin.size(), f) == cubin.size();
+  if (fclose(f) != 0 || !ok || rename(tmp.c_str(), path.c_str()) != 0) remove(tmp.c_str());
+}
+// nvrtc_compile behind the disk cache.
+static int compile_cached(const std::string& source, std::vector<char>* cubin) {
+  const std::string dir = disk_dir();
+  if (dir.empty()) return nvrtc_compile(source, cubin);
+  const std::string path = disk_path(dir, source);
+  if (disk_load(path, source.size(), cubin)) {
+    g_disk_hits.fetch_add(1);
+    return TWG_OK;
+  }
+  g_disk_misses.fetch_add(1);
+  if (int rc = nvrtc_compile(source, cubin)) return rc;
+  disk_store(path, source.size(), *cubin);
+  return TWG_OK;
+}
+
 struct DeviceModule {
   CUmodule mod = nullptr;
   CUfunction dense = nullptr, tile = nullptr, strided32 = nullptr, strided64 = nullptr;
@@ -546,6 +630,7 @@ extern "C" int twg_fused_set_nvrtc_path(const char* path) {
 }
 
 extern "C" int twg_fused_compile(const TwgFusedInstr* prog, int ninstr, TwgFusedProgram** out) {
+  TWG_TRACE("twg_fused_compile");
   TWG_REQUIRE(out != nullptr, "twg_fused_compile: null result pointer");
   *out = nullptr;
   Analysis an;
@@ -568,7 +653,7 @@ extern "C" int twg_fused_compile(const TwgFusedInstr* prog, int ninstr, TwgFused
     p->kind = 0;
   } else {
     p->kind = 1;
-    if (int rc = nvrtc_compile(source, &p->cubin)) {
+    if (int rc = compile_cached(source, &p->cubin)) {
       delete p;
       return rc;
     }
@@ -576,6 +661,19 @@ extern "C" int twg_fused_compile(const TwgFusedInstr* prog, int ninstr, TwgFused
   p->refs = 1;
   g_cache[source] = p;
   *out = p;
+  return TWG_OK;
+}
+
+extern "C" int twg_fused_set_cache_dir(const char* dir) {
+  std::lock_guard<std::mutex> lock(g_disk_mu);
+  g_disk_env_read = true;  // an explicit setting wins over the environment
+  g_disk_dir = dir ? dir : "";
+  return TWG_OK;
+}
+
+extern "C" int twg_fused_cache_stats(int64_t* hits, int64_t* misses) {
+  if (hits) *hits = g_disk_hits.load();
+  if (misses) *misses = g_disk_misses.load();
   return TWG_OK;
 }
 
@@ -592,6 +690,7 @@ extern "C" int twg_fused_source(const TwgFusedProgram* p, const char** source) {
 }
 
 extern "C" int twg_fused_launch(const TwgFusedProgram* cp, const TwgIterDesc* desc, void* const* ptrs, void* stream) {
+  TWG_TRACE("twg_fused_launch");
   TWG_REQUIRE(cp && ptrs, "twg_fused_launch: null argument");
   TwgFusedProgram* p = const_cast<TwgFusedProgram*>(cp);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -669,6 +768,7 @@ static int jit_select(TwgFusedProgram* p, int src, const SelectArgs& a, cudaStre
 extern "C" int twg_fused_select_f32(const TwgFusedProgram* cp, int src_input, int64_t numel, const void* const* inputs,
                                     float* out, int64_t* result_dev, void* workspace, size_t workspace_bytes,
                                     void* stream) {
+  TWG_TRACE("twg_fused_select_f32");
   TWG_REQUIRE(cp && inputs && result_dev, "twg_fused_select_f32: null argument");
   TwgFusedProgram* p = const_cast<TwgFusedProgram*>(cp);
   cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -664,6 +664,7 @@ static int masked_select_impl(const TwgIterDesc* desc, const float* src, const u
 
 extern "C" int twg_masked_select_f32(const TwgIterDesc* desc, const float* src, const uint8_t* mask, float* out,
                                      int64_t* result_dev, void* workspace, size_t workspace_bytes, void* stream) {
+  TWG_TRACE("twg_masked_select_f32");
   MsPublish none;
   std::memset(&none, 0, sizeof(none));
   return masked_select_impl(desc, src, mask, out, result_dev, workspace, workspace_bytes, stream, none, nullptr);
@@ -672,6 +673,7 @@ extern "C" int twg_masked_select_f32(const TwgIterDesc* desc, const float* src, 
 extern "C" int twg_masked_select_f32_publish(const TwgIterDesc* desc, const float* src, const uint8_t* mask, float* out,
                                              int64_t* result_dev, void* workspace, size_t workspace_bytes, void* xchg,
                                              int64_t seq, void* stream) {
+  TWG_TRACE("twg_masked_select_f32_publish");
   MsPublish pub;
   std::memset(&pub, 0, sizeof(pub));
   if (int rc = xchg_publish_slots(xchg, seq, &pub)) return rc;
@@ -730,6 +732,7 @@ extern "C" int64_t twg_masked_select_static_max_numel(void) { return twg::kMsSta
 
 extern "C" int twg_masked_select_f32_static(const TwgIterDesc* desc, const float* src, const uint8_t* mask, float* out,
                                             int64_t* result_dev, void* stream) {
+  TWG_TRACE("twg_masked_select_f32_static");
   if (int rc = check_desc(desc, 2)) return rc;
   if (desc->numel > kMsStaticMaxNumel)
     return set_error(TWG_ERR_UNSUPPORTED,

@@ -139,6 +139,7 @@ int and_bool(const TwgIterDesc* d, const void* a, const void* b, void* out, cuda
 using namespace twg;
 
 extern "C" int twg_unary_f32(int op, const TwgIterDesc* desc, const float* in, float* out, void* stream) {
+  TWG_TRACE("twg_unary_f32");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (op) {
     case TWG_UNARY_COPY: return run_unary<TWG_UNARY_COPY>(desc, in, out, s);
@@ -153,6 +154,7 @@ extern "C" int twg_unary_f32(int op, const TwgIterDesc* desc, const float* in, f
 
 extern "C" int twg_binary_f32(int op, const TwgIterDesc* desc, const float* a, const float* b, float alpha,
                               float* out, void* stream) {
+  TWG_TRACE("twg_binary_f32");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (op) {
     case TWG_BINARY_ADD: return run_binary<TWG_BINARY_ADD>(desc, a, b, alpha, out, s);
@@ -165,6 +167,7 @@ extern "C" int twg_binary_f32(int op, const TwgIterDesc* desc, const float* a, c
 
 extern "C" int twg_binary_scalar_f32(int op, const TwgIterDesc* desc, const float* a, float scalar, float alpha,
                                      float* out, void* stream) {
+  TWG_TRACE("twg_binary_scalar_f32");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (op) {
     case TWG_BINARY_ADD: return run_binary_scalar<TWG_BINARY_ADD>(desc, a, scalar, alpha, out, s);
@@ -177,18 +180,21 @@ extern "C" int twg_binary_scalar_f32(int op, const TwgIterDesc* desc, const floa
 
 extern "C" int twg_where_f32(const TwgIterDesc* desc, const uint8_t* cond, const float* a, const float* b, float* out,
                              void* stream) {
+  TWG_TRACE("twg_where_f32");
   void* ptrs[4] = {out, const_cast<uint8_t*>(cond), const_cast<float*>(a), const_cast<float*>(b)};
   return launch_pointwise(WhereF32{}, desc, ptrs, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int twg_masked_fill_f32(const TwgIterDesc* desc, const float* self, const uint8_t* mask, float value,
                                    float* out, void* stream) {
+  TWG_TRACE("twg_masked_fill_f32");
   void* ptrs[3] = {out, const_cast<float*>(self), const_cast<uint8_t*>(mask)};
   return launch_pointwise(MaskedFillF32{value}, desc, ptrs, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int twg_compare_f32(int op, const TwgIterDesc* desc, const float* a, const float* b, float scalar,
                                uint8_t* out, void* stream) {
+  TWG_TRACE("twg_compare_f32");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (op) {
     case TWG_CMP_EQ: return run_compare<TWG_CMP_EQ>(desc, a, b, scalar, out, s);

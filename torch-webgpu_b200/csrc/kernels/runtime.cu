@@ -4,12 +4,15 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <deque>
 #include <mutex>
 #include <set>
 #include <unordered_map>
 #include <vector>
+
+#include <nvtx3/nvToolsExt.h>
 
 #include "twg_launch.cuh"
 
@@ -40,6 +43,26 @@ int cuda_fail(cudaError_t e, const char* what, const char* file, int line) {
 }
 
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+// -1: not decided yet (the environment is read on first use), 0 off, 1 on
+static std::atomic<int> g_tracing{-1};
+static bool tracing_on() {
+  int v = g_tracing.load(std::memory_order_relaxed);
+  if (v < 0) {
+    const char* env = getenv("TWG_NVTX");
+    v = (env && *env && *env != '0') ? 1 : 0;
+    int expected = -1;
+    g_tracing.compare_exchange_strong(expected, v);
+    v = g_tracing.load();
+  }
+  return v == 1;
+}
+TraceRange::TraceRange(const char* name) : active(tracing_on()) {
+  if (active) nvtxRangePushA(name);
+}
+TraceRange::~TraceRange() {
+  if (active) nvtxRangePop();
+}
 
 constexpr int kMaxDevices = 64;
 
@@ -240,7 +263,17 @@ struct Block {
   Block* next = nullptr;
   int pending_events = 0;
   std::vector<cudaStream_t> extra_streams;
+  size_t user_bytes = 0;  // bytes the caller asked for (guard words start behind them)
+  bool guarded = false;
 };
+
+// Guard words (a debugging aid, off by default): while enabled, every new block is allocated
+// kGuardBytes larger than asked for and the bytes behind the caller's are filled with a pattern;
+// twg_check_guard_words compares them later.  A kernel that writes a little past its output lands
+// in the guard (inside the block, so nothing faults) and is reported with the block's address.
+constexpr size_t kGuardBytes = 512;
+constexpr unsigned char kGuardPattern = 0xA5;
+static std::atomic<int> g_guard_words{0};
 
 struct BlockLess {
   bool operator()(const Block* a, const Block* b) const {
@@ -361,6 +394,12 @@ extern "C" const char* twg_version(void) { return "twg 0.1 (sm_100a)"; }
 extern "C" int twg_last_launch_path(void) { return g_last_path; }
 extern "C" int64_t twg_launch_count(void) { return g_launches.load(); }
 extern "C" void twg_reset_launch_count(void) { g_launches.store(0); }
+
+extern "C" int twg_set_tracing(int enabled) {
+  g_tracing.store(enabled ? 1 : 0);
+  return TWG_OK;
+}
+extern "C" int twg_get_tracing(void) { return tracing_on() ? 1 : 0; }
 
 extern "C" int twg_device_count(int* count) {
   TWG_REQUIRE(count != nullptr, "twg_device_count: null argument");
@@ -531,7 +570,8 @@ extern "C" int twg_malloc(void** ptr, size_t nbytes, int device, void* stream) {
   if (nbytes == 0) return TWG_OK;
   if (int rc = check_device(device)) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const size_t size = round_size(nbytes);
+  const bool guarded = g_guard_words.load(std::memory_order_relaxed) != 0;
+  const size_t size = round_size(nbytes + (guarded ? kGuardBytes : 0));
   const bool small = size <= kSmallLimit;
 
   std::lock_guard<std::mutex> lock(g_alloc_mu);
@@ -588,10 +628,17 @@ extern "C" int twg_malloc(void** ptr, size_t nbytes, int device, void* stream) {
     set.insert(rest);
   }
   b->allocated = true;
+  b->user_bytes = nbytes;
+  b->guarded = false;
   g_live[b->ptr] = b;
   p.stats.num_allocs++;
   bump_allocated(p, (int64_t)b->size);
   *ptr = b->ptr;
+  if (guarded) {
+    // everything behind the caller's bytes, on the block's stream (ordered before its first use)
+    TWG_CUDA(cudaMemsetAsync(b->ptr + nbytes, kGuardPattern, b->size - nbytes, s));
+    b->guarded = true;
+  }
   return TWG_OK;
 }
 
@@ -648,6 +695,7 @@ extern "C" int twg_trim(void* ptr, size_t new_nbytes) {
   if (keep >= b->size) return TWG_OK;
   const size_t remaining = b->size - keep;
   if ((b->small && remaining < kRound) || (!b->small && remaining <= kSmallLimit)) return TWG_OK;
+  if (b->guarded) return TWG_OK;  // the guard words sit in the tail
   // A block that other streams also use (twg_record_stream) keeps its tail: those streams may
   // still touch it, and only twg_free orders a block's reuse after them.
   if (!b->extra_streams.empty()) return TWG_OK;
@@ -667,6 +715,40 @@ extern "C" int twg_trim(void* ptr, size_t new_nbytes) {
   // The tail may still be written by work already queued on the block's own stream, and a later
   // allocation on that stream is ordered after it, so it can go straight back to the free list.
   insert_free(p, rest);
+  return TWG_OK;
+}
+
+extern "C" int twg_set_guard_words(int enabled) {
+  g_guard_words.store(enabled ? 1 : 0);
+  return TWG_OK;
+}
+
+extern "C" int twg_check_guard_words(int device, int64_t* corrupted_blocks, void** first_block) {
+  if (int rc = check_device(device)) return rc;
+  if (corrupted_blocks) *corrupted_blocks = 0;
+  if (first_block) *first_block = nullptr;
+  std::lock_guard<std::mutex> lock(g_alloc_mu);
+  ScopedDevice guard(device);
+  TWG_CUDA(guard.err);
+  TWG_CUDA(cudaDeviceSynchronize());
+  std::vector<unsigned char> host;
+  int64_t bad = 0;
+  void* first = nullptr;
+  for (const auto& kv : g_live) {
+    const Block* b = kv.second;
+    if (b->device != device || !b->guarded) continue;
+    const size_t n = b->size - b->user_bytes;
+    host.resize(n);
+    TWG_CUDA(cudaMemcpy(host.data(), b->ptr + b->user_bytes, n, cudaMemcpyDeviceToHost));
+    bool ok = true;
+    for (size_t i = 0; i < n && ok; ++i) ok = host[i] == kGuardPattern;
+    if (!ok) {
+      ++bad;
+      if (first == nullptr || b->ptr < static_cast<char*>(first)) first = b->ptr;
+    }
+  }
+  if (corrupted_blocks) *corrupted_blocks = bad;
+  if (first_block) *first_block = first;
   return TWG_OK;
 }
 
@@ -760,6 +842,7 @@ static bool is_pinned(const void* p) {
 }  // namespace twg
 
 extern "C" int twg_memcpy_h2d(void* dst_dev, const void* src_host, size_t nbytes, void* stream) {
+  TWG_TRACE("twg_memcpy_h2d");
   if (nbytes == 0) return TWG_OK;
   TWG_REQUIRE(dst_dev && src_host, "twg_memcpy_h2d: null pointer");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -786,6 +869,7 @@ extern "C" int twg_memcpy_h2d(void* dst_dev, const void* src_host, size_t nbytes
 }
 
 extern "C" int twg_memcpy_d2h(void* dst_host, const void* src_dev, size_t nbytes, void* stream, int blocking) {
+  TWG_TRACE("twg_memcpy_d2h");
   if (nbytes == 0) return TWG_OK;
   TWG_REQUIRE(dst_host && src_dev, "twg_memcpy_d2h: null pointer");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -825,6 +909,7 @@ extern "C" int twg_memcpy_d2h(void* dst_host, const void* src_dev, size_t nbytes
 }
 
 extern "C" int twg_memcpy_d2d(void* dst_dev, const void* src_dev, size_t nbytes, void* stream) {
+  TWG_TRACE("twg_memcpy_d2d");
   if (nbytes == 0) return TWG_OK;
   TWG_REQUIRE(dst_dev && src_dev, "twg_memcpy_d2d: null pointer");
   TWG_CUDA(cudaMemcpyAsync(dst_dev, src_dev, nbytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));

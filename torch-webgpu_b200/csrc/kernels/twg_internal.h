@@ -14,6 +14,16 @@ namespace twg {
 int set_error(int code, const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what, const char* file, int line);
 void count_launch(int n = 1);
+// NVTX range around a C-ABI call, emitted only while tracing is on (twg_set_tracing / TWG_NVTX=1):
+// a profiler's timeline then shows which library call every kernel and copy belongs to.
+struct TraceRange {
+  bool active;
+  explicit TraceRange(const char* name);
+  ~TraceRange();
+  TraceRange(const TraceRange&) = delete;
+  TraceRange& operator=(const TraceRange&) = delete;
+};
+#define TWG_TRACE(name) ::twg::TraceRange twg_trace_range_(name)
 // Properties of the current device (cached per ordinal).
 int sm_count();
 

@@ -89,6 +89,8 @@ SIGNATURES = {
     "twg_memory_stats": (c_int, [c_int, POINTER(MemStats)]),
     "twg_reset_peak_stats": (c_int, [c_int]),
     "twg_set_memory_budget": (c_int, [c_int, c_size_t]),
+    "twg_set_guard_words": (c_int, [c_int]),
+    "twg_check_guard_words": (c_int, [c_int, POINTER(c_int64), POINTER(c_void_p)]),
     "twg_memcpy_h2d": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
     "twg_memcpy_d2h": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p, c_int]),
     "twg_memcpy_d2d": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
@@ -119,6 +121,8 @@ SIGNATURES = {
                                      c_size_t, c_void_p]),
     "twg_fused_set_nvrtc_path": (c_int, [c_char_p]),
     "twg_fused_source": (c_int, [c_void_p, POINTER(c_char_p)]),
+    "twg_fused_set_cache_dir": (c_int, [c_char_p]),
+    "twg_fused_cache_stats": (c_int, [POINTER(c_int64), POINTER(c_int64)]),
     "twg_comm_set_nccl_path": (c_int, [c_char_p]),
     "twg_comm_unique_id": (c_int, [c_void_p]),
     "twg_comm_init_rank": (c_int, [c_void_p, c_int, c_int, POINTER(c_void_p)]),
@@ -137,6 +141,8 @@ SIGNATURES = {
     "twg_exchange_gathered": (c_int, [c_void_p, c_int64, POINTER(c_void_p)]),
     "twg_exchange_set_timeout_ns": (c_int, [c_void_p, c_int64]),
     "twg_exchange_destroy": (c_int, [c_void_p]),
+    "twg_set_tracing": (c_int, [c_int]),
+    "twg_get_tracing": (c_int, []),
     "twg_launch_count": (c_int64, []),
     "twg_reset_launch_count": (None, []),
     "twg_last_launch_path": (c_int, []),
