@@ -24,9 +24,7 @@ import ctypes
 import json
 import os
 import statistics
-import subprocess
 import sys
-import tempfile
 import time
 from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
@@ -640,7 +638,7 @@ def run_gpu_arm(args) -> None:
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; this benchmark has no CPU fallback (use --impl reference for the CPU arm)")
 
-    import torch_webgpu
+    import torch_webgpu  # noqa: F401  (registers the webgpu device and the compile backend)
     from torch_webgpu import abi, webgpu_backend
     from torch_webgpu.sharding import NcclExchange, PeerStoreExchange, Rendezvous, shard_range
 
