@@ -41,12 +41,17 @@ SLAB = ROWS * COLS
 SEED = 4
 FALLBACK_HBM_GBS = 6650.0
 NOMINAL_HBM_GBS = 8000.0   # the round figure for B200 HBM3e; every fraction is also reported against it
-CHAIN_BYTES_PER_ELEM = 13  # read a, b, c (3 x 4 B), write the bool mask (1 B)
-# DRAM bytes the fused-chain kernel moves per element (dram__bytes_read.sum + dram__bytes_write.sum
-# of one ncu capture on 2^27 elements).  A constant taken from that capture, not a measurement of
-# this run: the traffic of a streaming kernel is proportional to its element count, so it is scaled
-# to the elements of a launch.
-CHAIN_DRAM_BYTES_PER_ELEM = 12.89
+# Algorithmic bytes per element of the step's dominant kernel, the fused chain: read a, b, c
+# (3 x 4 B) and write the mask - one bit per element (the default, --mask bits) or a bool tensor
+# (--mask bytes).
+CHAIN_BYTES_PER_ELEM = {"bits": 12.125, "bytes": 13.0}
+# DRAM bytes that kernel moves per element (dram__bytes_read.sum + dram__bytes_write.sum of one ncu
+# capture on 2^27 elements).  Constants taken from those captures, not measurements of this run:
+# the traffic of a streaming kernel is proportional to its element count, so it is scaled to the
+# elements of a launch.
+CHAIN_DRAM_BYTES_PER_ELEM = {"bits": 12.08, "bytes": 12.89}
+CHAIN_KERNEL = {"bits": "predicate_bits_kernel<AotChainMask> (fused chain, mask as bits: 12.125 B/elem)",
+                "bytes": "pw_contig_kernel<AotChainMask> (fused chain, bool mask: 13 B/elem)"}
 
 
 def slab_seed(tensor_id: int, batch_index: int) -> int:
@@ -252,9 +257,11 @@ def run_reference_arm(args) -> None:
     print(json.dumps(line), flush=True)
 
 
-def workload_config(n_gpus: int, depth: int) -> dict:
+def workload_config(n_gpus: int, depth: int, mask: str = "bits") -> dict:
+    calls = ("twg_fused_predicate_bits (the mask m as one bit per element) + twg_masked_select_bits_f32_publish" if mask == "bits"
+             else "twg_fused_launch (m as a bool tensor) + twg_masked_select_f32_publish")
     cfg = {"workload": "cfg5: y=relu(silu(a+b)+c); m=(y==0)&(a!=0); masked_select(a,m) over 64 x f32[4096,4096]; "
-                       "`value` = C ABI calls twg_fused_launch + twg_masked_select_f32_publish + twg_exchange_collect per step, "
+                       f"`value` = C ABI calls {calls} + twg_exchange_collect per step, "
                        "`public_api` / `e2e` = the same through torch.compile(backend=webgpu_backend)",
            "global_batch": BATCH, "elements_per_step": BATCH * SLAB, "parallelism": f"batch-sharded x{n_gpus}",
            "l2": "inputs (>= 1.5 GiB per rank) are larger than the 126 MB L2; no flush needed"}
@@ -446,12 +453,14 @@ def per_op_table(abi, stream, peak: float) -> dict:
         abi.check(L.twg_fused_release(handle))
     del dc0
 
-    # predicate + select: mask kernel then masked_select (two launches) against the one-launch form
+    # predicate + select: byte mask kernel then masked_select, against the form that keeps the mask as bits
     g = torch.Generator().manual_seed(4)
     for buf in (dx, dy):
         buf.upload(torch.randn(n2, generator=g).numpy(), stream)
     dc = abi.DeviceBuffer(4 * n2)
     dc.upload(torch.randn(n2, generator=g).numpy(), stream)
+    fws_bytes = L.twg_fused_select_workspace_bytes(n2)
+    fws = abi.DeviceBuffer(fws_bytes)
     F = abi
     positive = [(F.F_INPUT_F32, 0, 0, 0.0), (F.F_CONST_F32, 0, 0, 0.0), (F.F_GT, 0, 1, 0.0), (F.F_OUTPUT, 2, 0, 0.0)]
     for name, prog, nin in (("chain", abi.CHAIN_MASK_PROGRAM, 3), ("positive", positive, 1)):
@@ -465,17 +474,17 @@ def per_op_table(abi, stream, peak: float) -> dict:
             abi.check(L.twg_fused_launch(handle, ctypes.byref(dmask), mask_ptrs, stream))
             abi.check(L.twg_masked_select_f32(ctypes.byref(dsel), dx.ptr, dm.ptr, dz.ptr, res.ptr, ws.ptr, ws_bytes, stream))
 
-        def one_launch():
-            abi.check(L.twg_fused_select_f32(handle, 0, n2, in_ptrs, dz.ptr, res.ptr, ws.ptr, ws_bytes, stream))
+        def bit_mask():
+            abi.check(L.twg_fused_select_f32(handle, 0, n2, in_ptrs, dz.ptr, res.ptr, fws.ptr, fws_bytes, stream))
 
         ms2 = time_op(abi, stream, two_launches, iters=10)
         k2 = int(res.download(np.int64, 2, stream)[0])
-        ms1 = time_op(abi, stream, one_launch, iters=10)
+        ms1 = time_op(abi, stream, bit_mask, iters=10)
         k1, status = (int(v) for v in res.download(np.int64, 2, stream))
         if k1 != k2 or status != 0:
             raise RuntimeError(f"fused select kept {k1} elements (status {status}), the two-launch form {k2}")
         put(f"select_{name}_two_launches", (4 * nin + 1) * n2 + 5 * n2 + 4 * k2, ms2, f"k={k2}; mask written and read back")
-        put(f"select_{name}_one_launch", 4 * nin * n2 + 4 * k1, ms1, f"k={k1}; no mask in memory")
+        put(f"select_{name}_bit_mask", 4 * nin * n2 + n2 // 4 + 4 * n2 + 4 * k1, ms1, f"k={k1}; mask written and read back as bits")
         abi.check(L.twg_fused_release(handle))
     return table
 
@@ -580,14 +589,14 @@ def run_case(args) -> None:
         for b_ in ins:
             b_.upload(host(n))
         out, res = abi.DeviceBuffer(4 * n), abi.DeviceBuffer(16)
-        wsb = L.twg_masked_select_workspace_bytes(n)
+        wsb = L.twg_fused_select_workspace_bytes(n)
         ws = abi.DeviceBuffer(wsb)
         prog = abi.fused_compile(abi.CHAIN_MASK_PROGRAM)
         in_ptrs = (ctypes.c_void_p * 3)(*[i.ptr for i in ins])
         fn = lambda: abi.check(L.twg_fused_select_f32(prog, 0, n, in_ptrs, out.ptr, res.ptr, ws.ptr, wsb, stream))
         fn()
         k = int(res.download(np.int64, 2)[0])
-        nbytes = 12 * n + 4 * k
+        nbytes = 12 * n + n // 4 + 4 * n + 4 * k
         bufs = ins + [out, res, ws]
     else:
         raise SystemExit(f"unknown case {args.case}")
@@ -710,10 +719,12 @@ def run_gpu_arm(args) -> None:
     dev_in = [abi.DeviceBuffer(4 * n, local_rank, stream) for _ in range(3)]
     for buf, h in zip(dev_in, host):
         abi.check(L.twg_memcpy_h2d(buf.ptr, h.data_ptr(), 4 * n, stream))
-    d_mask = abi.DeviceBuffer(n, local_rank, stream)
+    bits_mode = args.mask == "bits"
+    d_mask = None if bits_mode else abi.DeviceBuffer(n, local_rank, stream)
     # DEPTH sets of everything a step writes: the host picks up the counts of step i while the GPU
     # already runs the steps after it, so the stream never waits for the host or for another rank.
     ws_bytes = L.twg_masked_select_workspace_bytes(n)
+    d_bits = abi.DeviceBuffer(L.twg_predicate_bits_bytes(n), local_rank, stream) if bits_mode else None
     d_out = [abi.DeviceBuffer(4 * n, local_rank, stream) for _ in range(DEPTH)]
     d_ws = [abi.DeviceBuffer(ws_bytes, local_rank, stream) for _ in range(DEPTH)]
     d_res = [abi.DeviceBuffer(16, local_rank, stream) for _ in range(DEPTH)]   # [count, status] of this rank
@@ -724,7 +735,8 @@ def run_gpu_arm(args) -> None:
     abi.check(L.twg_iter_contiguous(ctypes.byref(desc4), 4, n))
     desc2 = abi.IterDesc()
     abi.check(L.twg_iter_contiguous(ctypes.byref(desc2), 2, n))
-    ptrs = (ctypes.c_void_p * 4)(d_mask.ptr, dev_in[0].ptr, dev_in[1].ptr, dev_in[2].ptr)
+    ptrs = (ctypes.c_void_p * 4)(0 if bits_mode else d_mask.ptr, dev_in[0].ptr, dev_in[1].ptr, dev_in[2].ptr)
+    in_ptrs = (ctypes.c_void_p * 3)(dev_in[0].ptr, dev_in[1].ptr, dev_in[2].ptr)
 
     steps, warmup = args.steps, args.warmup
     ev = Events(abi, 2 + 2 * steps)
@@ -735,19 +747,26 @@ def run_gpu_arm(args) -> None:
     def launch(i: int | None) -> int:
         """Everything one step puts on the GPU: fused chain and compaction (which also publishes this
         rank's count to every rank) on the compute stream, and on a second stream the kernel that
-        gathers all ranks' counts for the host."""
+        gathers all ranks' counts for the host.  Events 2+2i / 3+2i bracket the fused chain."""
         t_issue = time.perf_counter()
         seq = seq_next[0]
         seq_next[0] += 1
         slot = seq % DEPTH
         if i is not None:
             ev.record(2 + 2 * i, stream)
-        abi.check(L.twg_fused_launch(program, ctypes.byref(desc4), ptrs, stream))
+        if bits_mode:
+            abi.check(L.twg_fused_predicate_bits(program, n, in_ptrs, d_bits.ptr, stream))
+        else:
+            abi.check(L.twg_fused_launch(program, ctypes.byref(desc4), ptrs, stream))
         if i is not None:
             ev.record(3 + 2 * i, stream)
         # compaction; its last chunk stores this rank's count into every rank's mailbox
-        xchg.masked_select_publish(seq, desc2, dev_in[0].ptr, d_mask.ptr, d_out[slot].ptr, d_res[slot].ptr,
-                                   d_ws[slot].ptr, ws_bytes, stream)
+        if bits_mode:
+            xchg.select_bits_publish(seq, dev_in[0].ptr, d_bits.ptr, n, d_out[slot].ptr, d_res[slot].ptr, d_ws[slot].ptr,
+                                     ws_bytes, stream)
+        else:
+            xchg.masked_select_publish(seq, desc2, dev_in[0].ptr, d_mask.ptr, d_out[slot].ptr, d_res[slot].ptr,
+                                       d_ws[slot].ptr, ws_bytes, stream)
         compacted.record(slot, stream)
         abi.check(L.twg_event_wait(compacted.ev[slot], side))
         xchg.collect(seq, side)
@@ -825,7 +844,11 @@ def run_gpu_arm(args) -> None:
         last_slot = (seq_next[0] - 1) % DEPTH
         k_mine = counts_seen[-1][0]
         for which in sorted({0, nb - 1}):
-            gmask = d_mask.download(np.uint8, SLAB, stream, offset_bytes=which * SLAB)
+            if bits_mode:   # bit i of byte j is element 8 j + i
+                packed = d_bits.download(np.uint8, SLAB // 8, stream, offset_bytes=which * (SLAB // 8))
+                gmask = np.unpackbits(packed, bitorder="little")
+            else:
+                gmask = d_mask.download(np.uint8, SLAB, stream, offset_bytes=which * SLAB)
             kept = int(np.count_nonzero(gmask))
             seg_lo = 0 if which == 0 else k_mine - kept      # first slab: head of the output; last slab: its tail
             if nb == 1 and kept != k_mine:
@@ -836,7 +859,7 @@ def run_gpu_arm(args) -> None:
         verified = all(x == b"ok" for x in rdv.share(b"ok"))
 
     # ---- per-op table (single GPU only) -----------------------------------------------------
-    del d_out, d_mask, d_ws
+    del d_out, d_mask, d_ws, d_bits
     for b_ in dev_in:
         b_.free()
     ops = per_op_table(abi, stream, peak) if world == 1 and not args.no_ops else None
@@ -848,6 +871,10 @@ def run_gpu_arm(args) -> None:
         m = torch.bitwise_and(torch.eq(y, 0), torch.ne(a, 0))
         return torch.masked_select(a, m)
 
+    # With this dynamo flag masked_select stays inside the compiled graph, and the backend hands the
+    # mask over as bits (webgpu::run_fused_select); without it dynamo cuts the graph in front of
+    # masked_select and the mask has to be a bool tensor.
+    torch._dynamo.config.capture_dynamic_output_shape_ops = bits_mode
     compiled = torch.compile(chain, backend=webgpu_backend)
     dev_name = f"webgpu:{local_rank}"
     d_cnt = abi.DeviceBuffer(16, local_rank, stream)
@@ -881,8 +908,10 @@ def run_gpu_arm(args) -> None:
         raise RuntimeError(f"bench: the public API selected {api_total} elements, the C ABI leg {total_k}")
     api_ms = max(float(x) for x in rdv.share(repr(ev3.elapsed(0, 1) / api_steps).encode()))
     public_api = {"value": BATCH * SLAB / (api_ms * 1e-3) / 1e9, "unit": "Gelem/s", "ms_per_step": api_ms, "steps": api_steps,
-                  "api": "torch.compile(chain, backend=webgpu_backend)(a, b, c) on device-resident webgpu tensors; "
-                         "every call ends with the blocking count read-back of masked_select"}
+                  "api": "torch.compile(chain, backend=webgpu_backend)(a, b, c) on device-resident webgpu tensors"
+                         + (", torch._dynamo.config.capture_dynamic_output_shape_ops=True (one graph, mask as bits)" if bits_mode
+                            else " (graph break in front of masked_select, mask as a bool tensor)")
+                         + "; every call ends with the blocking count read-back of masked_select"}
     del resident, sel
     abi.check(L.twg_empty_cache(local_rank))
 
@@ -957,17 +986,17 @@ def run_gpu_arm(args) -> None:
                   "uploads with nothing else running, all ranks at once"}
 
     if rank == 0:
-        achieved = CHAIN_BYTES_PER_ELEM * n / (fused_ms_max * 1e-3) / 1e9
-        traffic = CHAIN_DRAM_BYTES_PER_ELEM * n
+        achieved = CHAIN_BYTES_PER_ELEM[args.mask] * n / (fused_ms_max * 1e-3) / 1e9
+        traffic = CHAIN_DRAM_BYTES_PER_ELEM[args.mask] * n
         line = {
             "metric": "Gelem/s of the compiled chain + masked_select", "value": value, "unit": "Gelem/s", "n_gpus": world,
             "steps": steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(world, DEPTH),
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(world, DEPTH, args.mask),
             "selected_elements": total_k, "verified": verified,
-            "roofline": {"bound": "hbm", "kernel": "pw_contig_kernel<AotChainMask> (fused chain, 13 B/elem)",
+            "roofline": {"bound": "hbm", "kernel": CHAIN_KERNEL[args.mask],
                          "achieved": achieved, "peak": peak, "peak_kind": f"of {peak_kind}", "unit": "GB/s",
                          "frac": achieved / peak, "frac_of_nominal_8000": achieved / NOMINAL_HBM_GBS, "traffic": traffic,
-                         "ms_per_launch": fused_ms_max, "algorithmic_bytes_per_launch": CHAIN_BYTES_PER_ELEM * n},
+                         "ms_per_launch": fused_ms_max, "algorithmic_bytes_per_launch": CHAIN_BYTES_PER_ELEM[args.mask] * n},
             "e2e": e2e, "public_api": public_api, "gpu_launches": launches, "clocks": clocks,
             "step_ms_median": max(r["step_ms_median"] for r in per_rank),
             "step_timing": {"per_rank_ms_total": [round(r["ms_total"], 4) for r in per_rank],
@@ -1004,6 +1033,9 @@ def main() -> None:
     ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "nccl"],
                     help="how the ranks exchange their counts: the library's peer-store kernels, ncclAllGather through "
                          "the C ABI, or (auto) peer stores when every rank can map every other rank's mailbox")
+    ap.add_argument("--mask", default="bits", choices=["bits", "bytes"],
+                    help="how the chain hands its mask to masked_select in the `value` leg: one bit per element in scratch "
+                         "memory (what the compile backend does), or a bool tensor")
     ap.add_argument("--no-verify", action="store_true", help="skip the oracle check of each rank's first and last slab")
     ap.add_argument("--batch", type=int, default=64,
                     help="slabs in the batch (64 is the benchmark; smaller values are for diagnosing overheads)")

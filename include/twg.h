@@ -283,14 +283,28 @@ int twg_fused_launch(const TwgFusedProgram* p, const TwgIterDesc* desc, void* co
 /* Drops one reference; the last one unloads the program's modules (blocks until the devices that
  * ran it are idle) and frees it.  A handle must not be used after its release. */
 int twg_fused_release(TwgFusedProgram* p);
-/* Fused predicate + select: out = inputs[src_input][ prog(inputs) ] in ONE pass, for a program
- * that is a predicate (exactly one bool output over dense f32 inputs of `numel` elements each,
- * 16-byte aligned).  The mask never reaches memory: the kernel reads every input once and writes
- * only the selected values, instead of the fused kernel writing the mask and masked_select
- * (CPU fallback in the reference, csrc/bindings.cpp:42) reading it and src again.
- * out, result_dev, workspace and the bounded look-back behave as in twg_masked_select_f32.
- * TWG_ERR_UNSUPPORTED (program is not a predicate, an input is misaligned, no kernel for this
- * src_input) means: run twg_fused_launch followed by twg_masked_select_f32 instead. */
+/* Fused predicate + select: out = inputs[src_input][ prog(inputs) ], for a program that is a
+ * predicate (exactly one bool output over dense f32 inputs of `numel` elements each, 16-byte
+ * aligned).  Two launches: the predicate kernel reads every input once and writes ONE BIT per
+ * element into the workspace, and the compaction reads those bits and src and writes only the
+ * selected values - instead of the fused kernel writing a byte mask and masked_select (CPU
+ * fallback in the reference, csrc/bindings.cpp:42) reading it back: 0.25 bytes of mask traffic
+ * per element rather than 2.  out, result_dev and the bounded look-back behave as in
+ * twg_masked_select_f32; the workspace holds masked_select's plus the bits
+ * (twg_fused_select_workspace_bytes, 256-byte aligned).
+ * TWG_ERR_UNSUPPORTED (program is not a predicate, an input is misaligned) means: run
+ * twg_fused_launch followed by twg_masked_select_f32 instead. */
+size_t twg_fused_select_workspace_bytes(int64_t numel);
+/* The two halves on their own.  twg_fused_predicate_bits writes the predicate of `numel` elements
+ * as bits (bit i of 32-bit word w = element 32 w + i; twg_predicate_bits_bytes(numel) bytes, whole
+ * 16-byte vectors, zero at and beyond numel; `bits` 16-byte aligned).  twg_masked_select_bits_f32
+ * is masked_select of dense, 16-byte aligned `src` by such a mask; workspace as
+ * twg_masked_select_workspace_bytes(numel), result words as twg_masked_select_f32. */
+size_t twg_predicate_bits_bytes(int64_t numel);
+int twg_fused_predicate_bits(const TwgFusedProgram* p, int64_t numel, const void* const* inputs, uint32_t* bits,
+                             void* stream);
+int twg_masked_select_bits_f32(const float* src, const uint32_t* bits, int64_t numel, float* out, int64_t* result_dev,
+                               void* workspace, size_t workspace_bytes, void* stream);
 int twg_fused_select_f32(const TwgFusedProgram* p, int src_input, int64_t numel, const void* const* inputs,
                          float* out, int64_t* result_dev, void* workspace, size_t workspace_bytes, void* stream);
 /* Path of the NVRTC shared library to load on first use (default: the loader's search path for
@@ -359,6 +373,13 @@ int twg_exchange_collect(void* xchg, int64_t seq, void* stream);
 int twg_masked_select_f32_publish(const TwgIterDesc* desc, const float* src, const uint8_t* mask, float* out,
                                   int64_t* result_dev, void* workspace, size_t workspace_bytes, void* xchg, int64_t seq,
                                   void* stream);
+/* The same for the compaction by a bit mask and for the fused predicate + select. */
+int twg_masked_select_bits_f32_publish(const float* src, const uint32_t* bits, int64_t numel, float* out,
+                                       int64_t* result_dev, void* workspace, size_t workspace_bytes, void* exchange,
+                                       int64_t seq, void* stream);
+int twg_fused_select_f32_publish(const TwgFusedProgram* p, int src_input, int64_t numel, const void* const* inputs,
+                                 float* out, int64_t* result_dev, void* workspace, size_t workspace_bytes,
+                                 void* exchange, int64_t seq, void* stream);
 int twg_exchange_wait(void* xchg, int64_t seq, int64_t* counts, int64_t* statuses, int64_t* offset, int64_t* total,
                       int timeout_ms);
 /* Device copy of the record of `seq`: int64[2*nranks + 2] = counts, statuses, offset, total; valid

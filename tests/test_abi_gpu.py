@@ -517,7 +517,7 @@ def test_fused_program_compiled_at_run_time(abi):
         assert_bit_equal(flag, oracle.compare("gt", oracle.binary("mul", got_g, np.broadcast_to(y, x.shape).copy()), 0.5), "fused flag")
 
 
-@pytest.mark.parametrize("n", [1, 5, 4095, 7680, 7681, 8193, 100003, (1 << 22) + 7])
+@pytest.mark.parametrize("n", [1, 5, 127, 128, 129, 4095, 7680, 7681, 8193, 100003, (1 << 22) + 7, (1 << 24) + 513])
 def test_fused_select_equals_mask_then_masked_select(abi, n):
     a, bb, c = rnd(n, 85, -3, 3), rnd(n, 86, -3, 3), rnd(n, 87, -3, 3)
     a[::5] = 0.0
@@ -526,6 +526,36 @@ def test_fused_select_equals_mask_then_masked_select(abi, n):
     assert kind == "aot"
     assert_bit_equal(sel, abi.masked_select(a, m), "fused select vs mask + masked_select")
     assert_bit_equal(sel, oracle.masked_select(a, m), "fused select vs oracle on the same mask")
+
+
+@pytest.mark.parametrize("n", [1, 31, 128, 1000, 8192 * 3 + 77, (1 << 21) + 5])
+def test_predicate_bits_equal_the_bool_mask(abi, n):
+    """First half of the fused select: the same predicate as bits (ahead-of-time and NVRTC kernels,
+    1 / 2 / 3 inputs, i.e. 4 / 2 / 1 rounds per warp)."""
+    F = abi
+    a, bb, c = rnd(n, 185, -3, 3), rnd(n, 186, -3, 3), rnd(n, 187, -3, 3)
+    a[::5] = 0.0
+    positive = [(F.F_INPUT_F32, 0, 0, 0.0), (F.F_CONST_F32, 0, 0, 0.0), (F.F_GT, 0, 1, 0.0), (F.F_OUTPUT, 2, 0, 0.0)]
+    product = [(F.F_INPUT_F32, 0, 0, 0.0), (F.F_INPUT_F32, 1, 0, 0.0), (F.F_MUL, 0, 1, 0.0), (F.F_CONST_F32, 0, 0, 0.25),
+               (F.F_GT, 2, 3, 0.0), (F.F_OUTPUT, 4, 0, 0.0)]
+    for prog, ins in ((abi.CHAIN_MASK_PROGRAM, [a, bb, c]), (positive, [bb]), (product, [bb, c])):
+        try:
+            got = abi.predicate_bits(prog, ins)
+        except abi.TwgError as e:
+            if e.code == abi.TWG_ERR_UNSUPPORTED and prog is not abi.CHAIN_MASK_PROGRAM:
+                pytest.skip(f"NVRTC is not installed here: {e}")
+            raise
+        (m,), _ = abi.fused(prog, ins, [np.bool_])
+        assert np.array_equal(got, m), f"predicate bits differ from the bool mask ({len(ins)} inputs, n={n})"
+
+
+@pytest.mark.parametrize("n,density", [(0, 0.5), (1, 1.0), (127, 0.5), (4096, 0.0), (4096, 1.0), (100003, 0.03),
+                                       (100003, 0.5), ((1 << 22) + 9, 0.97), ((1 << 23), 1.0), ((1 << 23) + 1, 0.002)])
+def test_masked_select_by_bits_matches_the_oracle(abi, n, density):
+    """Second half: compaction of dense src by a bit mask (sparse, dense and full-span chunk paths)."""
+    src = rnd(n, 201, -5, 5)
+    mask = np.random.default_rng(202).random(n) < density
+    assert_bit_equal(abi.masked_select_bits(src, mask), oracle.masked_select(src, mask), f"n={n} p={density}")
 
 
 def test_fused_programs_are_reference_counted(abi):

@@ -115,6 +115,45 @@ def test_compaction_publishes_its_own_count(abi, n):
             x.close()
 
 
+@pytest.mark.parametrize("n", [0, 129, 4096 * 5 + 1, (1 << 22) + 3])
+def test_fused_select_publishes_its_own_count(abi, n):
+    """twg_fused_select_f32_publish: predicate bits, then the compaction whose last chunk writes the
+    mailboxes; same counts and values as the byte mask followed by masked_select."""
+    from torch_webgpu.sharding import PeerStoreExchange
+    L = abi.lib()
+    world = 2
+    xs = [PeerStoreExchange(abi, r, world, ring=4) for r in range(world)]
+    program = abi.fused_compile(abi.CHAIN_MASK_PROGRAM)
+    try:
+        for x in xs:
+            x.connect_local(xs)
+        rng = np.random.default_rng(n + 7)
+        expect, keep = [], []
+        for r, x in enumerate(xs):
+            a, b, c = (rng.uniform(-3, 3, n).astype(np.float32) for _ in range(3))
+            a[::4 + r] = 0.0
+            (m,), _ = abi.fused(abi.CHAIN_MASK_PROGRAM, [a, b, c], [np.bool_]) if n else ((np.zeros(0, np.bool_),), None)
+            ins = [abi.DeviceArray(v) if n else abi.DeviceBuffer(16) for v in (a, b, c)]
+            out, res = abi.DeviceBuffer(max(4 * n, 4)), abi.DeviceBuffer(16)
+            ws_bytes = L.twg_fused_select_workspace_bytes(n)
+            ws = abi.DeviceBuffer(max(ws_bytes, 256))
+            in_ptrs = (ctypes.c_void_p * 3)(*[i.ptr for i in ins])
+            L.twg_reset_launch_count()
+            x.fused_select_publish(1, program, 0, n, in_ptrs, out.ptr, res.ptr, ws.ptr, ws_bytes, None)
+            assert L.twg_launch_count() == (3 if n else 2)   # bits + clear + compaction; clear + publish when empty
+            expect.append(oracle.masked_select(a, m))
+            keep.append((ins, out, res, ws))
+        for x in xs:
+            x.collect(1, None)
+        for r, x in enumerate(xs):
+            counts, offset, total = x.wait(1, timeout_ms=5000)
+            assert counts == [e.size for e in expect] and offset == sum(counts[:r]) and total == sum(counts)
+            assert_bit_equal(keep[r][1].download(np.float32, counts[r]), expect[r], f"rank {r} values")
+    finally:
+        for x in xs:
+            x.close()
+
+
 def test_a_device_status_travels_with_the_count(abi):
     from torch_webgpu.sharding import PeerStoreExchange
     xs = [PeerStoreExchange(abi, r, 2, ring=2) for r in range(2)]

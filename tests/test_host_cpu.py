@@ -101,13 +101,13 @@ def test_nvrtc_builds_generated_source_without_a_gpu(abi):
             pytest.skip(f"NVRTC is not installed here: {e}")
         raise
     assert abi.fused_kind(h) == "nvrtc"
-    # a predicate (one bool output over f32 inputs) also gets its select kernels, one per input
+    # a predicate (one bool output over f32 inputs) also gets the kernel that writes it as bits
     pred = [(abi.F_INPUT_F32, 0, 0, 0.0), (abi.F_INPUT_F32, 1, 0, 0.0), (abi.F_MUL, 0, 1, 0.0),
             (abi.F_CONST_F32, 0, 0, 0.25), (abi.F_GT, 2, 3, 0.0), (abi.F_OUTPUT, 4, 0, 0.0)]
     assert abi.fused_kind(abi.fused_compile(pred)) == "nvrtc"
     src = ctypes.c_char_p()
     abi.check(abi.lib().twg_fused_source(abi.fused_compile(pred), ctypes.byref(src)))
-    assert b"twg_fused_select_0" in src.value and b"twg_fused_select_1" in src.value
+    assert b"twg_fused_bits" in src.value
 
 
 @pytest.mark.skipif(torch.cuda.is_available(), reason="checks the behaviour of a machine without a GPU")

@@ -465,17 +465,17 @@ def test_compiled_chain_with_the_select_in_the_graph_is_one_launch():
     try:
         torch._dynamo.reset()
         torch_webgpu._C.reset_launch_count()
-        one = torch.compile(chain, backend=webgpu_backend, options={"fuse_select": True})(da, db, dc)
+        one = torch.compile(chain, backend=webgpu_backend)(da, db, dc)              # the default: mask as bits
         assert wc.last_compile_report["fused_selects"] == 1 and wc.last_compile_report["kinds"] == ["aot"]
-        assert torch_webgpu._C.launch_count() == 2                 # the workspace clear and the fused select
+        assert torch_webgpu._C.launch_count() == 3                 # predicate bits, workspace clear, compaction
         torch._dynamo.reset()
-        two = torch.compile(chain, backend=webgpu_backend)(da, db, dc)   # the default: mask kernel + compaction
+        two = torch.compile(chain, backend=webgpu_backend, options={"fuse_select": False})(da, db, dc)   # bool mask + masked_select
         assert wc.last_compile_report["fused_selects"] == 0
         assert one.dim() == 1 and torch.equal(one.cpu(), two.cpu())
         # transposed views do not meet the fused kernel's layout rule: same answer by the two-launch route
         torch._dynamo.reset()
         ta, tb, tc = (t.transpose(1, 2) for t in (da, db, dc))
-        got = torch.compile(chain, backend=webgpu_backend, options={"fuse_select": True})(ta, tb, tc)
+        got = torch.compile(chain, backend=webgpu_backend)(ta, tb, tc)
         y = torch.relu(F.silu(ta + tb) + tc)
         eager = torch.masked_select(ta, torch.bitwise_and(torch.eq(y, 0), torch.ne(ta, 0)))
         assert torch.equal(got.cpu(), eager.cpu())

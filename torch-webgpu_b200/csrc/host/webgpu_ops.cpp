@@ -89,8 +89,8 @@ std::vector<at::Tensor> run_fused(int64_t handle, at::TensorList inputs, c10::In
   return outs;
 }
 
-// masked_select(inputs[src_index], program(inputs)) without materialising the mask.  The fused
-// kernel needs dense, equally shaped float32 inputs; any other case (and programs the library has
+// masked_select(inputs[src_index], program(inputs)) with the mask kept as one bit per element in
+// scratch memory.  The fused path needs dense, equally shaped float32 inputs; any other case (and programs the library has
 // no select form for) runs the program and masked_select one after the other - same result.
 at::Tensor run_fused_select(int64_t handle, at::TensorList inputs, int64_t src_index) {
   TORCH_CHECK(!inputs.empty() && src_index >= 0 && src_index < static_cast<int64_t>(inputs.size()),
@@ -107,7 +107,7 @@ at::Tensor run_fused_select(int64_t handle, at::TensorList inputs, int64_t src_i
     core::DeviceScope scope(dev);
     void* stream = core::current_stream(dev);
     // one block holds the kernel's workspace and, behind it, the two result words
-    const size_t ws_bytes = (twg_masked_select_workspace_bytes(numel) + 255) / 256 * 256;
+    const size_t ws_bytes = (twg_fused_select_workspace_bytes(numel) + 255) / 256 * 256;
     at::Tensor scratch = at::empty({static_cast<int64_t>(ws_bytes + 2 * sizeof(int64_t))}, src.options().dtype(at::kByte));
     auto* result = reinterpret_cast<int64_t*>(static_cast<char*>(scratch.data_ptr()) + ws_bytes);
     at::Tensor out = at::empty({numel}, src.options());

@@ -199,14 +199,10 @@ static std::string generate_source(const TwgFusedInstr* prog, int n, const Analy
   s += line;
   if (a.is_predicate()) {
     s += "#include \"twg_compact.cuh\"\n";
-    for (int k = 0; k < a.nin; ++k) {
-      snprintf(line, sizeof(line),
-               "extern \"C\" __global__ void __launch_bounds__(kSelThreads, kSelCtasPerSm) twg_fused_select_%d(PwPtrs<%d> in, float* out, i64 n, "
-               "i64 nchunks, u64* ticket, u64* desc, i64* result, i64 budget) "
-               "{ select_fused_body<Prog, %d>(in, Prog{}, out, n, nchunks, ticket, desc, result, budget); }\n",
-               k, a.nin, k);
-      s += line;
-    }
+    snprintf(line, sizeof(line),
+             "extern \"C\" __global__ void __launch_bounds__(kBlock) twg_fused_bits(PwPtrs<%d> in, u32* bits, i64 n) "
+             "{ predicate_bits_body<Prog>(in, Prog{}, bits, n); }\n", a.nin);
+    s += line;
   }
   return s;
 }
@@ -264,26 +260,16 @@ typedef int (*AotLaunch)(const TwgIterDesc*, void* const*, cudaStream_t);
 template <class F>
 int aot_launch(const TwgIterDesc* d, void* const* ptrs, cudaStream_t s) { return launch_pointwise(F{}, d, ptrs, s); }
 
-// fused predicate + select with src = input 0 (the form the benchmark's chain takes)
-struct SelectArgs {
-  const void* const* inputs;
-  float* out;
-  i64 n, nchunks;
-  unsigned grid;  // persistent CTAs
-  u64 *ticket, *desc;
-  i64* result;
-  i64 budget;
-};
-typedef int (*AotSelect)(const SelectArgs&, cudaStream_t);
+// first half of the fused predicate + select: the predicate as one bit per element
+static unsigned bits_grid(i64 n, int nin) {
+  return (unsigned)std::min<i64>(std::max<i64>(predicate_bits_ctas(n, nin), 1), 0x7fffffff);
+}
+typedef int (*AotBits)(const void* const*, unsigned*, i64, cudaStream_t);
 template <class F>
-int aot_select0(const SelectArgs& a, cudaStream_t s) {
+int aot_bits(const void* const* inputs, unsigned* bits, i64 n, cudaStream_t s) {
   PwPtrs<F::NIN> in;
-  for (int k = 0; k < F::NIN; ++k) in.p[k] = const_cast<void*>(a.inputs[k]);
-  // the attribute is per device; setting it again costs microseconds
-  TWG_CUDA(cudaFuncSetAttribute(select_fused_kernel<F, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                (int)kSelSmemBytes));
-  select_fused_kernel<F, 0><<<a.grid, kSelThreads, kSelSmemBytes, s>>>(in, F{}, a.out, a.n, a.nchunks, a.ticket, a.desc,
-                                                                       a.result, a.budget);
+  for (int k = 0; k < F::NIN; ++k) in.p[k] = const_cast<void*>(inputs[k]);
+  predicate_bits_kernel<F><<<bits_grid(n, F::NIN), kBlock, 0, s>>>(in, F{}, bits, n);
   TWG_CHECK_LAUNCH();
   return TWG_OK;
 }
@@ -292,11 +278,11 @@ struct AotEntry {
   const TwgFusedInstr* prog;
   int n;
   AotLaunch launch;
-  AotSelect select0;  // nullptr: no ahead-of-time select for this program
+  AotBits bits;  // nullptr: not a predicate
 };
 static const AotEntry kAot[] = {
     {kProgAddRelu, (int)(sizeof(kProgAddRelu) / sizeof(TwgFusedInstr)), &aot_launch<AotAddRelu>, nullptr},
-    {kProgChainMask, (int)(sizeof(kProgChainMask) / sizeof(TwgFusedInstr)), &aot_launch<AotChainMask>, &aot_select0<AotChainMask>},
+    {kProgChainMask, (int)(sizeof(kProgChainMask) / sizeof(TwgFusedInstr)), &aot_launch<AotChainMask>, &aot_bits<AotChainMask>},
     {kProgChainMaskY, (int)(sizeof(kProgChainMaskY) / sizeof(TwgFusedInstr)), &aot_launch<AotChainMaskY>, nullptr},
 };
 
@@ -513,7 +499,7 @@ static int compile_cached(const std::string& source, std::vector<char>* cubin) {
 struct DeviceModule {
   CUmodule mod = nullptr;
   CUfunction dense = nullptr, tile = nullptr, strided32 = nullptr, strided64 = nullptr;
-  CUfunction select[TWG_MAX_TENSORS] = {};  // twg_fused_select_<k>, predicates only
+  CUfunction bits = nullptr;  // twg_fused_bits, predicates only
 };
 
 }  // namespace twg
@@ -526,7 +512,7 @@ struct TwgFusedProgram {
   std::string source;
   int kind = 0;  // 0 ahead-of-time, 1 NVRTC
   AotLaunch aot = nullptr;
-  AotSelect aot_select0 = nullptr;
+  AotBits aot_bits = nullptr;
   std::vector<char> cubin;
   std::mutex mu;
   std::map<int, DeviceModule> modules;  // per device ordinal
@@ -554,14 +540,8 @@ static int get_module(TwgFusedProgram* p, DeviceModule** out) {
       if (r != 0) return cu_fail(r, "cuModuleGetFunction");
     }
     if (p->an.is_predicate()) {
-      for (int k = 0; k < p->an.nin; ++k) {
-        char name[32];
-        snprintf(name, sizeof(name), "twg_fused_select_%d", k);
-        r = g_dyn.ModuleGetFunction(&m.select[k], m.mod, name);
-        if (r != 0) return cu_fail(r, "cuModuleGetFunction");
-        r = g_dyn.FuncSetAttribute(m.select[k], 8 /* CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES */, (int)kSelSmemBytes);
-        if (r != 0) return cu_fail(r, "cuFuncSetAttribute");
-      }
+      r = g_dyn.ModuleGetFunction(&m.bits, m.mod, "twg_fused_bits");
+      if (r != 0) return cu_fail(r, "cuModuleGetFunction");
     }
     it = p->modules.emplace(dev, m).first;
   }
@@ -648,7 +628,7 @@ extern "C" int twg_fused_compile(const TwgFusedInstr* prog, int ninstr, TwgFused
   p->an = an;
   p->source = source;
   for (const AotEntry& e : kAot)
-    if (same_program(prog, ninstr, e.prog, e.n)) { p->aot = e.launch; p->aot_select0 = e.select0; break; }
+    if (same_program(prog, ninstr, e.prog, e.n)) { p->aot = e.launch; p->aot_bits = e.bits; break; }
   if (p->aot) {
     p->kind = 0;
   } else {
@@ -743,81 +723,105 @@ extern "C" int twg_fused_release(TwgFusedProgram* p) {
 }
 
 // ------------------------------------------------------------------------------------------
-// fused predicate + select
+// fused predicate + select: the predicate as one bit per element, then the compaction by bits
 // ------------------------------------------------------------------------------------------
 namespace twg {
 template <int NIN>
-static int jit_select(TwgFusedProgram* p, int src, const SelectArgs& a, cudaStream_t stream) {
+static int jit_bits(TwgFusedProgram* p, const void* const* inputs, unsigned* bits, i64 n, cudaStream_t stream) {
   DeviceModule* m = nullptr;
   if (int rc = get_module(p, &m)) return rc;
   PwPtrs<NIN> in;
-  for (int k = 0; k < NIN; ++k) in.p[k] = const_cast<void*>(a.inputs[k]);
-  float* out = a.out;
-  i64 n = a.n, nchunks = a.nchunks, budget = a.budget;
-  u64 *ticket = a.ticket, *desc = a.desc;
-  i64* result = a.result;
-  void* args[] = {&in, &out, &n, &nchunks, &ticket, &desc, &result, &budget};
-  CUresult r = g_dyn.LaunchKernel(m->select[src], a.grid, 1, 1, kSelThreads, 1, 1, kSelSmemBytes,
-                                  reinterpret_cast<CUstream>(stream), args, nullptr);
+  for (int k = 0; k < NIN; ++k) in.p[k] = const_cast<void*>(inputs[k]);
+  void* args[] = {&in, &bits, &n};
+  CUresult r = g_dyn.LaunchKernel(m->bits, bits_grid(n, NIN), 1, 1, kBlock, 1, 1, 0, reinterpret_cast<CUstream>(stream), args, nullptr);
   if (r != 0) return cu_fail(r, "cuLaunchKernel");
   count_launch();
   return TWG_OK;
 }
-}  // namespace twg
 
-extern "C" int twg_fused_select_f32(const TwgFusedProgram* cp, int src_input, int64_t numel, const void* const* inputs,
-                                    float* out, int64_t* result_dev, void* workspace, size_t workspace_bytes,
-                                    void* stream) {
-  TWG_TRACE("twg_fused_select_f32");
-  TWG_REQUIRE(cp && inputs && result_dev, "twg_fused_select_f32: null argument");
+// Layout of the fused select's workspace: ticket header and chunk descriptors (as masked_select's),
+// rounded to 256 bytes, then the bit mask.
+static size_t select_bits_offset(int64_t numel) { return (twg_masked_select_workspace_bytes(numel) + 255) / 256 * 256; }
+
+static int predicate_bits_impl(const TwgFusedProgram* cp, int64_t numel, const void* const* inputs, unsigned* bits,
+                               void* stream) {
+  TWG_REQUIRE(cp && inputs, "twg_fused_predicate_bits: null argument");
   TwgFusedProgram* p = const_cast<TwgFusedProgram*>(cp);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (!p->an.is_predicate())
+    return set_error(TWG_ERR_UNSUPPORTED, "twg_fused_predicate_bits: the program is not a predicate (one bool output over f32 inputs)");
+  TWG_REQUIRE(numel >= 0, "twg_fused_predicate_bits: negative numel");
+  if (numel == 0) return TWG_OK;
+  TWG_REQUIRE(bits != nullptr && is_aligned(bits, 16), "twg_fused_predicate_bits: bits is null or not 16-byte aligned");
+  for (int k = 0; k < p->an.nin; ++k) {
+    TWG_REQUIRE(inputs[k] != nullptr, "twg_fused_predicate_bits: input %d is null", k);
+    if (!is_aligned(inputs[k], 16))
+      return set_error(TWG_ERR_UNSUPPORTED, "twg_fused_predicate_bits: input %d is not 16-byte aligned", k);
+  }
+  TWG_REQUIRE(predicate_bits_ctas(numel, p->an.nin) <= 0x7fffffff, "twg_fused_predicate_bits: %lld elements exceed the grid limit",
+              (long long)numel);
+  if (p->aot_bits) return p->aot_bits(inputs, bits, numel, s);
+  if (p->kind != 1)
+    return set_error(TWG_ERR_UNSUPPORTED, "twg_fused_predicate_bits: this ahead-of-time program has no predicate form");
+  switch (p->an.nin) {
+    case 1: return jit_bits<1>(p, inputs, bits, numel, s);
+    case 2: return jit_bits<2>(p, inputs, bits, numel, s);
+    case 3: return jit_bits<3>(p, inputs, bits, numel, s);
+    case 4: return jit_bits<4>(p, inputs, bits, numel, s);
+    case 5: return jit_bits<5>(p, inputs, bits, numel, s);
+    case 6: return jit_bits<6>(p, inputs, bits, numel, s);
+    default: return jit_bits<7>(p, inputs, bits, numel, s);
+  }
+}
+
+// Checks shared by the two forms of the fused select; *bits is where the predicate's bits go.
+static int fused_select_check(const TwgFusedProgram* p, int src_input, int64_t numel, const void* const* inputs,
+                              void* workspace, size_t workspace_bytes, unsigned** bits) {
+  TWG_REQUIRE(p && inputs, "twg_fused_select_f32: null argument");
   if (!p->an.is_predicate())
     return set_error(TWG_ERR_UNSUPPORTED, "twg_fused_select_f32: the program is not a predicate (one bool output over f32 inputs)");
   TWG_REQUIRE(src_input >= 0 && src_input < p->an.nin, "twg_fused_select_f32: src_input %d out of range", src_input);
   TWG_REQUIRE(numel >= 0, "twg_fused_select_f32: negative numel");
-  g_last_path = kPathNone;
-  if (numel == 0) return ms_clear(nullptr, 0, result_dev, s);
-  TWG_REQUIRE(out != nullptr && is_aligned(out, 4), "twg_fused_select_f32: out is null or misaligned");
-  for (int k = 0; k < p->an.nin; ++k) {
-    TWG_REQUIRE(inputs[k] != nullptr, "twg_fused_select_f32: input %d is null", k);
-    if (!is_aligned(inputs[k], 16))
-      return set_error(TWG_ERR_UNSUPPORTED, "twg_fused_select_f32: input %d is not 16-byte aligned", k);
-  }
-  const int64_t chunk = kSelChunk;
-  const int64_t nchunks = (numel + chunk - 1) / chunk;
-  TWG_REQUIRE(nchunks <= 0x7fffffff, "twg_fused_select_f32: %lld elements exceed the chunk limit", (long long)numel);
-  const size_t need = kMsHeaderBytes + (size_t)nchunks * sizeof(u64);
+  *bits = nullptr;
+  if (numel == 0) return TWG_OK;
+  const size_t need = twg_fused_select_workspace_bytes(numel);
   TWG_REQUIRE(workspace != nullptr && workspace_bytes >= need && is_aligned(workspace, 256),
               "twg_fused_select_f32: workspace of %zu bytes is smaller than the %zu required or not 256-byte aligned",
               workspace_bytes, need);
-  if (int rc = ms_clear(workspace, need, result_dev, s)) return rc;
-  SelectArgs a;
-  a.inputs = inputs;
-  a.out = out;
-  a.n = numel;
-  a.nchunks = nchunks;
-  a.grid = (unsigned)std::min<int64_t>(nchunks, (int64_t)sm_count() * kSelCtasPerSm);  // persistent CTAs
-  a.ticket = static_cast<u64*>(workspace);
-  a.desc = reinterpret_cast<u64*>(static_cast<char*>(workspace) + kMsHeaderBytes);
-  a.result = reinterpret_cast<i64*>(result_dev);
-  a.budget = ms_poll_budget();
-  int rc;
-  if (p->aot_select0 && src_input == 0) {
-    rc = p->aot_select0(a, s);
-  } else if (p->kind == 1) {
-    switch (p->an.nin) {
-      case 1: rc = jit_select<1>(p, src_input, a, s); break;
-      case 2: rc = jit_select<2>(p, src_input, a, s); break;
-      case 3: rc = jit_select<3>(p, src_input, a, s); break;
-      case 4: rc = jit_select<4>(p, src_input, a, s); break;
-      case 5: rc = jit_select<5>(p, src_input, a, s); break;
-      case 6: rc = jit_select<6>(p, src_input, a, s); break;
-      default: rc = jit_select<7>(p, src_input, a, s); break;
-    }
-  } else {
-    return set_error(TWG_ERR_UNSUPPORTED, "twg_fused_select_f32: this ahead-of-time program has no select form for input %d", src_input);
-  }
-  if (rc == TWG_OK) g_last_path = kPathDense;
-  return rc;
+  *bits = reinterpret_cast<unsigned*>(static_cast<char*>(workspace) + select_bits_offset(numel));
+  return TWG_OK;
+}
+}  // namespace twg
+
+extern "C" int twg_fused_predicate_bits(const TwgFusedProgram* p, int64_t numel, const void* const* inputs, uint32_t* bits,
+                                        void* stream) {
+  TWG_TRACE("twg_fused_predicate_bits");
+  return predicate_bits_impl(p, numel, inputs, bits, stream);
+}
+
+extern "C" size_t twg_fused_select_workspace_bytes(int64_t numel) {
+  if (numel < 0) numel = 0;
+  return select_bits_offset(numel) + (size_t)predicate_bits_bytes(numel);
+}
+
+extern "C" int twg_fused_select_f32(const TwgFusedProgram* p, int src_input, int64_t numel, const void* const* inputs,
+                                    float* out, int64_t* result_dev, void* workspace, size_t workspace_bytes,
+                                    void* stream) {
+  TWG_TRACE("twg_fused_select_f32");
+  unsigned* bits = nullptr;
+  if (int rc = fused_select_check(p, src_input, numel, inputs, workspace, workspace_bytes, &bits)) return rc;
+  if (int rc = predicate_bits_impl(p, numel, inputs, bits, stream)) return rc;
+  return twg_masked_select_bits_f32(static_cast<const float*>(inputs[src_input]), bits, numel, out, result_dev, workspace,
+                                    select_bits_offset(numel), stream);
+}
+
+extern "C" int twg_fused_select_f32_publish(const TwgFusedProgram* p, int src_input, int64_t numel,
+                                            const void* const* inputs, float* out, int64_t* result_dev, void* workspace,
+                                            size_t workspace_bytes, void* xchg, int64_t seq, void* stream) {
+  TWG_TRACE("twg_fused_select_f32_publish");
+  unsigned* bits = nullptr;
+  if (int rc = fused_select_check(p, src_input, numel, inputs, workspace, workspace_bytes, &bits)) return rc;
+  if (int rc = predicate_bits_impl(p, numel, inputs, bits, stream)) return rc;
+  return twg_masked_select_bits_f32_publish(static_cast<const float*>(inputs[src_input]), bits, numel, out, result_dev,
+                                            workspace, select_bits_offset(numel), xchg, seq, stream);
 }

@@ -79,6 +79,7 @@ __device__ __forceinline__ u32 nonzero_nibble(u32 w) {
 constexpr int kMsDense = 0;    // src and mask dense
 constexpr int kMsRowMask = 1;  // src dense, one mask byte per row
 constexpr int kMsStrided = 2;  // both through the iteration descriptor (32-bit index math)
+constexpr int kMsBits = 3;     // src dense; `mask` points at one BIT per element (predicate_bits_body's output)
 
 // Offsets of logical element `lin` in src and mask; returns its coordinate along dimension 0, so
 // that a caller walking consecutive elements can step by the dimension-0 strides until the
@@ -210,6 +211,26 @@ __global__ void __launch_bounds__(kMsThreads, 4)
       if (lane == 0) sm.cnt[span0 + i] = (unsigned short)span;
     }
     __syncwarp();
+  } else if constexpr (MODE == kMsBits) {
+    // the mask already is one bit per element: every warp copies the words of its own stretch
+    // (16 per span, 128-byte runs) and counts them, half a warp per span
+    const u32* gbits = reinterpret_cast<const u32*>(mask);
+    const i64 total_words = ((n + 127) / 128) * 4;  // what the producer wrote (zero at and beyond n)
+    const i64 gw0 = chunk_base / 32 + (i64)span0 * 16;
+    constexpr int kWords = CH * 16;
+#pragma unroll
+    for (int j0 = 0; j0 < kWords; j0 += 32) {
+      const int idx = j0 + lane;
+      u32 word = 0;
+      if (idx < kWords && gw0 + idx < total_words) word = ld_b32(gbits + gw0 + idx);
+      if (idx < kWords) bits[span0 * 16 + idx] = word;
+      u32 cw = __popc(word);
+      c += cw;
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) cw += __shfl_xor_sync(0xffffffffu, cw, o);
+      if ((lane & 15) == 0 && idx < kWords) sm.cnt[span0 + (idx >> 4)] = (unsigned short)cw;
+    }
+    __syncwarp();
   } else if constexpr (MODE == kMsStrided) {
     // a warp takes whole spans; lane l looks at element 32 g + l of word g, so that neighbouring
     // lanes read neighbouring mask bytes, and a ballot is the word
@@ -300,7 +321,7 @@ __global__ void __launch_bounds__(kMsThreads, 4)
   // A warp that made its own bits (dense mode) starts fetching its first span right away: the
   // loads are in flight across the barrier and the look-back below.
   MsSpanRegs next;
-  const bool early = MODE == kMsDense && full_chunk;
+  const bool early = (MODE == kMsDense && full_chunk) || MODE == kMsBits;  // the warp made its own bits
   if (early) load_span(next, span0);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
@@ -570,6 +591,27 @@ static void launch_dense(int chunk_tiles, unsigned nchunks, cudaStream_t s, cons
 #undef TWG_MS_LAUNCH
 }
 
+// Compaction of dense src by a bit mask (one bit per element, as predicate_bits_body writes it).
+// `workspace` holds the ticket header and the chunk descriptors (twg_masked_select_workspace_bytes).
+int ms_select_from_bits(const float* src, const unsigned* bits, float* out, int64_t n, int64_t* result_dev,
+                        void* workspace, cudaStream_t s, const MsPublish& pub) {
+  const int chunk_tiles = dense_chunk_tiles(n);
+  const int64_t tile_elems = (int64_t)chunk_tiles * kMsRound;
+  const int64_t nchunks = (n + tile_elems - 1) / tile_elems;
+  TWG_REQUIRE(nchunks <= 0x7fffffff, "fused select: %lld elements exceed the chunk limit", (long long)n);
+  if (int rc = ms_clear(workspace, kMsHeaderBytes + (size_t)nchunks * sizeof(u64), result_dev, s)) return rc;
+  FastDiv32 row_len;
+  row_len.d = 1u;
+  make_fastdiv(row_len.d, &row_len.m, &row_len.s);
+  StridedDesc<2, u32> sd;
+  std::memset(&sd, 0, sizeof(sd));
+  launch_dense<kMsBits>(chunk_tiles, (unsigned)nchunks, s, src, reinterpret_cast<const u8*>(bits), out, n,
+                        static_cast<u64*>(workspace), reinterpret_cast<u64*>(static_cast<char*>(workspace) + kMsHeaderBytes),
+                        reinterpret_cast<i64*>(result_dev), ms_poll_budget(), row_len, sd, pub);
+  TWG_CHECK_LAUNCH();
+  return TWG_OK;
+}
+
 }  // namespace twg
 
 using namespace twg;
@@ -681,6 +723,51 @@ extern "C" int twg_masked_select_f32_publish(const TwgIterDesc* desc, const floa
   if (int rc = masked_select_impl(desc, src, mask, out, result_dev, workspace, workspace_bytes, stream, pub, &fused)) return rc;
   // layouts served by the one-tile-per-CTA kernel, and empty inputs: the publish kernel behind the compaction
   if (!fused) return twg_exchange_publish(xchg, seq, result_dev, stream);
+  return TWG_OK;
+}
+
+// masked_select of dense src by a bit mask (bit i of 32-bit word w = element 32 w + i), as
+// twg_fused_predicate_bits writes it.
+static int select_bits_impl(const float* src, const uint32_t* bits, int64_t numel, float* out, int64_t* result_dev,
+                            void* workspace, size_t workspace_bytes, void* stream, const MsPublish& pub, bool* published) {
+  if (published) *published = false;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  TWG_REQUIRE(result_dev != nullptr && numel >= 0, "twg_masked_select_bits_f32: null result or negative numel");
+  g_last_path = kPathNone;
+  if (numel == 0) return ms_clear(nullptr, 0, result_dev, s);
+  TWG_REQUIRE(src && bits && out, "twg_masked_select_bits_f32: null argument");
+  TWG_REQUIRE(is_aligned(src, 16) && is_aligned(bits, 16) && is_aligned(out, 4),
+              "twg_masked_select_bits_f32: src and bits must be 16-byte aligned, out 4-byte aligned");
+  const size_t need = twg_masked_select_workspace_bytes(numel);
+  TWG_REQUIRE(workspace != nullptr && workspace_bytes >= need && is_aligned(workspace, 8),
+              "twg_masked_select_bits_f32: workspace of %zu bytes is smaller than the %zu required or misaligned",
+              workspace_bytes, need);
+  if (int rc = ms_select_from_bits(src, bits, out, numel, result_dev, workspace, s, pub)) return rc;
+  g_last_path = kPathDense;
+  if (published) *published = pub.nranks != 0;
+  return TWG_OK;
+}
+
+extern "C" size_t twg_predicate_bits_bytes(int64_t numel) { return (size_t)predicate_bits_bytes(numel < 0 ? 0 : numel); }
+
+extern "C" int twg_masked_select_bits_f32(const float* src, const uint32_t* bits, int64_t numel, float* out,
+                                          int64_t* result_dev, void* workspace, size_t workspace_bytes, void* stream) {
+  TWG_TRACE("twg_masked_select_bits_f32");
+  MsPublish none;
+  std::memset(&none, 0, sizeof(none));
+  return select_bits_impl(src, bits, numel, out, result_dev, workspace, workspace_bytes, stream, none, nullptr);
+}
+
+extern "C" int twg_masked_select_bits_f32_publish(const float* src, const uint32_t* bits, int64_t numel, float* out,
+                                                  int64_t* result_dev, void* workspace, size_t workspace_bytes, void* xchg,
+                                                  int64_t seq, void* stream) {
+  TWG_TRACE("twg_masked_select_bits_f32_publish");
+  MsPublish pub;
+  std::memset(&pub, 0, sizeof(pub));
+  if (int rc = xchg_publish_slots(xchg, seq, &pub)) return rc;
+  bool published = false;
+  if (int rc = select_bits_impl(src, bits, numel, out, result_dev, workspace, workspace_bytes, stream, pub, &published)) return rc;
+  if (!published) return twg_exchange_publish(xchg, seq, result_dev, stream);  // empty input
   return TWG_OK;
 }
 

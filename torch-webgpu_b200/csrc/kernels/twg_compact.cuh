@@ -104,212 +104,106 @@ __device__ __forceinline__ void flush_stage(const float* stage, float* out, i64 
 }
 
 
-// Look-back for callers whose runs are short compared with an L2 round trip: as many runs are in
-// flight as there are CTAs, so the nearest resolved prefix is typically a hundred or more
-// descriptors back.  One poll fetches DEPTH * 32 descriptors at once (DEPTH coalesced loads in
-// flight together) and consumes them 32 at a time with the same rules as lookback_resolve.
-template <int DEPTH>
-__device__ __forceinline__ i64 lookback_resolve_deep(i64 tile, u32 tile_total, u64* desc, i64* result, i64 poll_budget) {
-  const int lane = threadIdx.x & 31;
-  if (tile == 0) return 0;
-  if (poll_budget < 0) poll_budget = -poll_budget;
-  u64 excl = 0;
-  i64 look = tile - 1;  // nearest predecessor not yet accounted for
-  i64 polls = 0;
-  bool done = false, timed_out = false;
-  while (!done) {
-    u64 d[DEPTH];
-#pragma unroll
-    for (int q = 0; q < DEPTH; ++q) {
-      const i64 idx = look - q * 32 - lane;
-      d[q] = idx >= 0 ? ld_relaxed_u64(desc + idx) : kMsPrefix;  // before run 0: prefix of 0
-    }
-    bool stalled = false;
-#pragma unroll
-    for (int q = 0; q < DEPTH; ++q) {
-      if (done || stalled) continue;
-      const u32 status = (u32)(d[q] >> 62);
-      const u32 invalid = __ballot_sync(0xffffffffu, status == 0u);
-      const u32 prefix = __ballot_sync(0xffffffffu, status == 2u);
-      const int first_invalid = invalid ? __ffs(invalid) - 1 : 32;
-      const int first_prefix = prefix ? __ffs(prefix) - 1 : 32;
-      if (first_prefix < first_invalid) {
-        excl += warp_sum_u64(lane <= first_prefix ? (d[q] & kMsValueMask) : 0ull);
-        done = true;
-      } else {
-        if (first_invalid > 0) {
-          excl += warp_sum_u64(lane < first_invalid ? (d[q] & kMsValueMask) : 0ull);
-          look -= first_invalid;
-        }
-        if (first_invalid < 32) stalled = true;  // an unpublished run: poll again from there
-      }
-    }
-    if (done) break;
-    if (stalled) {
-      if (++polls > poll_budget) { timed_out = true; break; }
-      if (polls > 64) __nanosleep(64);
-    }
-  }
-  if (timed_out) {
-    excl = 0;
-    if (lane == 0) {
-      result[1] = (i64)kErrTimeout;
-      __threadfence();  // the status is visible before the prefix that lets later runs finish
-    }
-  }
-  if (lane == 0) st_relaxed_u64(desc + tile, kMsPrefix | ((excl + (u64)tile_total) & kMsValueMask));
-  return (i64)excl;
+// ------------------------------------------------------------------------------------------
+// Fused predicate + select, first half: a pointwise predicate over dense f32 inputs, written as
+// ONE BIT per element.  The compaction kernel (masked_select.cu) reads those bits instead of a
+// byte mask, so a predicate that feeds nothing but masked_select of one of its inputs costs
+// 4 NIN + 1/8 bytes per element here and 4 1/8 + 4 k/N there, instead of 4 NIN + 1 and 5 + 4 k/N
+// with a bool tensor in between: 1.75 bytes per element less, and both launches are the dense
+// streaming kernels that run at the memory roofline.
+//
+// A warp takes 128 U consecutive elements (U = 4, 2, 1 for 1, 2, more inputs).  In each of its U rounds a lane takes one quad (4
+// consecutive elements, one 128-bit load per input; all rounds' loads are issued before the first
+// predicate is evaluated), evaluates the predicate four times and holds a nibble; the eight lanes
+// of a group OR their shifted nibbles into the word of their 32 elements (one redux per group).
+// Lane 8 g + t (t < U) then stores word g of round t, so the warp writes its 16 U bytes of bits
+// with one store instruction.  Bit i of word w is element 32 w + i; bits at and beyond n are
+// zero, and the buffer is written in whole 16-byte vectors (128 elements).
+// (An earlier one-launch kernel evaluated the predicate and staged the selected values in one
+// sweep over 16384-element chunks with a CTA-wide barrier around every look-back; it was no faster
+// than writing a byte mask and compacting in a second launch: 0.85 ms against 0.83 ms for the
+// three-input silu chain at 2^28 elements.)
+// ------------------------------------------------------------------------------------------
+// Bytes of the bit buffer for n elements.
+__host__ __device__ constexpr unsigned long long predicate_bits_bytes(long long n) {
+  return (unsigned long long)((n + 127) / 128) * 16ull;
+}
+// Rounds per warp: the unroll the dense pointwise kernel uses for as many inputs (one round with
+// three or more inputs keeps the kernel near 32 registers, i.e. eight CTAs per SM, which this
+// issue-bound loop needs more than it needs loads in flight per thread).
+__host__ __device__ constexpr int predicate_bits_rounds(int nin) { return nin <= 1 ? 4 : (nin == 2 ? 2 : 1); }
+// CTAs that cover n elements: every warp takes exactly one stretch.
+__host__ __device__ constexpr long long predicate_bits_ctas(long long n, int nin) {
+  const long long per_cta = 128ll * predicate_bits_rounds(nin) * (kBlock / 32);
+  return (n + per_cta - 1) / per_cta;
 }
 
-// ------------------------------------------------------------------------------------------
-// Fused predicate + select: out = src[pred(inputs)] in one pass, where `pred` is a pointwise
-// functor over dense f32 inputs with one bool output and src is one of its inputs.  The boolean
-// mask never exists in memory: HBM sees every input element once (4 * NIN bytes) and the selected
-// values once (4k bytes), instead of writing the mask, reading it back and reading src again.
-//
-// Persistent CTAs of 16 warps, three per SM, draw chunks of 16384 consecutive elements from a
-// ticket counter.  Warp w owns the contiguous span [w*1024, (w+1)*1024) of the chunk and walks it
-// in steps of 128 elements (one float4 quad per lane and input, the loads of kSelUnroll steps in
-// flight together).  Per step the warp evaluates the predicate, ranks its selected elements with
-// four independent ballots + popc and appends their src values to its own region of a 64 KB
-// shared-memory stage - no CTA-wide barrier inside the loop.  The sixteen warp totals give the
-// chunk count; it is published for the decoupled look-back (one link per chunk), warp 0 resolves
-// the exclusive prefix (bounded wait), and every warp writes its run to out[prefix + offset of
-// the warp ...] with 128-bit stores where aligned.
-//
-// Why these sizes (measured on B200, 2^28 elements, the three-input silu chain): a look-back
-// costs several L2 round trips whatever the chunk size - the nearest predecessors are staged at
-// the same moment by other SMs - so small chunks are look-back bound (2048 elements: 1.47 ms,
-// 4096: 0.99, 8192: 0.86, 16384: 0.78); the two other CTAs of the SM and their 32 warps cover the
-// wait.  A warp-specialised variant (one CTA per SM, TMA bulk loads into an mbarrier ring, scan
-// warps resolving several units at once) kept HBM busy but left only 16 warps for the predicate
-// arithmetic and measured 1.03 ms.
-// ------------------------------------------------------------------------------------------
-constexpr int kSelWarps = 16;
-constexpr int kSelThreads = kSelWarps * 32;
-constexpr int kSelChunk = 16384;
-constexpr int kSelSpan = kSelChunk / kSelWarps;  // 1024 elements per warp
-constexpr int kSelSteps = kSelSpan / 128;        // 8 steps of 32 quads
-constexpr int kSelCtasPerSm = 3;
-constexpr unsigned kSelSmemBytes = kSelChunk * 4u;  // dynamic: the stage
-constexpr int kSelLookDepth = 4;                    // 128 descriptors per poll
-// Steps whose loads are issued together: about 24 registers of loaded data per thread.
-__host__ __device__ constexpr int sel_unroll(int nin) { return nin == 1 ? 4 : (nin <= 3 ? 2 : 1); }
-
-struct SelShared {
-  u32 warp_total[kSelWarps];
-  i64 chunk;
-  i64 excl;
-};
-
-template <class F, int SRC>
-__device__ __forceinline__ void select_fused_body(const PwPtrs<F::NIN>& in, const F& f, float* out, i64 n, i64 nchunks,
-                                                  u64* ticket, u64* desc, i64* result, i64 poll_budget) {
-  static_assert(F::NOUT == 1 && F::kOutByteMask == 1u && F::kInByteMask == 0u, "predicate over f32 inputs");
-  static_assert(SRC >= 0 && SRC < F::NIN, "src is one of the inputs");
-  constexpr int NIN = F::NIN;
-  constexpr int U = sel_unroll(NIN);
-  __shared__ SelShared sm;
-  extern __shared__ float sel_stage[];  // [kSelWarps][kSelSpan]
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const u32 below = (1u << lane) - 1u;
-  float* region = sel_stage + warp * kSelSpan;
-
-  for (i64 iter = 0;; ++iter) {
-    i64 chunk = (i64)blockIdx.x + iter * (i64)gridDim.x;
-    if (ticket != nullptr) {
-      if (threadIdx.x == 0) sm.chunk = (i64)atomicAdd(ticket, 1ull);
-      __syncthreads();
-      chunk = sm.chunk;
-    }
-    if (chunk >= nchunks) return;
-    const i64 span_base = chunk * (i64)kSelChunk + (i64)warp * kSelSpan;
-    u32 running = 0;
-#pragma unroll 1
-    for (int s0 = 0; s0 < kSelSteps; s0 += U) {
-      u32 v[U][NIN][4];
+// The predicate over one quad as a nibble (bit b = element b).
+template <class F>
+__device__ __forceinline__ u32 predicate_nibble(const F& f, const u32 (&x)[4][F::NIN]) {
+  u32 nib = 0;
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const i64 e = span_base + (i64)(s0 + u) * 128 + lane * 4;
+  for (int b = 0; b < 4; ++b) {
+    u32 y[1];
+    f(x[b], y);
+    nib |= (y[0] & 1u) << b;
+  }
+  return nib;
+}
+
+template <class F>
+__device__ __forceinline__ void predicate_bits_body(const PwPtrs<F::NIN>& in, const F& f, u32* bits, i64 n) {
+  static_assert(F::NOUT == 1 && F::kOutByteMask == 1u && F::kInByteMask == 0u, "predicate over f32 inputs");
+  constexpr int NIN = F::NIN;
+  constexpr int U = predicate_bits_rounds(NIN);
+  const int lane = threadIdx.x & 31;
+  const int group = lane >> 3, t = lane & 7;
+  const u32 members = 0xffu << (lane & 24);   // the eight lanes of a group hold the 32 elements of one word
+  const i64 nquads = ((n + 127) / 128) * 32;  // whole rounds: 32 quads = 128 elements = one 16-byte vector of bits
+  {  // the grid covers every stretch (predicate_bits_ctas)
+    const i64 q0 = ((i64)blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5)) * (32 * U);
+    if (q0 >= nquads) return;
+    u32 x[U][4][NIN];
+    u32 mine = 0;  // word `group` of round t
+    if ((q0 + 32 * U) * 4 <= n) {
+#pragma unroll
+      for (int u = 0; u < U; ++u)
 #pragma unroll
         for (int k = 0; k < NIN; ++k) {
-          if (e + 3 < n) {
-            const uint4 q = ld_v4(reinterpret_cast<const float*>(in.p[k]) + e);
-            v[u][k][0] = q.x; v[u][k][1] = q.y; v[u][k][2] = q.z; v[u][k][3] = q.w;
-          } else {
+          const uint4 v = ld_v4(static_cast<const float*>(in.p[k]) + 4 * (q0 + lane) + 128 * u);
+          x[u][0][k] = v.x; x[u][1][k] = v.y; x[u][2][k] = v.z; x[u][3][k] = v.w;
+        }
 #pragma unroll
-            for (int b = 0; b < 4; ++b)
-              v[u][k][b] = (e + b < n) ? ld_b32(reinterpret_cast<const float*>(in.p[k]) + e + b) : 0u;
-          }
+      for (int u = 0; u < U; ++u) {
+        const u32 word = __reduce_or_sync(members, predicate_nibble<F>(f, x[u]) << (t * 4));
+        if (t == u) mine = word;
+      }
+    } else {  // the stretch that holds element n - 1
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const i64 e = 4 * (q0 + u * 32 + lane);
+#pragma unroll
+        for (int k = 0; k < NIN; ++k) {
+          const float* p = static_cast<const float*>(in.p[k]);
+#pragma unroll
+          for (int b = 0; b < 4; ++b) x[u][b][k] = (e + b < n) ? ld_b32(p + e + b) : 0u;
         }
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        // elements of this lane's quad that exist: 4 everywhere except at the very end of the data
-        const i64 left = n - (span_base + (i64)(s0 + u) * 128 + lane * 4);
-        const int live = left >= 4 ? 4 : (left > 0 ? (int)left : 0);
-        u32 flags = 0;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          u32 x[NIN], y[1];
-#pragma unroll
-          for (int k = 0; k < NIN; ++k) x[k] = v[u][k][q];
-          f(x, y);
-          if ((y[0] & 1u) && q < live) flags |= 1u << q;
-        }
-        // rank = selected elements of the lanes below (four independent ballots) + own earlier ones
-        u32 pos = running;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const u32 bal = __ballot_sync(0xffffffffu, (flags >> q) & 1u);
-          pos += __popc(bal & below);
-          running += __popc(bal);
-        }
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-          if ((flags >> q) & 1u) region[pos++] = __uint_as_float(v[u][SRC][q]);
+        const i64 left = n - 4 * (q0 + u * 32 + lane);  // elements of this quad that exist
+        const u32 valid = left >= 4 ? 0xfu : (left <= 0 ? 0u : (1u << (int)left) - 1u);
+        const u32 word = __reduce_or_sync(members, (predicate_nibble<F>(f, x[u]) & valid) << (t * 4));
+        if (t == u) mine = word;
       }
     }
-    if (lane == 0) sm.warp_total[warp] = running;
-    __syncthreads();
-    // offset of this warp's run inside the chunk, and the chunk count
-    u32 t = lane < kSelWarps ? sm.warp_total[lane] : 0u;
-    u32 warp_off = lane < warp ? t : 0u;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      t += __shfl_xor_sync(0xffffffffu, t, o);
-      warp_off += __shfl_xor_sync(0xffffffffu, warp_off, o);
-    }
-    if (warp == 0) {
-      if (lane == 0) lookback_publish(chunk, t, desc, poll_budget);
-      const i64 excl = lookback_resolve_deep<kSelLookDepth>(chunk, t, desc, result, poll_budget);
-      if (lane == 0) {
-        sm.excl = excl;
-        if (chunk == nchunks - 1) result[0] = excl + (i64)t;
-      }
-    }
-    __syncthreads();
-    // every warp writes its own run: 128-bit stores between the first and last 16-byte boundary
-    float* dst = out + sm.excl + warp_off;
-    const u32 head = min(running, (u32)(((16u - (u32)(reinterpret_cast<unsigned long long>(dst) & 15ull)) & 15u) >> 2));
-    if ((u32)lane < head) dst[lane] = region[lane];
-    const u32 nvec = (running - head) >> 2;
-    float4* dst4 = reinterpret_cast<float4*>(dst + head);
-    for (u32 i = lane; i < nvec; i += 32) {
-      const float* r = region + head + 4 * i;
-      dst4[i] = make_float4(r[0], r[1], r[2], r[3]);
-    }
-    const u32 tail0 = head + 4 * nvec;
-    if (tail0 + lane < running) dst[tail0 + lane] = region[tail0 + lane];
-    __syncthreads();  // the stage, warp_total and excl are rewritten by the next chunk
+    if (t < U && q0 + t * 32 < nquads) bits[(q0 >> 3) + 4 * t + group] = mine;
   }
 }
 
-template <class F, int SRC>
-__global__ void __launch_bounds__(kSelThreads, kSelCtasPerSm)
-    select_fused_kernel(PwPtrs<F::NIN> in, F f, float* out, i64 n, i64 nchunks, u64* ticket, u64* desc, i64* result,
-                        i64 poll_budget) {
-  select_fused_body<F, SRC>(in, f, out, n, nchunks, ticket, desc, result, poll_budget);
+template <class F>
+__global__ void __launch_bounds__(kBlock) predicate_bits_kernel(PwPtrs<F::NIN> in, F f, u32* bits, i64 n) {
+  predicate_bits_body<F>(in, f, bits, n);
 }
 
 }  // namespace twg

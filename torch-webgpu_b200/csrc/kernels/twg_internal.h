@@ -60,6 +60,9 @@ struct MsPublish {
   unsigned long long seq;
 };
 int xchg_publish_slots(void* xchg, int64_t seq, MsPublish* out);
+// Second half of the fused predicate + select (masked_select.cu): compaction by a bit mask.
+int ms_select_from_bits(const float* src, const unsigned* bits, float* out, int64_t n, int64_t* result_dev,
+                        void* workspace, cudaStream_t s, const MsPublish& pub);
 // Zero a compaction workspace prefix and the two result words with one kernel (masked_select.cu).
 int ms_clear(void* workspace, size_t nbytes, int64_t* result, cudaStream_t s);
 // After coalescing: every one of the first `nt` operands is one contiguous run (copy.cu).

@@ -117,8 +117,16 @@ SIGNATURES = {
     "twg_fused_kind": (c_int, [c_void_p, POINTER(c_int)]),
     "twg_fused_launch": (c_int, [c_void_p, POINTER(IterDesc), POINTER(c_void_p), c_void_p]),
     "twg_fused_release": (c_int, [c_void_p]),
+    "twg_fused_select_workspace_bytes": (c_size_t, [c_int64]),
+    "twg_predicate_bits_bytes": (c_size_t, [c_int64]),
+    "twg_fused_predicate_bits": (c_int, [c_void_p, c_int64, POINTER(c_void_p), c_void_p, c_void_p]),
+    "twg_masked_select_bits_f32": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "twg_masked_select_bits_f32_publish": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_size_t,
+                                                   c_void_p, c_int64, c_void_p]),
     "twg_fused_select_f32": (c_int, [c_void_p, c_int, c_int64, POINTER(c_void_p), c_void_p, c_void_p, c_void_p,
                                      c_size_t, c_void_p]),
+    "twg_fused_select_f32_publish": (c_int, [c_void_p, c_int, c_int64, POINTER(c_void_p), c_void_p, c_void_p, c_void_p,
+                                             c_size_t, c_void_p, c_int64, c_void_p]),
     "twg_fused_set_nvrtc_path": (c_int, [c_char_p]),
     "twg_fused_source": (c_int, [c_void_p, POINTER(c_char_p)]),
     "twg_fused_set_cache_dir": (c_int, [c_char_p]),
@@ -469,13 +477,13 @@ def fused(instrs, inputs, out_dtypes, *, shape=None, stream=None):
 
 
 def fused_select(instrs, inputs, src: int, *, stream=None):
-    """out = inputs[src][program(inputs)] in one kernel (dense f32 inputs); returns (values, kind)."""
+    """out = inputs[src][program(inputs)] with the mask as bits (dense f32 inputs); returns (values, kind)."""
     handle = fused_compile(instrs)
     n = int(inputs[0].size)
     dins = [DeviceArray(np.ascontiguousarray(i), stream=stream) for i in inputs]
     out = DeviceBuffer(max(4 * n, 4), stream=stream)
     result = DeviceBuffer(16, stream=stream)
-    ws_bytes = lib().twg_masked_select_workspace_bytes(n)
+    ws_bytes = lib().twg_fused_select_workspace_bytes(n)
     ws = DeviceBuffer(ws_bytes, stream=stream)
     ptrs = (c_void_p * len(dins))(*[d.ptr for d in dins])
     check(lib().twg_fused_select_f32(handle, src, n, ptrs, out.ptr, result.ptr, ws.ptr, ws_bytes, stream))
@@ -483,6 +491,41 @@ def fused_select(instrs, inputs, src: int, *, stream=None):
     if status != 0:
         raise TwgError(status, "fused select: the device-side scan reported an error")
     return out.download(np.float32, k, stream), fused_kind(handle)
+
+
+def predicate_bits(instrs, inputs, *, stream=None):
+    """The predicate `instrs` over dense f32 inputs as a bool array, computed on the device as one
+    bit per element (twg_fused_predicate_bits) and unpacked here."""
+    handle = fused_compile(instrs)
+    n = int(inputs[0].size)
+    dins = [DeviceArray(np.ascontiguousarray(i), stream=stream) for i in inputs]
+    nbytes = lib().twg_predicate_bits_bytes(n)
+    bits = DeviceBuffer(max(nbytes, 16), stream=stream)
+    ptrs = (c_void_p * len(dins))(*[d.ptr for d in dins])
+    check(lib().twg_fused_predicate_bits(handle, n, ptrs, bits.ptr, stream))
+    packed = bits.download(np.uint8, nbytes, stream)
+    unpacked = np.unpackbits(packed, bitorder="little")
+    assert not unpacked[n:].any(), "bits at and beyond numel must be zero"
+    return unpacked[:n].astype(np.bool_)
+
+
+def masked_select_bits(src, mask, *, stream=None):
+    """masked_select of dense f32 `src` by a bool array handed over as bits (twg_masked_select_bits_f32)."""
+    src = np.ascontiguousarray(src, dtype=np.float32).ravel()
+    n = src.size
+    nbytes = lib().twg_predicate_bits_bytes(n)
+    packed = np.zeros(max(nbytes, 16), np.uint8)
+    packed[:(n + 7) // 8] = np.packbits(np.asarray(mask, np.bool_).ravel(), bitorder="little")
+    dsrc, dbits = DeviceArray(src if n else np.zeros(4, np.float32), stream=stream), DeviceArray(packed, stream=stream)
+    out = DeviceBuffer(max(4 * n, 4), stream=stream)
+    result = DeviceBuffer(16, stream=stream)
+    ws_bytes = lib().twg_masked_select_workspace_bytes(n)
+    ws = DeviceBuffer(max(ws_bytes, 256), stream=stream)
+    check(lib().twg_masked_select_bits_f32(dsrc.ptr, dbits.ptr, n, out.ptr, result.ptr, ws.ptr, ws_bytes, stream))
+    k, status = (int(v) for v in result.download(np.int64, 2, stream))
+    if status != 0:
+        raise TwgError(status, "masked_select by bits: the device-side scan reported an error")
+    return out.download(np.float32, k, stream)
 
 
 # the benchmark's chain  m = (relu(silu(a + b) + c) == 0) & (a != 0)  as the compile backend emits it

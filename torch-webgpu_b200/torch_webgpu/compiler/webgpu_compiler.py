@@ -201,7 +201,7 @@ def fuse_graph(gm: fx.GraphModule, options: dict | None = None) -> fx.GraphModul
         prog, inputs, out_nodes = build_program(group)
         if not out_nodes:
             continue
-        pattern = select_pattern(group, inputs, out_nodes) if options.get("fuse_select", False) else None
+        pattern = select_pattern(group, inputs, out_nodes) if options.get("fuse_select", True) else None
         if pattern is not None:
             sel, src_index = pattern
             kernel = FusedSelectKernel(prog, src_index)
@@ -244,15 +244,15 @@ def fuse_graph(gm: fx.GraphModule, options: dict | None = None) -> fx.GraphModul
 
 @register_backend
 def webgpu_backend(gm: fx.GraphModule, example_inputs: List[torch.Tensor], **kwargs) -> Callable:
-    """torch.compile(fn, backend=webgpu_backend[, options={"fuse_select": True}]).
+    """torch.compile(fn, backend=webgpu_backend[, options={"fuse_select": False}]).
 
     masked_select has a data-dependent output shape, so dynamo cuts the graph in front of it unless
-    `torch._dynamo.config.capture_dynamic_output_shape_ops = True`.  With that flag set and
-    `options={"fuse_select": True}`, a mask that feeds nothing but masked_select of one of the
-    chain's own inputs is never written to memory (one launch instead of two).  The option is off
-    by default: on B200 the one-launch kernel measures no faster than the fused mask kernel followed
-    by the compaction kernel (0.85 ms against 0.83 ms for the three-input silu chain over 2^28
-    elements), so the default keeps the two kernels that each run at the memory roofline.
+    `torch._dynamo.config.capture_dynamic_output_shape_ops = True`.  With that flag set, a mask that
+    feeds nothing but masked_select of one of the chain's own inputs is never written as a bool
+    tensor: the fused kernel writes it as one bit per element into scratch memory and the compaction
+    reads the bits (webgpu::run_fused_select; 0.75 ms against 0.83 ms for the three-input silu chain
+    over 2^28 elements on B200).  `options={"fuse_select": False}` keeps the bool tensor and the
+    plain masked_select; without the dynamo flag the graph break leaves no other choice.
     """
     options = dict(kwargs.pop("options", None) or {})
 

@@ -163,6 +163,18 @@ class PeerStoreExchange:
         self.abi.check(self.abi.lib().twg_masked_select_f32_publish(
             ctypes.byref(desc), src_ptr, mask_ptr, out_ptr, result_ptr, ws_ptr, ws_bytes, self.handle, seq, stream))
 
+    def select_bits_publish(self, seq: int, src_ptr: int, bits_ptr: int, n: int, out_ptr: int, result_ptr: int,
+                            ws_ptr: int, ws_bytes: int, stream) -> None:
+        """The compaction by a bit mask (twg_masked_select_bits_f32) publishing its count the same way."""
+        self.abi.check(self.abi.lib().twg_masked_select_bits_f32_publish(
+            src_ptr, bits_ptr, n, out_ptr, result_ptr, ws_ptr, ws_bytes, self.handle, seq, stream))
+
+    def fused_select_publish(self, seq: int, program, src_index: int, n: int, in_ptrs, out_ptr: int, result_ptr: int,
+                             ws_ptr: int, ws_bytes: int, stream) -> None:
+        """Predicate bits + that compaction as one call (twg_fused_select_f32)."""
+        self.abi.check(self.abi.lib().twg_fused_select_f32_publish(
+            program, src_index, n, in_ptrs, out_ptr, result_ptr, ws_ptr, ws_bytes, self.handle, seq, stream))
+
     def collect(self, seq: int, stream) -> None:
         self.abi.check(self.abi.lib().twg_exchange_collect(self.handle, seq, stream))
 
@@ -222,6 +234,18 @@ class NcclExchange:
                               ws_ptr: int, ws_bytes: int, stream) -> None:
         self.abi.check(self.abi.lib().twg_masked_select_f32(ctypes.byref(desc), src_ptr, mask_ptr, out_ptr, result_ptr,
                                                             ws_ptr, ws_bytes, stream))
+        self.publish(seq, result_ptr, stream)
+
+    def select_bits_publish(self, seq: int, src_ptr: int, bits_ptr: int, n: int, out_ptr: int, result_ptr: int,
+                            ws_ptr: int, ws_bytes: int, stream) -> None:
+        self.abi.check(self.abi.lib().twg_masked_select_bits_f32(src_ptr, bits_ptr, n, out_ptr, result_ptr, ws_ptr, ws_bytes,
+                                                                stream))
+        self.publish(seq, result_ptr, stream)
+
+    def fused_select_publish(self, seq: int, program, src_index: int, n: int, in_ptrs, out_ptr: int, result_ptr: int,
+                             ws_ptr: int, ws_bytes: int, stream) -> None:
+        self.abi.check(self.abi.lib().twg_fused_select_f32(program, src_index, n, in_ptrs, out_ptr, result_ptr, ws_ptr,
+                                                           ws_bytes, stream))
         self.publish(seq, result_ptr, stream)
 
     def collect(self, seq: int, stream) -> None:
