@@ -49,7 +49,7 @@ CHAIN_BYTES_PER_ELEM = {"bits": 12.125, "bytes": 13.0}
 # capture on 2^27 elements).  Constants taken from those captures, not measurements of this run:
 # the traffic of a streaming kernel is proportional to its element count, so it is scaled to the
 # elements of a launch.
-CHAIN_DRAM_BYTES_PER_ELEM = {"bits": 12.08, "bytes": 12.89}
+CHAIN_DRAM_BYTES_PER_ELEM = {"bits": 12.07, "bytes": 12.89}
 CHAIN_KERNEL = {"bits": "predicate_bits_kernel<AotChainMask> (fused chain, mask as bits: 12.125 B/elem)",
                 "bytes": "pw_contig_kernel<AotChainMask> (fused chain, bool mask: 13 B/elem)"}
 
@@ -897,17 +897,20 @@ def run_gpu_arm(args) -> None:
     for _ in range(2):
         compiled(*resident)
     barrier()
-    ev3 = Events(abi, 2)
+    ev3 = Events(abi, 2 + api_steps)
     ev3.record(0, stream)
-    for _ in range(api_steps):
+    for i in range(api_steps):
         sel = compiled(*resident)     # ends with the count read-back that sizes the result
         api_total = exchange_count(sel.numel())[1]
+        ev3.record(2 + i, stream)
     ev3.record(1, stream)
     ev3.sync(1)
+    api_each = [ev3.elapsed(2 + i - 1 if i else 0, 2 + i) for i in range(api_steps)]
     if api_total != total_k:
         raise RuntimeError(f"bench: the public API selected {api_total} elements, the C ABI leg {total_k}")
     api_ms = max(float(x) for x in rdv.share(repr(ev3.elapsed(0, 1) / api_steps).encode()))
     public_api = {"value": BATCH * SLAB / (api_ms * 1e-3) / 1e9, "unit": "Gelem/s", "ms_per_step": api_ms, "steps": api_steps,
+                  "ms_per_step_median_rank0": statistics.median(api_each), "ms_each_rank0": [round(x, 3) for x in api_each],
                   "api": "torch.compile(chain, backend=webgpu_backend)(a, b, c) on device-resident webgpu tensors"
                          + (", torch._dynamo.config.capture_dynamic_output_shape_ops=True (one graph, mask as bits)" if bits_mode
                             else " (graph break in front of masked_select, mask as a bool tensor)")
