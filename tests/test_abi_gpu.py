@@ -549,6 +549,25 @@ def test_predicate_bits_equal_the_bool_mask(abi, n):
         assert np.array_equal(got, m), f"predicate bits differ from the bool mask ({len(ins)} inputs, n={n})"
 
 
+@pytest.mark.parametrize("spread", [4.0, 30.0, 95.0])
+def test_bits_of_the_chain_equal_the_exact_chain_near_its_decision_boundary(abi, spread):
+    """The ahead-of-time bits kernel decides the cfg-5 predicate from a fast silu wherever that is
+    provably the exact chain's decision; here c = -silu(a + b) (1 + d) with |d| from 1e-8 to 1e-2,
+    a + b across +-2 spread, so that many elements lie inside, at the edge of and just outside the
+    band that is sent to the exact evaluation."""
+    n = 1 << 22
+    rng = np.random.default_rng(int(spread) + 300)
+    a = ((rng.random(n, dtype=np.float32) * 2 - 1) * np.float32(spread)).astype(np.float32)
+    bb = ((rng.random(n, dtype=np.float32) * 2 - 1) * np.float32(spread)).astype(np.float32)
+    s = oracle.unary("silu", oracle.binary("add", a, bb)).astype(np.float64)
+    d = 10.0 ** rng.uniform(-8, -2, n) * rng.choice([-1.0, 1.0], n)
+    c = (-s * (1.0 + d)).astype(np.float32)
+    got, _ = abi.predicate_bits(abi.CHAIN_MASK_PROGRAM, [a, bb, c]), None
+    (m,), _ = abi.fused(abi.CHAIN_MASK_PROGRAM, [a, bb, c], [np.bool_])
+    assert 0.1 < m.mean() < 0.9
+    assert np.array_equal(got, m), f"{int((got != m).sum())} decisions differ from the exact chain"
+
+
 @pytest.mark.parametrize("n,density", [(0, 0.5), (1, 1.0), (127, 0.5), (4096, 0.0), (4096, 1.0), (100003, 0.03),
                                        (100003, 0.5), ((1 << 22) + 9, 0.97), ((1 << 23), 1.0), ((1 << 23) + 1, 0.002)])
 def test_masked_select_by_bits_matches_the_oracle(abi, n, density):
@@ -629,9 +648,13 @@ def test_fused_select_on_the_decision_boundary_of_the_chain(abi):
     rng = np.random.default_rng(91)
     a = (rng.random(n, dtype=np.float32) * 8 - 4).astype(np.float32)
     bb = (rng.random(n, dtype=np.float32) * 8 - 4).astype(np.float32)
+    k = np.arange(n) % 8
+    a[k == 7] *= np.float32(11.0)                                 # a + b out to +-88: the whole range of exp
+    bb[k == 7] *= np.float32(11.0)
     s = oracle.unary("silu", oracle.binary("add", a, bb))
     c = (-s).astype(np.float32)                                   # silu(a + b) + c is within a few ulp of zero
-    k = np.arange(n) % 8
+    wide = k == 7
+    c[wide] = (c[wide].view(np.int32) + rng.integers(-60, 61, int(wide.sum())).astype(np.int32)).view(np.float32)
     for step, sel in ((1, k == 1), (2, k == 2), (40, k == 3), (400, k == 4)):
         c[sel] = (c[sel].view(np.int32) + step).view(np.float32)  # a few ulp to a few hundred ulp away
     for step, sel in ((1, k == 5), (300, k == 6)):

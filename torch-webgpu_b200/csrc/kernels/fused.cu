@@ -228,6 +228,34 @@ struct AotChainMask {
     out[0] = f_and(f_eq(y, 0.0f), f_ne(a, 0.0f));
   }
 };
+// The same predicate, decided from a fast evaluation wherever that is provably the decision of the
+// exact chain; used where only the mask is wanted as bits (predicate_bits_kernel is close to
+// issue-bound with the exact chain's 46 instructions per element).
+//   y == 0  <=>  silu(a + b) + c <= 0  (relu), so only the sign of q = silu(t) + c matters.
+// Fast silu: ex2.approx and rcp.approx.  Error of __expf(x): 2 + 1.173 |x| ulp; of the division
+// and of 1 + e: 3 ulp; the exact path's own silu: 3 ulp.  So both evaluations lie within
+// 6e-8 (8 + 1.2 |t|) |s| of the true value, and when |q| exceeds twice that (plus a floor that
+// covers flushed denormals) both sums have the sign of q.  Everything else - the band around
+// zero, NaN, infinities (every comparison with NaN is false) - takes the exact path.
+struct AotChainMaskQuick {
+  static constexpr int NIN = 3, NOUT = 1;
+  static constexpr unsigned kInByteMask = 0u, kOutByteMask = 1u;
+  __device__ __forceinline__ void operator()(const u32* in, u32* out) const {
+    const float a = as_f(in[0]), b = as_f(in[1]), c = as_f(in[2]);
+    const float t = f_add(a, b, 1.0f);
+    const float s = __fdividef(t, 1.0f + __expf(-t));
+    const float q = s + c;
+    const float band = fabsf(s) * fmaf(fabsf(t), 3.0e-7f, 2.0e-6f) + 1e-30f;
+    u32 y_is_zero;
+    if (fabsf(q) > band) {
+      y_is_zero = q < 0.0f ? 1u : 0u;
+    } else {
+      const float y = f_relu(f_add(f_silu(t), c, 1.0f));
+      y_is_zero = f_eq(y, 0.0f);
+    }
+    out[0] = f_and(y_is_zero, f_ne(a, 0.0f));
+  }
+};
 // Same chain that also keeps y.
 struct AotChainMaskY {
   static constexpr int NIN = 3, NOUT = 2;
@@ -282,7 +310,7 @@ struct AotEntry {
 };
 static const AotEntry kAot[] = {
     {kProgAddRelu, (int)(sizeof(kProgAddRelu) / sizeof(TwgFusedInstr)), &aot_launch<AotAddRelu>, nullptr},
-    {kProgChainMask, (int)(sizeof(kProgChainMask) / sizeof(TwgFusedInstr)), &aot_launch<AotChainMask>, &aot_bits<AotChainMask>},
+    {kProgChainMask, (int)(sizeof(kProgChainMask) / sizeof(TwgFusedInstr)), &aot_launch<AotChainMask>, &aot_bits<AotChainMaskQuick>},
     {kProgChainMaskY, (int)(sizeof(kProgChainMaskY) / sizeof(TwgFusedInstr)), &aot_launch<AotChainMaskY>, nullptr},
 };
 
