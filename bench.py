@@ -50,7 +50,7 @@ CHAIN_BYTES_PER_ELEM = {"bits": 12.125, "bytes": 13.0}
 # the traffic of a streaming kernel is proportional to its element count, so it is scaled to the
 # elements of a launch.
 CHAIN_DRAM_BYTES_PER_ELEM = {"bits": 12.07, "bytes": 12.89}
-CHAIN_KERNEL = {"bits": "predicate_bits_kernel<AotChainMask> (fused chain, mask as bits: 12.125 B/elem)",
+CHAIN_KERNEL = {"bits": "predicate_bits_kernel<AotChainMaskQuick> (fused chain, mask as bits: 12.125 B/elem)",
                 "bytes": "pw_contig_kernel<AotChainMask> (fused chain, bool mask: 13 B/elem)"}
 
 
