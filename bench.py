@@ -3,18 +3,19 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (the torch.compile configuration of BASELINE.json): a batch of 64 f32 [4096,4096] tensors
+Workload (the reference's torch.compile configuration): a batch of 64 f32 [4096,4096] tensors
 a, b, c ~ N(0,1); one step computes  y = relu(silu(a + b) + c),  m = (y == 0) & (a != 0)  and
 masked_select(a, m)  over the whole batch.  The batch is cut by its leading dimension over the N
-ranks (one process per GPU); the only exchange is an all-gather of one int64 count per rank.
+ranks (one process per GPU); the only exchange is one int64 count (and a status) per rank.
 Total work is fixed, so scaling is "strong".  Inputs are synthetic: every [4096,4096] slab is
 drawn with its own seed so that a rank can build its shard without generating the others.
 
 One JSON line is printed by rank 0.  `value` is whole-job Gelem/s with the inputs resident in HBM;
 `e2e` is the same metric through the public PyTorch API with pinned HOST buffers, upload of a, b, c
 and read-back of the selected values inside the timed region.  `roofline` describes the dominant
-kernel (the fused pointwise chain, 13 algorithmic bytes per element); `ops` lists achieved GB/s of
-every single op of the other configurations.  `--impl reference` times the CPU implementation of
+kernel (the fused pointwise chain, which hands its mask to the compaction as one bit per element:
+12.125 algorithmic bytes per element; 13 with --mask bytes); `ops` lists achieved GB/s of every
+single op of the other configurations.  `--impl reference` times the CPU implementation of
 the same path on the host cores instead.
 """
 from __future__ import annotations
