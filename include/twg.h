@@ -298,8 +298,9 @@ size_t twg_fused_select_workspace_bytes(int64_t numel);
 /* The two halves on their own.  twg_fused_predicate_bits writes the predicate of `numel` elements
  * as bits (bit i of 32-bit word w = element 32 w + i; twg_predicate_bits_bytes(numel) bytes, whole
  * 16-byte vectors, zero at and beyond numel; `bits` 16-byte aligned).  twg_masked_select_bits_f32
- * is masked_select of dense, 16-byte aligned `src` by such a mask; workspace as
- * twg_masked_select_workspace_bytes(numel), result words as twg_masked_select_f32. */
+ * is masked_select of dense, 16-byte aligned `src` by such a mask; workspace
+ * (twg_masked_select_workspace_bytes(numel), 256-byte aligned) and result words as
+ * twg_masked_select_f32. */
 size_t twg_predicate_bits_bytes(int64_t numel);
 int twg_fused_predicate_bits(const TwgFusedProgram* p, int64_t numel, const void* const* inputs, uint32_t* bits,
                              void* stream);

@@ -739,8 +739,8 @@ static int select_bits_impl(const float* src, const uint32_t* bits, int64_t nume
   TWG_REQUIRE(is_aligned(src, 16) && is_aligned(bits, 16) && is_aligned(out, 4),
               "twg_masked_select_bits_f32: src and bits must be 16-byte aligned, out 4-byte aligned");
   const size_t need = twg_masked_select_workspace_bytes(numel);
-  TWG_REQUIRE(workspace != nullptr && workspace_bytes >= need && is_aligned(workspace, 8),
-              "twg_masked_select_bits_f32: workspace of %zu bytes is smaller than the %zu required or misaligned",
+  TWG_REQUIRE(workspace != nullptr && workspace_bytes >= need && is_aligned(workspace, 256),
+              "twg_masked_select_bits_f32: workspace of %zu bytes is smaller than the %zu required or not 256-byte aligned",
               workspace_bytes, need);
   if (int rc = ms_select_from_bits(src, bits, out, numel, result_dev, workspace, s, pub)) return rc;
   g_last_path = kPathDense;
