@@ -90,6 +90,36 @@ def test_fused_program_analysis_and_ahead_of_time_match(abi):
         assert e.value.code == abi.TWG_ERR_INVALID
 
 
+def test_bit_mask_sizes_and_argument_checks_need_no_gpu(abi):
+    """Sizes of the predicate's bit mask and of the fused select's workspace, and the argument
+    checks of the entry points around them (every call below returns before touching a device)."""
+    L = abi.lib()
+    assert [L.twg_predicate_bits_bytes(n) for n in (-5, 0, 1, 128, 129, 1 << 20)] == [0, 0, 16, 16, 32, 1 << 17]
+    for n in (0, 1, 4097, (1 << 22) + 3):
+        ms = L.twg_masked_select_workspace_bytes(n)
+        assert L.twg_fused_select_workspace_bytes(n) == (ms + 255) // 256 * 256 + L.twg_predicate_bits_bytes(n)
+    chain = abi.fused_compile(abi.CHAIN_MASK_PROGRAM)
+    add_relu = abi.fused_compile([(abi.F_INPUT_F32, 0, 0, 0.0), (abi.F_INPUT_F32, 1, 0, 0.0), (abi.F_ADD, 0, 1, 1.0),
+                                  (abi.F_RELU, 2, 0, 0.0), (abi.F_OUTPUT, 3, 0, 0.0)])
+    three = (ctypes.c_void_p * 3)(256, 512, 768)          # never dereferenced: the calls fail before any launch
+    assert L.twg_fused_predicate_bits(None, 8, three, 1024, None) == abi.TWG_ERR_INVALID
+    assert L.twg_fused_predicate_bits(chain, -1, three, 1024, None) == abi.TWG_ERR_INVALID
+    assert L.twg_fused_predicate_bits(chain, 8, three, 1028, None) == abi.TWG_ERR_INVALID          # bits misaligned
+    assert b"16-byte aligned" in L.twg_last_error()
+    assert L.twg_fused_predicate_bits(add_relu, 8, three, 1024, None) == abi.TWG_ERR_UNSUPPORTED    # f32 output, no predicate
+    assert b"not a predicate" in L.twg_last_error()
+    misaligned = (ctypes.c_void_p * 3)(256, 516, 768)
+    assert L.twg_fused_predicate_bits(chain, 8, misaligned, 1024, None) == abi.TWG_ERR_UNSUPPORTED  # caller falls back
+    assert L.twg_masked_select_bits_f32(256, 1024, 8, 2048, None, 4096, 4096, None) == abi.TWG_ERR_INVALID   # no result words
+    assert L.twg_masked_select_bits_f32(256, 1024, 8, 2048, 8192, 4096, 16, None) == abi.TWG_ERR_INVALID     # workspace too small
+    assert b"smaller than" in L.twg_last_error()
+    assert L.twg_masked_select_bits_f32(260, 1024, 8, 2048, 8192, 4096, 4096, None) == abi.TWG_ERR_INVALID   # src misaligned
+    assert L.twg_fused_select_f32(chain, 3, 8, three, 2048, 8192, 4096, 1 << 20, None) == abi.TWG_ERR_INVALID  # src_input
+    assert L.twg_fused_select_f32(add_relu, 0, 8, three, 2048, 8192, 4096, 1 << 20, None) == abi.TWG_ERR_UNSUPPORTED
+    assert L.twg_fused_select_f32(chain, 0, 8, three, 2048, 8192, 4096, 64, None) == abi.TWG_ERR_INVALID      # workspace too small
+    assert L.twg_fused_select_f32(chain, 0, 8, three, 2048, 8192, 4100, 1 << 20, None) == abi.TWG_ERR_INVALID  # workspace misaligned
+
+
 def test_nvrtc_builds_generated_source_without_a_gpu(abi):
     prog = [(abi.F_INPUT_F32, 0, 0, 0.0), (abi.F_INPUT_BOOL, 1, 0, 0.0), (abi.F_GELU_TANH, 0, 0, 0.0),
             (abi.F_CONST_F32, 0, 0, 0.25), (abi.F_LE, 2, 3, 0.0), (abi.F_AND, 4, 1, 0.0), (abi.F_OUTPUT, 5, 0, 0.0),
