@@ -643,7 +643,8 @@ def test_nvrtc_results_are_cached_on_disk(abi, tmp_path):
 
 def test_fused_select_on_the_decision_boundary_of_the_chain(abi):
     """Inputs placed on and next to the boundary silu(a + b) + c == 0, huge and non-finite values:
-    the one-launch form must select exactly what the chain's mask says."""
+    the fused select (whose bits kernel decides most elements from a fast silu) must select exactly
+    what the exact chain's mask says."""
     n = 1 << 18
     rng = np.random.default_rng(91)
     a = (rng.random(n, dtype=np.float32) * 8 - 4).astype(np.float32)

@@ -10,8 +10,12 @@ This backend keeps the entry point and does the job for real:
   2. maximal runs of supported pointwise ops over one iteration shape are cut out of the graph
      (`partition`), each becomes one SSA program (`program.Program`) and one call to
      `torch.ops.webgpu.run_fused` - one kernel, no intermediate tensor touches HBM;
-  3. everything else (views, copies, masked_select, ops the library has no fused form for) stays
-     in the graph and runs through the dispatcher on the same device - there is no CPU fallback.
+  3. a group whose only output is a bool mask consumed by masked_select of one of the group's own
+     inputs becomes `torch.ops.webgpu.run_fused_select`: the mask travels as one bit per element
+     in scratch memory instead of as a bool tensor (possible when dynamo keeps masked_select in
+     the graph, see `webgpu_backend`);
+  4. everything else (views, copies, ops the library has no fused form for) stays in the graph
+     and runs through the dispatcher on the same device - there is no CPU fallback.
 """
 from __future__ import annotations
 
@@ -166,7 +170,8 @@ def select_pattern(group: list[fx.Node], inputs: list, out_nodes: list[fx.Node])
 
 
 class FusedSelectKernel:
-    """Callable placed in the rewritten graph: predicate and masked_select in one launch."""
+    """Callable placed in the rewritten graph: predicate (written as one bit per element) and the
+    compaction that reads those bits, in place of a bool mask tensor followed by masked_select."""
 
     def __init__(self, prog: P.Program, src_index: int):
         self.program = prog
